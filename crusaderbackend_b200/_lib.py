@@ -1,0 +1,64 @@
+"""ctypes binding of libcrusader_b200.so (the C ABI declared in include/crusader_b200.h).
+
+There is no fallback: if the shared library is missing or does not load, importing a compute entry
+point raises. Build it with `python -m crusaderbackend_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "lib" / "libcrusader_b200.so"
+
+CB_OK, CB_EINVAL, CB_ECUDA, CB_ETIMEOUT, CB_EUNSUPPORTED, CB_ENOMEM = 0, -1, -2, -3, -4, -5
+CB_MATH_TF32, CB_MATH_3XTF32, CB_MATH_FP32 = 0, 1, 2
+
+_f = C.c_void_p  # device pointers travel as integers
+_i = C.c_int
+_ll = C.c_longlong
+_fl = C.c_float
+_ctx = C.c_void_p
+
+# name -> (restype, argtypes); must list every symbol include/crusader_b200.h declares
+SIGNATURES = {
+    "cb_version": (C.c_char_p, []),
+    "cb_create": (_i, [C.POINTER(_ctx), _i, C.c_void_p]),
+    "cb_destroy": (_i, [_ctx]),
+    "cb_set_stream": (_i, [_ctx, C.c_void_p]),
+    "cb_set_math": (_i, [_ctx, _i]),
+    "cb_get_math": (_i, [_ctx]),
+    "cb_set_sync": (_i, [_ctx, _i]),
+    "cb_set_deterministic": (_i, [_ctx, _i]),
+    "cb_synchronize": (_i, [_ctx]),
+    "cb_last_error": (C.c_char_p, [_ctx]),
+    "cb_launch_count": (_ll, [_ctx]),
+    "cb_last_kernel": (C.c_char_p, [_ctx]),
+    "cb_gemm": (_i, [_ctx, _i, _i, _i, _i, _i, _f, _i, _f, _i, _f, _i, _i, _ll, _ll, _ll, _i]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library (once) and attaches the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built "
+            "(python -m crusaderbackend_b200.build). There is no CPU fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class CrusaderError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"crusader_b200 error {code}: {msg}")
+        self.code = code

@@ -1,0 +1,241 @@
+// C-ABI entry points: context management, error reporting and the GEMM dispatcher.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "cb_internal.h"
+#include "cb_ptx.cuh"
+
+namespace cb {
+
+int fail(cb_ctx* ctx, int code, const std::string& msg) {
+    if (ctx) ctx->last_error = msg;
+    return code;
+}
+
+int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return CB_OK;
+    return fail(ctx, CB_ECUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+static const char* status_name(int s) {
+    switch (s) {
+        case CBK_TIMEOUT_EMPTY: return "producer timed out waiting for a free stage";
+        case CBK_TIMEOUT_FULL: return "MMA issuer timed out waiting for operands";
+        case CBK_TIMEOUT_XFORM: return "MMA issuer timed out waiting for the split stage";
+        case CBK_TIMEOUT_TMEM_EMPTY: return "MMA issuer timed out waiting for a drained accumulator";
+        case CBK_TIMEOUT_TMEM_FULL: return "epilogue timed out waiting for an accumulator";
+        case CBK_TIMEOUT_XFORM_FULL: return "split warps timed out waiting for operands";
+        case CBK_TIMEOUT_DRAIN: return "drain after abort timed out";
+        default: return "unknown device status";
+    }
+}
+
+static int read_status(cb_ctx* ctx, const char* what) {
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    int st = 0;
+    e = cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "status readback");
+    if (st != 0) {
+        cudaMemset(ctx->d_status, 0, sizeof(int));
+        char buf[160];
+        snprintf(buf, sizeof(buf), "%s: device status %d (%s)", what, st, status_name(st));
+        return fail(ctx, CB_ETIMEOUT, buf);
+    }
+    return CB_OK;
+}
+
+int finish(cb_ctx* ctx, const char* what) {
+    if (!ctx->sync) return CB_OK;
+    return read_status(ctx, what);
+}
+
+int ensure_workspace(cb_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->workspace_bytes) return CB_OK;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "workspace growth sync");
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + 255) & ~size_t(255);
+    e = cudaMalloc(&ctx->workspace, want);
+    if (e != cudaSuccess) {
+        check_cuda(ctx, e, "workspace cudaMalloc");
+        return CB_ENOMEM;
+    }
+    ctx->workspace_bytes = want;
+    return CB_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn resolve_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int encode_tmap(cb_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides,
+                int swizzle_bytes) {
+    EncodeTiledFn fn = resolve_encode();
+    if (!fn) return fail(ctx, CB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t gd[5];
+    cuuint64_t gs[4];
+    cuuint32_t bd[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        gd[i] = dims[i];
+        bd[i] = box[i];
+        es[i] = elem_strides ? elem_strides[i] : 1;
+    }
+    for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+    CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+    else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    else if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    else if (swizzle_bytes == 129) sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bd, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[256];
+        snprintf(buf, sizeof(buf),
+                 "cuTensorMapEncodeTiled failed (CUresult %d): rank %d dims [%llu %llu %llu %llu] box [%u %u %u %u]",
+                 (int)r, rank, (unsigned long long)gd[0], (unsigned long long)(rank > 1 ? gd[1] : 0),
+                 (unsigned long long)(rank > 2 ? gd[2] : 0), (unsigned long long)(rank > 3 ? gd[3] : 0), bd[0],
+                 rank > 1 ? bd[1] : 0, rank > 2 ? bd[2] : 0, rank > 3 ? bd[3] : 0);
+        return fail(ctx, CB_ECUDA, buf);
+    }
+    return CB_OK;
+}
+
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+const char* cb_version(void) { return "crusader_b200 0.1 (sm_100a)"; }
+
+int cb_create(cb_ctx** out, int device, void* cuda_stream) {
+    if (!out) return CB_EINVAL;
+    *out = nullptr;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) return CB_ECUDA;
+    if (device < 0 || device >= ndev) return CB_EINVAL;
+    if (cudaSetDevice(device) != cudaSuccess) return CB_ECUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return CB_ECUDA;
+    if (prop.major != 10) {
+        fprintf(stderr, "crusader_b200: device %d is sm_%d%d; this library only carries sm_100a code\n", device,
+                prop.major, prop.minor);
+        return CB_EUNSUPPORTED;
+    }
+    cb_ctx* ctx = new (std::nothrow) cb_ctx();
+    if (!ctx) return CB_ENOMEM;
+    ctx->device = device;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return CB_ENOMEM;
+    }
+    *out = ctx;
+    return CB_OK;
+}
+
+int cb_destroy(cb_ctx* ctx) {
+    if (!ctx) return CB_EINVAL;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    delete ctx;
+    return CB_OK;
+}
+
+int cb_set_stream(cb_ctx* ctx, void* cuda_stream) {
+    if (!ctx) return CB_EINVAL;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    return CB_OK;
+}
+
+int cb_set_math(cb_ctx* ctx, int mode) {
+    if (!ctx) return CB_EINVAL;
+    if (mode != CB_MATH_TF32 && mode != CB_MATH_3XTF32 && mode != CB_MATH_FP32)
+        return fail(ctx, CB_EINVAL, "cb_set_math: unknown mode");
+    ctx->math = mode;
+    return CB_OK;
+}
+
+int cb_get_math(const cb_ctx* ctx) { return ctx ? ctx->math : CB_EINVAL; }
+
+int cb_set_sync(cb_ctx* ctx, int on) {
+    if (!ctx) return CB_EINVAL;
+    ctx->sync = on ? 1 : 0;
+    return CB_OK;
+}
+
+int cb_set_deterministic(cb_ctx* ctx, int on) {
+    if (!ctx) return CB_EINVAL;
+    ctx->deterministic = on ? 1 : 0;
+    return CB_OK;
+}
+
+int cb_synchronize(cb_ctx* ctx) {
+    if (!ctx) return CB_EINVAL;
+    return read_status(ctx, "cb_synchronize");
+}
+
+const char* cb_last_error(const cb_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+long long cb_launch_count(const cb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+const char* cb_last_kernel(const cb_ctx* ctx) { return ctx ? ctx->last_kernel : "none"; }
+
+int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
+            int ldb, float* C, int ldc, int batch, long long strideA, long long strideB, long long strideC,
+            int accumulate) {
+    if (!ctx) return CB_EINVAL;
+    if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(ctx, CB_EINVAL, "cb_gemm: negative extent");
+    if (M == 0 || N == 0 || batch == 0) return CB_OK;
+    if (!A || !B || !C) return fail(ctx, CB_EINVAL, "cb_gemm: null operand");
+    if (lda < (transA ? M : K) || ldb < (transB ? K : N) || ldc < N)
+        return fail(ctx, CB_EINVAL, "cb_gemm: leading dimension smaller than the row length");
+    if (K == 0) {
+        if (!accumulate) {
+            for (int b = 0; b < batch; ++b) {
+                cudaError_t e = cudaMemset2DAsync(C + (long long)b * strideC, (size_t)ldc * 4, 0, (size_t)N * 4, M,
+                                                  ctx->stream);
+                if (e != cudaSuccess) return check_cuda(ctx, e, "cb_gemm: clear of C for K == 0");
+            }
+        }
+        return finish(ctx, "cb_gemm");
+    }
+    GemmCall g;
+    g.I = N; g.J = M; g.K = K; g.batch = batch;
+    g.P = B; g.ldp = ldb; g.strideP = strideB; g.p_mn = transB ? 0 : 1;
+    g.Q = A; g.ldq = lda; g.strideQ = strideA; g.q_mn = transA ? 1 : 0;
+    g.C = C; g.ldc = ldc; g.strideC = strideC; g.out_mode = 0;
+    g.accumulate = accumulate ? 1 : 0;
+    int rc;
+    if (ctx->math != CB_MATH_FP32 && umma_gemm_eligible(g))
+        rc = launch_umma_gemm(ctx, g, ctx->math == CB_MATH_3XTF32);
+    else
+        rc = launch_simt_gemm(ctx, g);
+    if (rc != CB_OK) return rc;
+    return finish(ctx, "cb_gemm");
+}
+
+}  // extern "C"

@@ -1,0 +1,67 @@
+// Host-side internals shared by the C-ABI translation units: the context object, error helpers,
+// tensor-map encoding (cuTensorMapEncodeTiled resolved at run time through the CUDA runtime, so the
+// library does not link against libcuda) and the launch wrappers of each kernel family.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/crusader_b200.h"
+
+struct cb_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int math = CB_MATH_TF32;
+    int sync = 0;
+    int deterministic = 0;
+    int* d_status = nullptr;       // device status word (0 = ok, CBK_* otherwise)
+    void* workspace = nullptr;     // scratch: split-K partials, packed filters
+    size_t workspace_bytes = 0;
+    long long launches = 0;
+    int sm_count = 148;
+    int max_smem_optin = 0;
+    std::string last_error;
+    const char* last_kernel = "none";
+};
+
+namespace cb {
+
+int fail(cb_ctx* ctx, int code, const std::string& msg);
+int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what);
+// Returns after an optional sync; maps a non-zero device status word to CB_ETIMEOUT.
+int finish(cb_ctx* ctx, const char* what);
+// Grows the context workspace to at least `bytes` (stream-ordered with respect to earlier users
+// because growth synchronises the stream before freeing the old block).
+int ensure_workspace(cb_ctx* ctx, size_t bytes);
+
+// Encodes a tiled fp32 tensor map. dims/box are innermost-first; strides_bytes has rank-1 entries
+// (the innermost stride is 4 bytes). swizzle_bytes in {0, 32, 64, 128}, or 129 for
+// the 128-byte swizzle with 32-byte atoms. elem_strides may be null (all 1).
+int encode_tmap(cb_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides,
+                int swizzle_bytes);
+
+// Fused per-element tail applied while the accumulator is written out.
+struct Epilogue {
+    const float* bias_i = nullptr;  // added per UMMA-M index (null = none)
+    const float* bias_j = nullptr;  // added per UMMA-N index (null = none)
+    int relu = 0;
+};
+
+// D[i][j] = sum_k P[i][k] * Q[j][k]; i < I tiles of 128 (UMMA M), j < J (UMMA N).
+// p_mn / q_mn: operand stored with the i / j index contiguous (MN-major) instead of k (K-major).
+// out_mode 0: C[j*ldc + i]; out_mode 1: C[i*ldc + j].
+struct GemmCall {
+    int I = 0, J = 0, K = 0, batch = 1;
+    const float* P = nullptr; long long ldp = 0, strideP = 0; int p_mn = 0;
+    const float* Q = nullptr; long long ldq = 0, strideQ = 0; int q_mn = 0;
+    float* C = nullptr; long long ldc = 0, strideC = 0; int out_mode = 0;
+    int accumulate = 0;
+    Epilogue ep;
+};
+bool umma_gemm_eligible(const GemmCall& g);
+int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3);
+int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g);
+
+}  // namespace cb
