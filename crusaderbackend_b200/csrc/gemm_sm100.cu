@@ -34,6 +34,7 @@ struct GemmParams {
     int mi, bn;            // P sub-tiles per CTA tile, UMMA N
     int stages;
     int num_kb, splits, kb_per_split;
+    int kc;                // k-blocks per accumulation chunk: the accumulator is drained to C every kc blocks
     int tmem_cols;         // allocated TMEM columns (power of two >= 2*bn)
     int p_batched, q_batched;
     float* C;
@@ -203,12 +204,15 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                     if (!ok) break;
                 }
                 tc_fence_after();
+                const int kc_pos = (kb - it.kb0) % p.kc;
+                const bool chunk_first = kc_pos == 0;
+                const bool chunk_last = kc_pos == p.kc - 1 || kb == it.kb1 - 1;
                 const uint32_t sP = tiles_base + s * stage_bytes;
                 const uint32_t sQ = sP + p_bytes;
                 for (int m = 0; m < p.mi && ok; ++m) {
                     const uint32_t u = sub + (uint32_t)m;
                     const uint32_t a = u & 1u;
-                    if (kb == it.kb0) {
+                    if (chunk_first) {
                         // first product into this accumulator: the epilogue must have drained its last use
                         ok = warp_wait(smem_u32(&ps.tempty[a]), ((u >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
                                        CBK_TIMEOUT_TMEM_EMPTY);
@@ -217,14 +221,14 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                     }
                     if (lane == 0) {
                         const uint32_t d_tmem = tmem_base + a * acc_stride;
-                        const uint32_t pm = sP + (P_MN ? m * 4u * 4096u : m * (uint32_t)kPTileBytes);
+                        const uint32_t pm = sP + (uint32_t)m * (uint32_t)kPTileBytes;
 #pragma unroll
                         for (int kk = 0; kk < kBK / 8; ++kk) {
                             const uint32_t p_off = P_MN ? kk * 1024u : kk * 32u;
                             const uint32_t q_off = Q_MN ? kk * 1024u : kk * 32u;
                             const uint64_t dP = P_MN ? desc_mn(pm + p_off) : desc_k(pm + p_off);
                             const uint64_t dQ = Q_MN ? desc_mn(sQ + q_off) : desc_k(sQ + q_off);
-                            const uint32_t first = (kb == it.kb0 && kk == 0) ? 0u : 1u;
+                            const uint32_t first = (chunk_first && kk == 0) ? 0u : 1u;
                             if (X3) {
                                 const uint64_t dPl = P_MN ? desc_mn(pm + hi_bytes + p_off) : desc_k(pm + hi_bytes + p_off);
                                 const uint64_t dQl = Q_MN ? desc_mn(sQ + hi_bytes + q_off) : desc_k(sQ + hi_bytes + q_off);
@@ -239,16 +243,15 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                     __syncwarp();
                 }
                 if (!ok) break;
-                if (lane == 0) tc_commit(smem_u32(&ps.empty[s]));  // stage reusable once these MMAs retire
+                if (lane == 0) {
+                    tc_commit(smem_u32(&ps.empty[s]));  // stage reusable once these MMAs retire
+                    if (chunk_last)
+                        for (int m = 0; m < p.mi; ++m) tc_commit(smem_u32(&ps.tfull[(sub + m) & 1u]));
+                }
                 __syncwarp();
+                if (chunk_last) sub += (uint32_t)p.mi;
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
             }
-            if (!ok) break;
-            if (lane == 0) {
-                for (int m = 0; m < p.mi; ++m) tc_commit(smem_u32(&ps.tfull[(sub + m) & 1u]));
-            }
-            __syncwarp();
-            sub += (uint32_t)p.mi;
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (TMEM -> global)
@@ -258,62 +261,67 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
             const WorkItem it = decode_work(p, w);
             float* Cb = p.C + (long long)it.b * p.strideC;
-            const bool add_bias = (it.split == 0);
-            for (int m = 0; m < p.mi && ok; ++m, ++sub) {
-                const uint32_t a = sub & 1u;
-                ok = mbar_wait(smem_u32(&ps.tfull[a]), (sub >> 1) & 1u, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const int i = it.i0 + 128 * m + 32 * quarter + lane;
-                const bool i_ok = i < p.I;
-                float bi = 0.f;
-                if (p.bias_i != nullptr && i_ok && add_bias) bi = p.bias_i[i];
-                const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
-                for (int c = 0; c < p.bn; c += 16) {
-                    if (it.j0 + c >= p.J) break;  // warp-uniform
-                    uint32_t r[16];
-                    tmem_ld16(t_row + (uint32_t)c, r);
-                    tmem_ld_wait();
-                    if (!i_ok) continue;
-                    if (p.out_mode == 0) {
+            const int nchunks = (it.kb1 - it.kb0 + p.kc - 1) / p.kc;
+            for (int ch = 0; ch < nchunks && ok; ++ch) {
+                const bool add_bias = (it.split == 0 && ch == 0);
+                const bool add_old = p.accumulate || ch > 0;      // later chunks add onto what this thread wrote
+                const bool relu_now = p.relu && ch == nchunks - 1;
+                for (int m = 0; m < p.mi && ok; ++m, ++sub) {
+                    const uint32_t a = sub & 1u;
+                    ok = mbar_wait(smem_u32(&ps.tfull[a]), (sub >> 1) & 1u, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int i = it.i0 + 128 * m + 32 * quarter + lane;
+                    const bool i_ok = i < p.I;
+                    float bi = 0.f;
+                    if (p.bias_i != nullptr && i_ok && add_bias) bi = p.bias_i[i];
+                    const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
+                    for (int c = 0; c < p.bn; c += 16) {
+                        if (it.j0 + c >= p.J) break;  // warp-uniform
+                        uint32_t r[16];
+                        tmem_ld16(t_row + (uint32_t)c, r);
+                        tmem_ld_wait();
+                        if (!i_ok) continue;
+                        if (p.out_mode == 0) {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const int j = it.j0 + c + e;
-                            if (j < p.J) {
-                                float v = __uint_as_float(r[e]) + bi;
-                                if (p.bias_j != nullptr && add_bias) v += p.bias_j[j];
-                                float* dst = Cb + (long long)j * p.ldc + i;
-                                if (p.atomic_out) {
-                                    atomicAdd(dst, v);
-                                } else {
-                                    if (p.accumulate) v += *dst;
-                                    if (p.relu) v = fmaxf(v, 0.f);
-                                    *dst = v;
+                            for (int e = 0; e < 16; ++e) {
+                                const int j = it.j0 + c + e;
+                                if (j < p.J) {
+                                    float v = __uint_as_float(r[e]) + bi;
+                                    if (p.bias_j != nullptr && add_bias) v += p.bias_j[j];
+                                    float* dst = Cb + (long long)j * p.ldc + i;
+                                    if (p.atomic_out) {
+                                        atomicAdd(dst, v);
+                                    } else {
+                                        if (add_old) v += *dst;
+                                        if (relu_now) v = fmaxf(v, 0.f);
+                                        *dst = v;
+                                    }
                                 }
                             }
-                        }
-                    } else {
-                        float* row = Cb + (long long)i * p.ldc + it.j0 + c;
+                        } else {
+                            float* row = Cb + (long long)i * p.ldc + it.j0 + c;
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const int j = it.j0 + c + e;
-                            if (j < p.J) {
-                                float v = __uint_as_float(r[e]) + bi;
-                                if (p.bias_j != nullptr && add_bias) v += p.bias_j[j];
-                                if (p.atomic_out) {
-                                    atomicAdd(row + e, v);
-                                } else {
-                                    if (p.accumulate) v += row[e];
-                                    if (p.relu) v = fmaxf(v, 0.f);
-                                    row[e] = v;
+                            for (int e = 0; e < 16; ++e) {
+                                const int j = it.j0 + c + e;
+                                if (j < p.J) {
+                                    float v = __uint_as_float(r[e]) + bi;
+                                    if (p.bias_j != nullptr && add_bias) v += p.bias_j[j];
+                                    if (p.atomic_out) {
+                                        atomicAdd(row + e, v);
+                                    } else {
+                                        if (add_old) v += row[e];
+                                        if (relu_now) v = fmaxf(v, 0.f);
+                                        row[e] = v;
+                                    }
                                 }
                             }
                         }
                     }
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&ps.tempty[a]));
                 }
-                tc_fence_before();
-                mbar_arrive(smem_u32(&ps.tempty[a]));
             }
         }
     } else {
@@ -509,7 +517,10 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
             const long long tiles = (long long)g.batch * ((g.I + 128 * mi - 1) / (128 * mi)) *
                                     ((g.J + bn_eff - 1) / bn_eff);
             int splits = 1;
-            if (!ctx->deterministic && g.ep.relu == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8) {
+            // split K across CTAs (atomic adds into C) only for small outputs: atomics on a large C cost more
+            // than the idle SMs they would fill
+            if (!ctx->deterministic && g.ep.relu == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8 &&
+                (long long)g.I * g.J * g.batch <= 65536) {
                 splits = (int)(ctx->sm_count / tiles);
                 if (splits > num_kb / 4) splits = num_kb / 4;
                 if (splits < 1) splits = 1;
@@ -539,6 +550,9 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     gp.splits = best_splits;
     gp.kb_per_split = (num_kb + gp.splits - 1) / gp.splits;
     gp.splits = (num_kb + gp.kb_per_split - 1) / gp.kb_per_split;  // no empty split
+    // 3xTF32: the tensor core's fp32 accumulation error grows with the number of accumulated products, so the
+    // accumulator is drained into C (round-to-nearest fp32 adds) every 512 k
+    gp.kc = x3 ? 16 : (1 << 30);
     int cols = 32;
     while (cols < 2 * gp.bn) cols <<= 1;
     gp.tmem_cols = cols;

@@ -1,0 +1,613 @@
+// Memory-bound neighbours of the contraction path: per-(c,h,w) BatchNorm, ReLU, average / global-average
+// pooling, softmax + cross-entropy, bias add / bias gradient, Momentum-SGD and the in-place tensor arithmetic of
+// seblas::Tensor. All kernels stream HBM with 128-bit accesses where alignment allows, use grid-stride loops
+// sized to the SM count, and reduce with warp shuffles.
+#include "cb_internal.h"
+
+namespace cb {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(const cb_ctx* ctx, long long work_items, int per_block = kThreads) {
+    long long blocks = (work_items + per_block - 1) / per_block;
+    const long long cap = (long long)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ------------------------------------------------------------------ BatchNorm over the batch, per position
+// One thread owns VEC consecutive positions p (a float4 when VEC == 4) and walks the batch with stride P, so a
+// warp reads 512 contiguous bytes per sample. Two passes over X for mean / variance, third pass writes Y, xhat.
+template <int VEC>
+__global__ void bn_fwd_kernel(const float* __restrict__ X, const float* __restrict__ beta,
+                              const float* __restrict__ gamma, float* __restrict__ mean, float* __restrict__ var,
+                              float* __restrict__ Y, float* __restrict__ xhat, int N, long long P) {
+    const long long nvec = P / VEC;
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long p = v * VEC;
+        float m[VEC], s[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { m[e] = 0.f; s[e] = 0.f; }
+        for (int n = 0; n < N; ++n) {
+            float x[VEC];
+            if (VEC == 4) *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+            else x[0] = X[n * P + p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) m[e] += x[e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) m[e] /= (float)N;
+        for (int n = 0; n < N; ++n) {
+            float x[VEC];
+            if (VEC == 4) *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+            else x[0] = X[n * P + p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) s[e] += (x[e] - m[e]) * (x[e] - m[e]);
+        }
+        float inv[VEC], g[VEC], b[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            s[e] /= (float)N;
+            inv[e] = 1.0f / sqrtf(s[e] + 1e-8f);
+            g[e] = gamma[p + e];
+            b[e] = beta[p + e];
+        }
+        for (int n = 0; n < N; ++n) {
+            float x[VEC], y[VEC], h[VEC];
+            if (VEC == 4) *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+            else x[0] = X[n * P + p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                h[e] = (x[e] - m[e]) * inv[e];
+                y[e] = h[e] * g[e] + b[e];
+            }
+            if (VEC == 4) {
+                *reinterpret_cast<float4*>(Y + n * P + p) = *reinterpret_cast<float4*>(y);
+                if (xhat) *reinterpret_cast<float4*>(xhat + n * P + p) = *reinterpret_cast<float4*>(h);
+            } else {
+                Y[n * P + p] = y[0];
+                if (xhat) xhat[n * P + p] = h[0];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            if (mean) mean[p + e] = m[e];
+            if (var) var[p + e] = s[e];
+        }
+    }
+}
+
+template <int VEC>
+__global__ void bn_bwd_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
+                              const float* __restrict__ X, float* __restrict__ dX, int N, long long P) {
+    const long long nvec = P / VEC;
+    const float invN = 1.0f / (float)N;
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long p = v * VEC;
+        float m[VEC], s[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { m[e] = 0.f; s[e] = 0.f; }
+        for (int n = 0; n < N; ++n) {
+            float x[VEC];
+            if (VEC == 4) *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+            else x[0] = X[n * P + p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) m[e] += x[e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) m[e] *= invN;
+        // one pass gathers sum(dxhat * xc), sum(dxhat), sum(xc) and sum(xc^2)
+        float sdx[VEC], sd[VEC], sxc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { sdx[e] = 0.f; sd[e] = 0.f; sxc[e] = 0.f; }
+        float g[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) g[e] = gamma[p + e];
+        for (int n = 0; n < N; ++n) {
+            float x[VEC], dy[VEC];
+            if (VEC == 4) {
+                *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+                *reinterpret_cast<float4*>(dy) = *reinterpret_cast<const float4*>(dY + n * P + p);
+            } else {
+                x[0] = X[n * P + p];
+                dy[0] = dY[n * P + p];
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float xc = x[e] - m[e];
+                const float dxh = dy[e] * g[e];
+                s[e] += xc * xc;
+                sdx[e] += dxh * xc;
+                sd[e] += dxh;
+                sxc[e] += xc;
+            }
+        }
+        float inv[VEC], dvar[VEC], dmean[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const float varv = s[e] * invN + 1e-8f;
+            inv[e] = 1.0f / sqrtf(varv);
+            dvar[e] = sdx[e] * -0.5f * inv[e] * inv[e] * inv[e];
+            dmean[e] = -sd[e] * inv[e] + dvar[e] * (-2.0f * sxc[e]) * invN;
+        }
+        for (int n = 0; n < N; ++n) {
+            float x[VEC], dy[VEC], o[VEC];
+            if (VEC == 4) {
+                *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(X + n * P + p);
+                *reinterpret_cast<float4*>(dy) = *reinterpret_cast<const float4*>(dY + n * P + p);
+            } else {
+                x[0] = X[n * P + p];
+                dy[0] = dY[n * P + p];
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+                o[e] = dy[e] * g[e] * inv[e] + dvar[e] * (x[e] - m[e]) * 2.0f * invN + dmean[e] * invN;
+            if (VEC == 4) *reinterpret_cast<float4*>(dX + n * P + p) = *reinterpret_cast<float4*>(o);
+            else dX[n * P + p] = o[0];
+        }
+    }
+}
+
+template <int VEC>
+__global__ void bn_paramgrad_kernel(const float* __restrict__ dY, const float* __restrict__ xhat,
+                                    float* __restrict__ dgamma, float* __restrict__ dbeta, int N, long long P) {
+    const long long nvec = P / VEC;
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long p = v * VEC;
+        float sg[VEC], sb[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { sg[e] = 0.f; sb[e] = 0.f; }
+        for (int n = 0; n < N; ++n) {
+            float h[VEC], dy[VEC];
+            if (VEC == 4) {
+                *reinterpret_cast<float4*>(h) = *reinterpret_cast<const float4*>(xhat + n * P + p);
+                *reinterpret_cast<float4*>(dy) = *reinterpret_cast<const float4*>(dY + n * P + p);
+            } else {
+                h[0] = xhat[n * P + p];
+                dy[0] = dY[n * P + p];
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { sb[e] += dy[e]; sg[e] += dy[e] * h[e]; }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { dgamma[p + e] = sg[e]; dbeta[p + e] = sb[e]; }
+    }
+}
+
+// ------------------------------------------------------------------ elementwise
+enum { OP_RELU, OP_RELU_GRAD, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_ADDS, OP_SUBS, OP_MULS, OP_DIVS, OP_FILL,
+       OP_ADD_ZERO_B };
+
+template <int OP>
+__device__ __forceinline__ float ew(float a, float b, float c, float s) {
+    switch (OP) {
+        case OP_RELU: return fmaxf(a, 0.f);
+        case OP_RELU_GRAD: return a > 0.f ? b : 0.f;
+        case OP_ADD: case OP_ADD_ZERO_B: return a + b;
+        case OP_SUB: return a - b;
+        case OP_MUL: return a * b;
+        case OP_DIV: return a / b;
+        case OP_ADDS: return a + s;
+        case OP_SUBS: return a - s;
+        case OP_MULS: return a * s;
+        case OP_DIVS: return a / s;
+        default: return s;
+    }
+}
+
+// out[i] = f(a[i], b[i], s). OP_ADD_ZERO_B additionally clears b (gradient hand-over in the backward pass).
+template <int OP, bool VEC>
+__global__ void eltwise_kernel(const float* __restrict__ a, float* __restrict__ b, float* __restrict__ out, float s,
+                               long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if (VEC) {
+        const long long nv = n >> 2;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += stride) {
+            float4 x = a ? reinterpret_cast<const float4*>(a)[i] : make_float4(0, 0, 0, 0);
+            float4 y = b ? reinterpret_cast<const float4*>(b)[i] : make_float4(0, 0, 0, 0);
+            float4 r;
+            r.x = ew<OP>(x.x, y.x, 0, s); r.y = ew<OP>(x.y, y.y, 0, s);
+            r.z = ew<OP>(x.z, y.z, 0, s); r.w = ew<OP>(x.w, y.w, 0, s);
+            reinterpret_cast<float4*>(out)[i] = r;
+            if (OP == OP_ADD_ZERO_B) reinterpret_cast<float4*>(b)[i] = make_float4(0, 0, 0, 0);
+        }
+    } else {
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+            const float x = a ? a[i] : 0.f, y = b ? b[i] : 0.f;
+            out[i] = ew<OP>(x, y, 0, s);
+            if (OP == OP_ADD_ZERO_B) b[i] = 0.f;
+        }
+    }
+}
+
+template <int OP>
+int launch_eltwise(cb_ctx* ctx, const float* a, float* b, float* out, float s, long long n, const char* what) {
+    if (n == 0) return CB_OK;
+    const bool vec = (n % 4 == 0) && aligned16(a) && aligned16(b) && aligned16(out);
+    const int grid = grid_for(ctx, vec ? n / 4 : n);
+    if (vec) eltwise_kernel<OP, true><<<grid, kThreads, 0, ctx->stream>>>(a, b, out, s, n);
+    else eltwise_kernel<OP, false><<<grid, kThreads, 0, ctx->stream>>>(a, b, out, s, n);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    ctx->launches += 1;
+    return finish(ctx, what);
+}
+
+// ------------------------------------------------------------------ pooling
+// Non-overlapping rH x rW windows; one thread per output element, consecutive threads -> consecutive ow.
+__global__ void avgpool_kernel(const float* __restrict__ X, float* __restrict__ Y, long long total, int H, int W,
+                               int rH, int rW) {
+    const int OH = H / rH, OW = W / rW;
+    const float inv = 1.0f / (float)(rH * rW);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int ow = (int)(i % OW);
+        const long long t = i / OW;
+        const int oh = (int)(t % OH);
+        const long long c = t / OH;
+        const float* src = X + (c * H + (long long)oh * rH) * W + (long long)ow * rW;
+        float s = 0.f;
+        for (int a = 0; a < rH; ++a)
+            for (int b = 0; b < rW; ++b) s += src[a * W + b];
+        Y[i] = s * inv;
+    }
+}
+// One thread per INPUT element: every dX element of a covered window gets dY / (rH*rW), the rest zero.
+__global__ void avgpool_back_kernel(float* __restrict__ dX, const float* __restrict__ dY, long long total, int H,
+                                    int W, int rH, int rW) {
+    const int OH = H / rH, OW = W / rW;
+    const float inv = 1.0f / (float)(rH * rW);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int w = (int)(i % W);
+        const long long t = i / W;
+        const int h = (int)(t % H);
+        const long long c = t / H;
+        const int oh = h / rH, ow = w / rW;
+        dX[i] = (oh < OH && ow < OW) ? dY[(c * OH + oh) * OW + ow] * inv : 0.f;
+    }
+}
+// Global average pool: one warp per (n,c) plane.
+__global__ void gap_kernel(const float* __restrict__ X, float* __restrict__ Y, long long planes, int HW) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long pl = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; pl < planes; pl += warps) {
+        const float* src = X + pl * HW;
+        float s = 0.f;
+        for (int i = lane; i < HW; i += 32) s += src[i];
+        s = warp_sum(s);
+        if (lane == 0) Y[pl] = s / (float)HW;
+    }
+}
+__global__ void gap_back_kernel(float* __restrict__ dX, const float* __restrict__ dY, long long total, int HW) {
+    const float inv = 1.0f / (float)HW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        dX[i] = dY[i / HW] * inv;
+}
+
+// ------------------------------------------------------------------ softmax / cross entropy
+// One warp per row of `step` elements: y = exp(x - max) / (sum + 1e-10).
+__global__ void softmax_kernel(const float* __restrict__ X, float* __restrict__ Y, int rows, int step) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const float* x = X + (long long)r * step;
+        float mx = -1e15f;
+        for (int i = lane; i < step; i += 32) mx = fmaxf(mx, x[i]);
+        mx = warp_max(mx);
+        float s = 0.f;
+        for (int i = lane; i < step; i += 32) s += expf(x[i] - mx);
+        s = warp_sum(s);
+        const float inv = 1.0f / (s + 1e-10f);
+        for (int i = lane; i < step; i += 32) Y[(long long)r * step + i] = expf(x[i] - mx) * inv;
+    }
+}
+// dY = Y - labels and loss += sum(-log(Y + 1e-10) * labels); one atomic per block.
+__global__ void cross_entropy_kernel(const float* __restrict__ Y, const float* __restrict__ labels,
+                                     float* __restrict__ dY, float* __restrict__ loss, long long n) {
+    __shared__ float part[kThreads / 32];
+    float s = 0.f;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float y = Y[i], l = labels[i];
+        if (dY) dY[i] = y - l;
+        s += -logf(y + 1e-10f) * l;
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < kThreads / 32 ? part[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0 && loss) atomicAdd(loss, v);
+    }
+}
+
+// ------------------------------------------------------------------ bias
+__global__ void bias_add_kernel(float* __restrict__ Y, const float* __restrict__ bias, long long total, int C,
+                                int HW) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        Y[i] += bias[(i / HW) % C];
+}
+// db[c] (+)= sum over (n, hw) of dY[n,c,hw]; one block per channel.
+__global__ void bias_grad_kernel(const float* __restrict__ dY, float* __restrict__ db, int N, int C, int HW,
+                                 int accumulate) {
+    __shared__ float part[kThreads / 32];
+    const int c = blockIdx.x;
+    float s = 0.f;
+    const long long per = (long long)N * HW;
+    for (long long i = threadIdx.x; i < per; i += blockDim.x) {
+        const long long n = i / HW, r = i - n * HW;
+        s += dY[(n * C + c) * HW + r];
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < kThreads / 32 ? part[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) db[c] = accumulate ? db[c] + v : v;
+    }
+}
+
+// ------------------------------------------------------------------ Momentum-SGD over many tensors in one launch
+struct MomentumTensor {
+    float* w; float* g; float* m;
+    long long n;
+    int is_weight;
+};
+// blockIdx.y = tensor. w *= (1 - l2) for weight tensors, m = beta m + (1 - beta) g, w -= lr m, g = 0.
+__global__ void momentum_multi_kernel(const MomentumTensor* __restrict__ ts, float lr, float beta, float l2) {
+    const MomentumTensor t = ts[blockIdx.y];
+    const float decay = t.is_weight ? (1.0f - l2) : 1.0f;
+    const float omb = 1.0f - beta;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const bool vec = (t.n % 4 == 0) && (((uintptr_t)t.w | (uintptr_t)t.g | (uintptr_t)t.m) & 15u) == 0;
+    if (vec) {
+        const long long nv = t.n >> 2;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += stride) {
+            float4 w = reinterpret_cast<float4*>(t.w)[i];
+            const float4 g = reinterpret_cast<float4*>(t.g)[i];
+            float4 m = reinterpret_cast<float4*>(t.m)[i];
+            m.x = beta * m.x + omb * g.x; m.y = beta * m.y + omb * g.y;
+            m.z = beta * m.z + omb * g.z; m.w = beta * m.w + omb * g.w;
+            w.x = w.x * decay - lr * m.x; w.y = w.y * decay - lr * m.y;
+            w.z = w.z * decay - lr * m.z; w.w = w.w * decay - lr * m.w;
+            reinterpret_cast<float4*>(t.w)[i] = w;
+            reinterpret_cast<float4*>(t.m)[i] = m;
+            reinterpret_cast<float4*>(t.g)[i] = make_float4(0, 0, 0, 0);
+        }
+    } else {
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < t.n; i += stride) {
+            const float m = beta * t.m[i] + omb * t.g[i];
+            t.w[i] = t.w[i] * decay - lr * m;
+            t.m[i] = m;
+            t.g[i] = 0.f;
+        }
+    }
+}
+
+int done(cb_ctx* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    ctx->launches += 1;
+    return finish(ctx, what);
+}
+
+}  // namespace
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
+              float* xhat, int N, long long P) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd: negative extent");
+    if (N == 0 || P == 0) return CB_OK;
+    if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd: null operand");
+    const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(Y) && (!xhat || aligned16(xhat));
+    if (vec) bn_fwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
+    else bn_fwd_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
+    return done(ctx, "cb_bn_fwd");
+}
+
+int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, int N, long long P) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd: negative extent");
+    if (N == 0 || P == 0) return CB_OK;
+    if (!dY || !gamma || !X || !dX) return fail(ctx, CB_EINVAL, "cb_bn_bwd: null operand");
+    const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
+    if (vec) bn_bwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(dY, gamma, X, dX, N, P);
+    else bn_bwd_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(dY, gamma, X, dX, N, P);
+    return done(ctx, "cb_bn_bwd");
+}
+
+int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgamma, float* dbeta, int N, long long P) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_paramgrad: negative extent");
+    if (P == 0) return CB_OK;
+    if (!dY || !xhat || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_paramgrad: null operand");
+    const bool vec = (P % 4 == 0) && aligned16(xhat) && aligned16(dY);
+    if (vec) bn_paramgrad_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(dY, xhat, dgamma, dbeta, N, P);
+    else bn_paramgrad_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(dY, xhat, dgamma, dbeta, N, P);
+    return done(ctx, "cb_bn_paramgrad");
+}
+
+int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && (!X || !Y))) return fail(ctx, CB_EINVAL, "cb_relu: bad argument");
+    return launch_eltwise<OP_RELU>(ctx, X, nullptr, Y, 0.f, n, "cb_relu");
+}
+
+int cb_relu_grad(cb_ctx* ctx, const float* X, const float* dY, float* dX, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && (!X || !dY || !dX))) return fail(ctx, CB_EINVAL, "cb_relu_grad: bad argument");
+    return launch_eltwise<OP_RELU_GRAD>(ctx, X, const_cast<float*>(dY), dX, 0.f, n, "cb_relu_grad");
+}
+
+int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && !A)) return fail(ctx, CB_EINVAL, "cb_tensor_op: bad argument");
+    if (op >= CB_OP_ADD && op <= CB_OP_DIV && n > 0 && !B) return fail(ctx, CB_EINVAL, "cb_tensor_op: null B");
+    float* b = const_cast<float*>(B);
+    switch (op) {
+        case CB_OP_ADD: return launch_eltwise<OP_ADD>(ctx, A, b, A, 0.f, n, "cb_tensor_op(add)");
+        case CB_OP_SUB: return launch_eltwise<OP_SUB>(ctx, A, b, A, 0.f, n, "cb_tensor_op(sub)");
+        case CB_OP_MUL: return launch_eltwise<OP_MUL>(ctx, A, b, A, 0.f, n, "cb_tensor_op(mul)");
+        case CB_OP_DIV: return launch_eltwise<OP_DIV>(ctx, A, b, A, 0.f, n, "cb_tensor_op(div)");
+        case CB_OP_ADD_SCALAR: return launch_eltwise<OP_ADDS>(ctx, A, nullptr, A, scalar, n, "cb_tensor_op(add scalar)");
+        case CB_OP_SUB_SCALAR: return launch_eltwise<OP_SUBS>(ctx, A, nullptr, A, scalar, n, "cb_tensor_op(sub scalar)");
+        case CB_OP_MUL_SCALAR: return launch_eltwise<OP_MULS>(ctx, A, nullptr, A, scalar, n, "cb_tensor_op(mul scalar)");
+        case CB_OP_DIV_SCALAR: return launch_eltwise<OP_DIVS>(ctx, A, nullptr, A, scalar, n, "cb_tensor_op(div scalar)");
+        case CB_OP_FILL: return launch_eltwise<OP_FILL>(ctx, nullptr, nullptr, A, scalar, n, "cb_tensor_op(fill)");
+        default: return fail(ctx, CB_EINVAL, "cb_tensor_op: unknown op");
+    }
+}
+
+int cb_grad_handover(cb_ctx* ctx, float* dA, float* dA_reserve, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && (!dA || !dA_reserve))) return fail(ctx, CB_EINVAL, "cb_grad_handover: bad argument");
+    return launch_eltwise<OP_ADD_ZERO_B>(ctx, dA, dA_reserve, dA, 0.f, n, "cb_grad_handover");
+}
+
+int cb_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H, int W, int rH, int rW) {
+    if (!ctx) return CB_EINVAL;
+    if (NC < 0 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool: bad extent");
+    const long long total = NC * (H / rH) * (W / rW);
+    if (total == 0) return CB_OK;
+    if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_avgpool: null operand");
+    avgpool_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(X, Y, total, H, W, rH, rW);
+    return done(ctx, "cb_avgpool");
+}
+
+int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H, int W, int rH, int rW) {
+    if (!ctx) return CB_EINVAL;
+    if (NC < 0 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool_back: bad extent");
+    const long long total = NC * H * W;
+    if (total == 0) return CB_OK;
+    if (!dX || !dY) return fail(ctx, CB_EINVAL, "cb_avgpool_back: null operand");
+    avgpool_back_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(dX, dY, total, H, W, rH, rW);
+    return done(ctx, "cb_avgpool_back");
+}
+
+int cb_global_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int HW) {
+    if (!ctx) return CB_EINVAL;
+    if (NC < 0 || HW < 1) return fail(ctx, CB_EINVAL, "cb_global_avgpool: bad extent");
+    if (NC == 0) return CB_OK;
+    if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_global_avgpool: null operand");
+    gap_kernel<<<grid_for(ctx, NC * 32), kThreads, 0, ctx->stream>>>(X, Y, NC, HW);
+    return done(ctx, "cb_global_avgpool");
+}
+
+int cb_global_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int HW) {
+    if (!ctx) return CB_EINVAL;
+    if (NC < 0 || HW < 1) return fail(ctx, CB_EINVAL, "cb_global_avgpool_back: bad extent");
+    if (NC == 0) return CB_OK;
+    if (!dX || !dY) return fail(ctx, CB_EINVAL, "cb_global_avgpool_back: null operand");
+    gap_back_kernel<<<grid_for(ctx, NC * HW), kThreads, 0, ctx->stream>>>(dX, dY, NC * HW, HW);
+    return done(ctx, "cb_global_avgpool_back");
+}
+
+int cb_softmax(cb_ctx* ctx, const float* X, float* Y, int rows, int step) {
+    if (!ctx) return CB_EINVAL;
+    if (rows < 0 || step < 1) return fail(ctx, CB_EINVAL, "cb_softmax: bad extent");
+    if (rows == 0) return CB_OK;
+    if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_softmax: null operand");
+    softmax_kernel<<<grid_for(ctx, (long long)rows * 32), kThreads, 0, ctx->stream>>>(X, Y, rows, step);
+    return done(ctx, "cb_softmax");
+}
+
+int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY, float* loss_sum, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0) return fail(ctx, CB_EINVAL, "cb_cross_entropy: negative extent");
+    if (!Y || !labels) return fail(ctx, CB_EINVAL, "cb_cross_entropy: null operand");
+    if (loss_sum) {
+        cudaError_t e = cudaMemsetAsync(loss_sum, 0, sizeof(float), ctx->stream);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cb_cross_entropy: clear of the loss word");
+    }
+    if (n == 0) return CB_OK;
+    cross_entropy_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(Y, labels, dY, loss_sum, n);
+    return done(ctx, "cb_cross_entropy");
+}
+
+int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || C < 0 || HW < 0) return fail(ctx, CB_EINVAL, "cb_conv_bias: negative extent");
+    const long long total = (long long)N * C * HW;
+    if (total == 0) return CB_OK;
+    if (!Y || !bias) return fail(ctx, CB_EINVAL, "cb_conv_bias: null operand");
+    bias_add_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(Y, bias, total, C, HW);
+    return done(ctx, "cb_conv_bias");
+}
+
+int cb_conv_bias_grad(cb_ctx* ctx, const float* dY, float* db, int N, int C, int HW, int accumulate) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || C < 0 || HW < 0) return fail(ctx, CB_EINVAL, "cb_conv_bias_grad: negative extent");
+    if (C == 0) return CB_OK;
+    if (!dY || !db) return fail(ctx, CB_EINVAL, "cb_conv_bias_grad: null operand");
+    bias_grad_kernel<<<C, kThreads, 0, ctx->stream>>>(dY, db, N, C, HW, accumulate ? 1 : 0);
+    return done(ctx, "cb_conv_bias_grad");
+}
+
+int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
+                      const long long* sizes, const unsigned char* is_weight, float lr, float beta, float l2) {
+    if (!ctx) return CB_EINVAL;
+    if (ntensors < 0) return fail(ctx, CB_EINVAL, "cb_momentum_multi: negative tensor count");
+    if (ntensors == 0) return CB_OK;
+    if (!w || !g || !m || !sizes) return fail(ctx, CB_EINVAL, "cb_momentum_multi: null table");
+    if (ntensors > 65535) return fail(ctx, CB_EUNSUPPORTED, "cb_momentum_multi: more than 65535 tensors");
+    // descriptor table: staged through the context workspace (pinned-free path: small synchronous copy)
+    const size_t bytes = sizeof(MomentumTensor) * (size_t)ntensors;
+    int rc = ensure_workspace(ctx, bytes);
+    if (rc != CB_OK) return rc;
+    MomentumTensor* host = new MomentumTensor[ntensors];
+    long long biggest = 1;
+    for (int i = 0; i < ntensors; ++i) {
+        if (sizes[i] < 0 || (sizes[i] > 0 && (!w[i] || !g[i] || !m[i]))) {
+            delete[] host;
+            return fail(ctx, CB_EINVAL, "cb_momentum_multi: bad tensor entry");
+        }
+        host[i] = MomentumTensor{w[i], g[i], m[i], sizes[i], is_weight ? (int)is_weight[i] : 0};
+        if (sizes[i] > biggest) biggest = sizes[i];
+    }
+    cudaError_t e = cudaMemcpyAsync(ctx->workspace, host, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // host table is freed below
+    delete[] host;
+    if (e != cudaSuccess) return check_cuda(ctx, e, "cb_momentum_multi: descriptor upload");
+    int gx = (int)((biggest / 4 + kThreads - 1) / kThreads);
+    if (gx < 1) gx = 1;
+    if (gx > 64) gx = 64;
+    momentum_multi_kernel<<<dim3(gx, ntensors), kThreads, 0, ctx->stream>>>(
+        static_cast<const MomentumTensor*>(ctx->workspace), lr, beta, l2);
+    return done(ctx, "cb_momentum_multi");
+}
+
+int cb_momentum(cb_ctx* ctx, float* w, float* g, float* m, long long n, float lr, float beta, float l2,
+                int is_weight) {
+    unsigned char flag = is_weight ? 1 : 0;
+    return cb_momentum_multi(ctx, 1, &w, &g, &m, &n, &flag, lr, beta, l2);
+}
+
+}  // extern "C"
