@@ -35,7 +35,34 @@ SIGNATURES = {
     "cb_launch_count": (_ll, [_ctx]),
     "cb_last_kernel": (C.c_char_p, [_ctx]),
     "cb_gemm": (_i, [_ctx, _i, _i, _i, _i, _i, _f, _i, _f, _i, _f, _i, _i, _ll, _ll, _ll, _i]),
+    "cb_conv_fwd": (_i, [_ctx, _f, _f, _f, _f] + [_i] * 12),
+    "cb_conv_dgrad": (_i, [_ctx, _f, _f, _f] + [_i] * 11),
+    "cb_conv_wgrad": (_i, [_ctx, _f, _f, _f] + [_i] * 12),
+    "cb_conv_bias": (_i, [_ctx, _f, _f, _i, _i, _i]),
+    "cb_conv_bias_grad": (_i, [_ctx, _f, _f, _i, _i, _i, _i]),
+    "cb_linear_fwd": (_i, [_ctx, _f, _f, _f, _f, _i, _i, _i]),
+    "cb_linear_xgrad": (_i, [_ctx, _f, _f, _f, _i, _i, _i]),
+    "cb_linear_paramgrad": (_i, [_ctx, _f, _f, _f, _f, _i, _i, _i]),
+    "cb_bn_fwd": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_bwd": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_paramgrad": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
+    "cb_relu": (_i, [_ctx, _f, _f, _ll]),
+    "cb_relu_grad": (_i, [_ctx, _f, _f, _f, _ll]),
+    "cb_tensor_op": (_i, [_ctx, _i, _f, _f, _fl, _ll]),
+    "cb_grad_handover": (_i, [_ctx, _f, _f, _ll]),
+    "cb_avgpool": (_i, [_ctx, _f, _f, _ll, _i, _i, _i, _i]),
+    "cb_avgpool_back": (_i, [_ctx, _f, _f, _ll, _i, _i, _i, _i]),
+    "cb_global_avgpool": (_i, [_ctx, _f, _f, _ll, _i]),
+    "cb_global_avgpool_back": (_i, [_ctx, _f, _f, _ll, _i]),
+    "cb_softmax": (_i, [_ctx, _f, _f, _i, _i]),
+    "cb_cross_entropy": (_i, [_ctx, _f, _f, _f, _f, _ll]),
+    "cb_momentum": (_i, [_ctx, _f, _f, _f, _ll, _fl, _fl, _fl, _i]),
+    "cb_momentum_multi": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                               C.POINTER(_ll), C.POINTER(C.c_ubyte), _fl, _fl, _fl]),
 }
+
+CB_OP_ADD, CB_OP_SUB, CB_OP_MUL, CB_OP_DIV = 0, 1, 2, 3
+CB_OP_ADD_SCALAR, CB_OP_SUB_SCALAR, CB_OP_MUL_SCALAR, CB_OP_DIV_SCALAR, CB_OP_FILL = 4, 5, 6, 7, 8
 
 _lib = None
 

@@ -118,3 +118,132 @@ class Context:
     def sgemmNT(self, A, B, Cout):
         """seblas::sgemmNT: C = A @ B^T, B stored N x K (seblas/operations/cuGEMM.cu:1685)."""
         return self.gemm(A, B, Cout, transB=True)
+
+    # ---- convolution: arguments in the order of seblas::conv / convDerive / convError
+    @staticmethod
+    def _geo(W, X, stride, pad):
+        N, IC, IH, IW = X.shape
+        OC, IC2, FH, FW = W.shape
+        if IC2 != IC:
+            raise ValueError("conv: channel counts do not agree")
+        return [N, IC, IH, IW, OC, FH, FW, stride[0], stride[1], pad[0], pad[1]]
+
+    def conv(self, A, B, Cout, strideH=1, strideW=1, padH=0, padW=0, biases=None, relu=False):
+        """seblas::conv(A=filters OC x IC x FH x FW, B=input N x IC x IH x IW, C=output), seblas/operations/cuConv.cu:757."""
+        geo = self._geo(A, B, (strideH, strideW), (padH, padW))
+        self._check(self.lib.cb_conv_fwd(self.h, _ptr(A), _ptr(B), _ptr(Cout), _ptr(biases), *geo, int(relu)))
+        return Cout
+
+    def convDerive(self, A, B, Cout, strideH=1, strideW=1, padH=0, padW=0):
+        """seblas::convDerive(A=filters, B=dY, C=dX), seblas/operations/cuConv.cu:774."""
+        geo = self._geo(A, Cout, (strideH, strideW), (padH, padW))
+        self._check(self.lib.cb_conv_dgrad(self.h, _ptr(A), _ptr(B), _ptr(Cout), *geo))
+        return Cout
+
+    def convError(self, A, B, Cout, strideH=1, strideW=1, padH=0, padW=0, accumulate=True):
+        """seblas::convError(A=dY, B=input, C=filter gradient, accumulated), seblas/operations/cuConv.cu:793.
+        Returns A, as the reference does."""
+        geo = self._geo(Cout, B, (strideH, strideW), (padH, padW))
+        self._check(self.lib.cb_conv_wgrad(self.h, _ptr(A), _ptr(B), _ptr(Cout), *geo, int(accumulate)))
+        return A
+
+    def convBias(self, Y, biases):
+        N, Cc, H, W = Y.shape
+        self._check(self.lib.cb_conv_bias(self.h, _ptr(Y), _ptr(biases), N, Cc, H * W))
+        return Y
+
+    def convBiasGrad(self, dY, db, accumulate=False):
+        N, Cc, H, W = dY.shape
+        self._check(self.lib.cb_conv_bias_grad(self.h, _ptr(dY), _ptr(db), N, Cc, H * W, int(accumulate)))
+        return db
+
+    # ---- linear: seblas::linear / linearXGrad / linearParamGrad (seblas/operations/cuLinear.cu:1052-1115)
+    def linear(self, X, W, B, Y):
+        batch, IN = X.shape[0], X.numel() // X.shape[0]
+        self._check(self.lib.cb_linear_fwd(self.h, _ptr(X), _ptr(W), _ptr(B), _ptr(Y), batch, IN, W.shape[-2]))
+        return Y
+
+    def linearXGrad(self, dY, W, dX):
+        batch = dX.shape[0]
+        self._check(self.lib.cb_linear_xgrad(self.h, _ptr(dY), _ptr(W), _ptr(dX), batch, W.shape[-1], W.shape[-2]))
+        return dX
+
+    def linearParamGrad(self, dY, X, dW, dB):
+        batch = X.shape[0]
+        self._check(self.lib.cb_linear_paramgrad(self.h, _ptr(dY), _ptr(X), _ptr(dW), _ptr(dB), batch, dW.shape[-1],
+                                                 dW.shape[-2]))
+        return dW
+
+    # ---- neighbours
+    def batchNorm(self, X, beta, gamma, mean, var, Y, xHat):
+        N = X.shape[0]
+        self._check(self.lib.cb_bn_fwd(self.h, _ptr(X), _ptr(beta), _ptr(gamma), _ptr(mean), _ptr(var), _ptr(Y),
+                                       _ptr(xHat), N, X.numel() // N))
+        return Y
+
+    def batchNormGrad(self, dY, gamma, X, dX):
+        N = X.shape[0]
+        self._check(self.lib.cb_bn_bwd(self.h, _ptr(dY), _ptr(gamma), _ptr(X), _ptr(dX), N, X.numel() // N))
+        return dX
+
+    def batchNormParamGrads(self, dY, xHat, dGamma, dBeta):
+        N = dY.shape[0]
+        self._check(self.lib.cb_bn_paramgrad(self.h, _ptr(dY), _ptr(xHat), _ptr(dGamma), _ptr(dBeta), N,
+                                             dY.numel() // N))
+
+    def relu(self, X, Y):
+        self._check(self.lib.cb_relu(self.h, _ptr(X), _ptr(Y), X.numel()))
+        return Y
+
+    def reluGradFast(self, X, dY, dX):
+        self._check(self.lib.cb_relu_grad(self.h, _ptr(X), _ptr(dY), _ptr(dX), X.numel()))
+        return dX
+
+    def tensor_op(self, op: int, A, B=None, scalar: float = 0.0):
+        self._check(self.lib.cb_tensor_op(self.h, op, _ptr(A), _ptr(B), scalar, A.numel()))
+        return A
+
+    def grad_handover(self, dA, dAReserve):
+        self._check(self.lib.cb_grad_handover(self.h, _ptr(dA), _ptr(dAReserve), dA.numel()))
+        return dA
+
+    def avgPool(self, X, Y, rangeH=2, rangeW=2):
+        N, Cc, H, W = X.shape
+        self._check(self.lib.cb_avgpool(self.h, _ptr(X), _ptr(Y), N * Cc, H, W, rangeH, rangeW))
+        return Y
+
+    def avgPoolBack(self, dX, dY, rangeH=2, rangeW=2):
+        N, Cc, H, W = dX.shape
+        self._check(self.lib.cb_avgpool_back(self.h, _ptr(dX), _ptr(dY), N * Cc, H, W, rangeH, rangeW))
+        return dX
+
+    def globalAvgPool(self, X, Y):
+        N, Cc, H, W = X.shape
+        self._check(self.lib.cb_global_avgpool(self.h, _ptr(X), _ptr(Y), N * Cc, H * W))
+        return Y
+
+    def globalAvgPoolBack(self, dX, dY):
+        N, Cc, H, W = dX.shape
+        self._check(self.lib.cb_global_avgpool_back(self.h, _ptr(dX), _ptr(dY), N * Cc, H * W))
+        return dX
+
+    def softmax(self, A, out, step=None):
+        rows = A.shape[0]
+        step = step or A.numel() // rows
+        self._check(self.lib.cb_softmax(self.h, _ptr(A), _ptr(out), A.numel() // step, step))
+        return out
+
+    def crossEntropy(self, Y, labels, dY=None, loss=None):
+        self._check(self.lib.cb_cross_entropy(self.h, _ptr(Y), _ptr(labels), _ptr(dY), _ptr(loss), Y.numel()))
+        return loss
+
+    def momentumApply(self, X, Xgrad, V, lr, beta, l2=0.0, is_weight=False):
+        self._check(self.lib.cb_momentum(self.h, _ptr(X), _ptr(Xgrad), _ptr(V), X.numel(), lr, beta, l2,
+                                         int(is_weight)))
+
+    def momentumApplyMulti(self, params, grads, moms, is_weight, lr, beta, l2):
+        n = len(params)
+        arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() for t in ts])
+        sizes = (C.c_longlong * n)(*[t.numel() for t in params])
+        flags = (C.c_ubyte * n)(*[1 if f else 0 for f in is_weight])
+        self._check(self.lib.cb_momentum_multi(self.h, n, arr(params), arr(grads), arr(moms), sizes, flags, lr, beta, l2))

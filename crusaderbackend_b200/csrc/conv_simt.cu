@@ -1,0 +1,263 @@
+// CUDA-core fp32 convolution kernels (any filter size, stride and padding) and the cb_conv_* dispatchers.
+// These serve CB_MATH_FP32 and every geometry the tensor-core implicit-GEMM kernels do not cover; they compute
+// exact fp32 FMAs. Index maps follow seblas/operations/cuConv.cu:105-115 (forward) and the adjoint of it for the
+// two gradients (the reference's weight-gradient map at :570-571 is wrong for stride > 1 and is not reproduced).
+#include "cb_internal.h"
+
+namespace cb {
+namespace {
+
+struct ConvGeo {
+    int N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, OH, OW;
+};
+
+constexpr int kOcTile = 8;
+
+// Forward: one thread per output pixel, kOcTile output channels in registers; consecutive threads walk ow, so
+// X loads are coalesced and every weight load is a warp-wide broadcast.
+__global__ void __launch_bounds__(256) conv_fwd_simt(const float* __restrict__ W, const float* __restrict__ X,
+                                                     float* __restrict__ Y, const float* __restrict__ bias,
+                                                     const ConvGeo g, int relu) {
+    const long long pix = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long npix = (long long)g.N * g.OH * g.OW;
+    if (pix >= npix) return;
+    const int oc0 = blockIdx.y * kOcTile;
+    const int ow = (int)(pix % g.OW);
+    const long long t = pix / g.OW;
+    const int oh = (int)(t % g.OH);
+    const int n = (int)(t / g.OH);
+    float acc[kOcTile];
+#pragma unroll
+    for (int o = 0; o < kOcTile; ++o) acc[o] = (bias && oc0 + o < g.OC) ? bias[oc0 + o] : 0.f;
+    const float* Xn = X + (long long)n * g.IC * g.IH * g.IW;
+    const long long wstride = (long long)g.IC * g.FH * g.FW;
+    for (int ic = 0; ic < g.IC; ++ic) {
+        for (int fh = 0; fh < g.FH; ++fh) {
+            const int ih = oh * g.sH - g.pH + fh;
+            if (ih < 0 || ih >= g.IH) continue;
+            for (int fw = 0; fw < g.FW; ++fw) {
+                const int iw = ow * g.sW - g.pW + fw;
+                if (iw < 0 || iw >= g.IW) continue;
+                const float x = Xn[((long long)ic * g.IH + ih) * g.IW + iw];
+                const float* wp = W + ((long long)oc0 * g.IC + ic) * g.FH * g.FW + fh * g.FW + fw;
+#pragma unroll
+                for (int o = 0; o < kOcTile; ++o)
+                    if (oc0 + o < g.OC) acc[o] = fmaf(__ldg(wp + o * wstride), x, acc[o]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 0; o < kOcTile; ++o)
+        if (oc0 + o < g.OC) {
+            float v = acc[o];
+            if (relu) v = fmaxf(v, 0.f);
+            Y[(((long long)n * g.OC + oc0 + o) * g.OH + oh) * g.OW + ow] = v;
+        }
+}
+
+// Data gradient: one thread per dX pixel, kOcTile input channels in registers.
+__global__ void __launch_bounds__(256) conv_dgrad_simt(const float* __restrict__ W, const float* __restrict__ dY,
+                                                       float* __restrict__ dX, const ConvGeo g) {
+    const long long pix = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long npix = (long long)g.N * g.IH * g.IW;
+    if (pix >= npix) return;
+    const int ic0 = blockIdx.y * kOcTile;
+    const int iw = (int)(pix % g.IW);
+    const long long t = pix / g.IW;
+    const int ih = (int)(t % g.IH);
+    const int n = (int)(t / g.IH);
+    float acc[kOcTile];
+#pragma unroll
+    for (int o = 0; o < kOcTile; ++o) acc[o] = 0.f;
+    const float* dYn = dY + (long long)n * g.OC * g.OH * g.OW;
+    const int taps = g.FH * g.FW;
+    for (int fh = 0; fh < g.FH; ++fh) {
+        const int th = ih + g.pH - fh;
+        if (th < 0 || th % g.sH) continue;
+        const int oh = th / g.sH;
+        if (oh >= g.OH) continue;
+        for (int fw = 0; fw < g.FW; ++fw) {
+            const int tw = iw + g.pW - fw;
+            if (tw < 0 || tw % g.sW) continue;
+            const int ow = tw / g.sW;
+            if (ow >= g.OW) continue;
+            for (int oc = 0; oc < g.OC; ++oc) {
+                const float d = dYn[((long long)oc * g.OH + oh) * g.OW + ow];
+                const float* wp = W + ((long long)oc * g.IC + ic0) * taps + fh * g.FW + fw;
+#pragma unroll
+                for (int o = 0; o < kOcTile; ++o)
+                    if (ic0 + o < g.IC) acc[o] = fmaf(__ldg(wp + o * taps), d, acc[o]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 0; o < kOcTile; ++o)
+        if (ic0 + o < g.IC) dX[(((long long)n * g.IC + ic0 + o) * g.IH + ih) * g.IW + iw] = acc[o];
+}
+
+// Weight gradient: one block per (oc, ic) pair and batch slice; threads stride over the output pixels and keep up
+// to 9 filter taps in registers, then reduce across the block with warp shuffles.
+constexpr int kTapGroup = 9;
+__global__ void __launch_bounds__(256) conv_wgrad_simt(const float* __restrict__ dY, const float* __restrict__ X,
+                                                       float* __restrict__ dW, const ConvGeo g, int n_per_split,
+                                                       int mode /*0 store, 1 add, 2 atomic*/) {
+    __shared__ float part[8][kTapGroup];
+    const int oc = blockIdx.x, ic = blockIdx.y;
+    const int n0 = blockIdx.z * n_per_split;
+    const int n1 = min(g.N, n0 + n_per_split);
+    const int taps = g.FH * g.FW;
+    const int opix = g.OH * g.OW;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int t0 = 0; t0 < taps; t0 += kTapGroup) {
+        float acc[kTapGroup];
+#pragma unroll
+        for (int t = 0; t < kTapGroup; ++t) acc[t] = 0.f;
+        for (int n = n0; n < n1; ++n) {
+            const float* dyp = dY + ((long long)n * g.OC + oc) * opix;
+            const float* xp = X + ((long long)n * g.IC + ic) * g.IH * g.IW;
+            for (int q = threadIdx.x; q < opix; q += blockDim.x) {
+                const int oh = q / g.OW, ow = q - oh * g.OW;
+                const float d = dyp[q];
+#pragma unroll
+                for (int t = 0; t < kTapGroup; ++t) {
+                    const int tap = t0 + t;
+                    if (tap < taps) {
+                        const int fh = tap / g.FW, fw = tap - fh * g.FW;
+                        const int ih = oh * g.sH - g.pH + fh, iw = ow * g.sW - g.pW + fw;
+                        if (ih >= 0 && ih < g.IH && iw >= 0 && iw < g.IW) acc[t] = fmaf(d, xp[ih * g.IW + iw], acc[t]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTapGroup; ++t) {
+            float v = acc[t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) part[warp][t] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < kTapGroup && t0 + threadIdx.x < taps) {
+            float v = 0.f;
+            for (int w = 0; w < 8; ++w) v += part[w][threadIdx.x];
+            float* dst = dW + ((long long)oc * g.IC + ic) * taps + t0 + threadIdx.x;
+            if (mode == 2) atomicAdd(dst, v);
+            else if (mode == 1) *dst += v;
+            else *dst = v;
+        }
+        __syncthreads();
+    }
+}
+
+int make_geo(cb_ctx* ctx, ConvGeo& g, int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH,
+             int pW, const char* who) {
+    if (N < 0 || IC < 0 || OC < 0 || IH < 0 || IW < 0) return fail(ctx, CB_EINVAL, std::string(who) + ": negative extent");
+    if (FH < 1 || FW < 1 || sH < 1 || sW < 1 || pH < 0 || pW < 0)
+        return fail(ctx, CB_EINVAL, std::string(who) + ": filter, stride must be >= 1 and padding >= 0");
+    if (IH + 2 * pH < FH || IW + 2 * pW < FW) return fail(ctx, CB_EINVAL, std::string(who) + ": filter larger than the padded input");
+    g = ConvGeo{N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, (IH - FH + 2 * pH) / sH + 1, (IW - FW + 2 * pW) / sW + 1};
+    return CB_OK;
+}
+
+int after_launch(cb_ctx* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+    ctx->launches += 1;
+    ctx->last_kernel = "simt_fp32";
+    return finish(ctx, what);
+}
+
+}  // namespace
+
+// Tensor-core paths (conv_sm100.cu). Each returns CB_EUNSUPPORTED when the geometry is outside what it covers.
+int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
+                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of);
+int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate);
+
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
+                int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu) {
+    if (!ctx) return CB_EINVAL;
+    ConvGeo g;
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_fwd");
+    if (rc != CB_OK) return rc;
+    const long long npix = (long long)N * g.OH * g.OW;
+    if (npix == 0 || OC == 0) return CB_OK;
+    if (!W || !X || !Y) return fail(ctx, CB_EINVAL, "cb_conv_fwd: null operand");
+    if (ctx->math == CB_MATH_TF32) {  // the tensor-core kernels are TF32; 3xTF32 and FP32 requests keep fp32 accuracy on CUDA cores
+        rc = umma_conv_fwd(ctx, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, relu, false);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_fwd") : rc;
+    }
+    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((OC + kOcTile - 1) / kOcTile));
+    conv_fwd_simt<<<grid, 256, 0, ctx->stream>>>(W, X, Y, bias, g, relu ? 1 : 0);
+    return after_launch(ctx, "cb_conv_fwd");
+}
+
+int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
+                  int FH, int FW, int sH, int sW, int pH, int pW) {
+    if (!ctx) return CB_EINVAL;
+    ConvGeo g;
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_dgrad");
+    if (rc != CB_OK) return rc;
+    const long long npix = (long long)N * IH * IW;
+    if (npix == 0 || IC == 0) return CB_OK;
+    if (!W || !dY || !dX) return fail(ctx, CB_EINVAL, "cb_conv_dgrad: null operand");
+    if (ctx->math == CB_MATH_TF32) {
+        rc = umma_conv_fwd(ctx, W, dY, dX, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, true);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_dgrad") : rc;
+    }
+    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((IC + kOcTile - 1) / kOcTile));
+    conv_dgrad_simt<<<grid, 256, 0, ctx->stream>>>(W, dY, dX, g);
+    return after_launch(ctx, "cb_conv_dgrad");
+}
+
+int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                  int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
+    if (!ctx) return CB_EINVAL;
+    ConvGeo g;
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_wgrad");
+    if (rc != CB_OK) return rc;
+    if (OC == 0 || IC == 0) return CB_OK;
+    if (!dW) return fail(ctx, CB_EINVAL, "cb_conv_wgrad: null operand");
+    const size_t wbytes = (size_t)OC * IC * FH * FW * sizeof(float);
+    if ((long long)N * g.OH * g.OW == 0) {
+        if (!accumulate) {
+            cudaError_t e = cudaMemsetAsync(dW, 0, wbytes, ctx->stream);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "cb_conv_wgrad: clear");
+        }
+        return finish(ctx, "cb_conv_wgrad");
+    }
+    if (!dY || !X) return fail(ctx, CB_EINVAL, "cb_conv_wgrad: null operand");
+    if (ctx->math == CB_MATH_TF32) {
+        rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_wgrad") : rc;
+    }
+    if (OC > 65535 || IC > 65535) return fail(ctx, CB_EUNSUPPORTED, "cb_conv_wgrad: more than 65535 channels");
+    int splits = 1;
+    if (!ctx->deterministic) {
+        const long long pairs = (long long)OC * IC;
+        splits = (int)((4LL * ctx->sm_count + pairs - 1) / pairs);
+        if (splits > N) splits = N;
+        if (splits < 1) splits = 1;
+    }
+    const int nps = (N + splits - 1) / splits;
+    splits = (N + nps - 1) / nps;
+    int mode = accumulate ? 1 : 0;
+    if (splits > 1) {
+        mode = 2;
+        if (!accumulate) {
+            cudaError_t e = cudaMemsetAsync(dW, 0, wbytes, ctx->stream);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "cb_conv_wgrad: clear");
+        }
+    }
+    conv_wgrad_simt<<<dim3(OC, IC, splits), 256, 0, ctx->stream>>>(dY, X, dW, g, nps, mode);
+    return after_launch(ctx, "cb_conv_wgrad");
+}
+
+}  // extern "C"

@@ -75,6 +75,89 @@ int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const floa
  * "umma_3xtf32", "simt_fp32"); for tests and launch accounting. */
 const char* cb_last_kernel(const cb_ctx* ctx);
 
+/* ---- convolution (NCHW fp32) ------------------------------------------------------------------ */
+
+/*
+ * Geometry shared by the three passes: X is N x IC x IH x IW, W is OC x IC x FH x FW, Y is N x OC x OH x OW with
+ * OH = (IH - FH + 2 pH)/sH + 1 and OW likewise (the relation seblas::assertConv enforces,
+ * seblas/operations/cuConv.cu:731-755).
+ */
+
+/* Y = conv(W, X) (+ bias[oc]) (then ReLU if relu != 0). Replaces seblas::conv (seblas/operations/cuConv.cu:757). */
+int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
+                int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu);
+/* dX = data gradient of the same convolution. Replaces seblas::convDerive (seblas/operations/cuConv.cu:774). */
+int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
+                  int FH, int FW, int sH, int sW, int pH, int pW);
+/* dW (+)= weight gradient; the reference always accumulates (accumulate = 1). Uses the correct index map
+ * ih = oh*sH - pH + fh for every stride. Replaces seblas::convError (seblas/operations/cuConv.cu:793). */
+int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                  int FH, int FW, int sH, int sW, int pH, int pW, int accumulate);
+/* Y[n,c,:,:] += bias[c]. Replaces seblas::convBias (seblas/operations/cuConv.cu:808). */
+int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW);
+/* db[c] (+)= sum over (n,h,w) of dY: the bias gradient cuConv2D takes from cuDNN
+ * (seann/operands/cudnn/cuConv2D.cu:69). */
+int cb_conv_bias_grad(cb_ctx* ctx, const float* dY, float* db, int N, int C, int HW, int accumulate);
+
+/* ---- Linear (dense layer) ------------------------------------------------------------------------ */
+
+/* Y[n,m] = sum_k W[m,k] X[n,k] + b[m]; X: batch x IN, W: OUT x IN, b: OUT (nullable), Y: batch x OUT.
+ * Replaces seblas::linear (seblas/operations/cuLinear.cu:1052). */
+int cb_linear_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, float* Y, int batch, int IN, int OUT);
+/* dX[n,k] = sum_m W[m,k] dY[n,m]. Replaces seblas::linearXGrad (seblas/operations/cuLinear.cu:1075). */
+int cb_linear_xgrad(cb_ctx* ctx, const float* dY, const float* W, float* dX, int batch, int IN, int OUT);
+/* dW[m,k] += sum_n dY[n,m] X[n,k]; db[m] += sum_n dY[n,m] (db nullable; each term counted once).
+ * Replaces seblas::linearParamGrad (seblas/operations/cuLinear.cu:1098). */
+int cb_linear_paramgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, float* db, int batch, int IN,
+                        int OUT);
+
+/* ---- memory-bound neighbours ------------------------------------------------------------------- */
+
+/* BatchNorm with statistics per (c,h,w) position over the batch (P = C*H*W positions), eps = 1e-8, any batch
+ * size. mean, var and xhat may be NULL. Replaces seblas::batchNorm / batchNormGrad / batchNormParamGrads
+ * (seblas/operations/cuBatchNorm.cu:150,167,180). */
+int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
+              float* xhat, int N, long long P);
+int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, int N, long long P);
+int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgamma, float* dbeta, int N, long long P);
+
+/* seblas::relu / reluGradFast (seblas/operations/cuActivation.cu:268,296). */
+int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n);
+int cb_relu_grad(cb_ctx* ctx, const float* X, const float* dY, float* dX, long long n);
+
+/* In-place tensor arithmetic of seblas::Tensor (operator+ - * / with a tensor or a scalar, constFill;
+ * seblas/tensor/Tensor.cu:462-660): A = A op B or A = A op scalar. */
+enum {
+    CB_OP_ADD = 0, CB_OP_SUB = 1, CB_OP_MUL = 2, CB_OP_DIV = 3,
+    CB_OP_ADD_SCALAR = 4, CB_OP_SUB_SCALAR = 5, CB_OP_MUL_SCALAR = 6, CB_OP_DIV_SCALAR = 7, CB_OP_FILL = 8
+};
+int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, long long n);
+/* dA += dA_reserve; dA_reserve = 0 in one pass: the step every operand's xGrads begins with
+ * (e.g. seann/operands/seblas/Conv2D.cu:19-21). */
+int cb_grad_handover(cb_ctx* ctx, float* dA, float* dA_reserve, long long n);
+
+/* Non-overlapping average pooling over NC planes of H x W and its gradient (seblas::avgPool / avgPoolBack,
+ * seblas/operations/cuPool.cu:153-169); global average pooling and its gradient (cuPool.cu:171-184). */
+int cb_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H, int W, int rH, int rW);
+int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H, int W, int rH, int rW);
+int cb_global_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int HW);
+int cb_global_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int HW);
+
+/* Row softmax y = exp(x - max)/(sum + 1e-10) (seblas::softmax, seblas/operations/cuReduce.cu:296), and the
+ * softmax cross-entropy pair: dY = Y - labels (seblas::crossEntropyLoss, cuLoss.cu:231) with the summed loss
+ * -sum(log(Y + 1e-10) * labels) written to the device word *loss_sum (crossEntropyCalc, cuLoss.cu:220).
+ * dY and loss_sum may be NULL. */
+int cb_softmax(cb_ctx* ctx, const float* X, float* Y, int rows, int step);
+int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY, float* loss_sum, long long n);
+
+/* Momentum step of seann (seann/optimizers/Optimizers.cu:17-22 over seblas::momentumApply,
+ * seblas/operations/cuOptim.cu:38-46): w *= (1 - l2) if is_weight; m = beta m + (1 - beta) g; w -= lr m; g = 0.
+ * The multi form updates every tensor of a model in one launch. */
+int cb_momentum(cb_ctx* ctx, float* w, float* g, float* m, long long n, float lr, float beta, float l2,
+                int is_weight);
+int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
+                      const long long* sizes, const unsigned char* is_weight, float lr, float beta, float l2);
+
 #ifdef __cplusplus
 }
 #endif
