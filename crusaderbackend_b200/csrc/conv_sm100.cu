@@ -5,22 +5,24 @@
 // channels (UMMA N = OC rounded up to 16), K walks 8 input channels of one filter tap per tcgen05.mma.
 //
 //  * Pixels are grouped in "lines" of 32 consecutive floats of one channel plane (32/W image rows of a W-wide map,
-//    W in {8,16,32}); a CTA tile is 4 lines. For each filter row fh and line, one TMA box (W, 32/W rows, 8 channels)
-//    of the NCHW input lands as an [8 channels][128 bytes] block — exactly the MN-major operand layout the tensor
+//    W in {8,16,32}); a CTA tile is 4 lines. For each filter row fh and line, one TMA box (32 pixels of the
+//    flattened H*W plane, 8 channels) of the NCHW input lands as an [8 channels][128 bytes] block — exactly the MN-major operand layout the tensor
 //    core reads (128-byte swizzle with 32-byte atoms). Rows above / below the image are out of bounds for the
 //    tensor map and arrive as zeros, which is the vertical padding.
 //  * A TMA box may not start at an odd column (its innermost coordinate must be 16-byte aligned), so the
-//    horizontal taps cannot be fetched as shifted boxes. Four "shift" warps build the fw = 0 and fw = 2 copies of
-//    every block in shared memory from the centre copy (a register rotate by one float per 128-byte row, with
-//    zeros entering at the row edges = the horizontal padding) and hand them to the MMA warp through an mbarrier.
-//  * The filter is packed once per call into [tap][32-channel group][oc][32 channels] (K-major rows of 128 bytes,
+//    horizontal taps cannot be fetched as shifted boxes. They are not shifted on the input side at all: the three
+//    horizontal taps of a filter row are folded into the UMMA N dimension (N = 3 x OC, accumulator column
+//    fw*OCp + oc holds the partial sum of tap fw evaluated at the UNSHIFTED pixel), and the epilogue adds
+//    D0[x-1] + D1[x] + D2[x+1] with two warp shuffles per value; lanes at a row edge take zero instead, which is
+//    the horizontal padding. A pipeline stage is therefore only the centre copy of the input rows.
+//  * The filter is packed once per call into [fh][32-channel group][fw][oc][32 channels] (K-major rows of 128 bytes,
 //    zero padded) in the context workspace and stays resident in shared memory for the whole persistent CTA.
 //    For the data gradient the pack transposes the channel roles and rotates the filter by 180 degrees
 //    (seblas/operations/cuConv.cu:321-326 does the same rotation on the fly).
 //  * Epilogue: tcgen05.ld, + bias, ReLU, and stores in which the 32 lanes of a warp write 128 contiguous bytes.
 //
 // Covered geometry: stride 1, filter 1x1 (pad 0) or 3x3 (pad 1) per axis, W in {8,16,32}, (32/W) | H,
-// OC <= 256, packed filter <= ~150 KB. Everything else is served by the CUDA-core kernels in conv_simt.cu.
+// FW * OC(rounded to 16) <= 256, packed filter <= ~150 KB. Everything else is served by the CUDA-core kernels in conv_simt.cu.
 #include "cb_internal.h"
 #include "cb_ptx.cuh"
 
@@ -28,23 +30,27 @@ namespace cb {
 namespace {
 
 constexpr int kCB = 8;          // input channels per pipeline stage (= one UMMA K step per tap)
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 8;
 constexpr int kRowBytes = 128;  // one line of 32 floats
+constexpr uint32_t kBlockBytes = kCB * kRowBytes;  // one line of 8 channels
 
 struct ConvParams {
     int N, Cin, H, W, Cout;   // "input" and "output" of this pass (forward: X -> Y, dgrad: dY -> dX)
     int FH, FW, pH;           // vertical taps, horizontal taps, vertical padding
-    int OCp;                  // Cout rounded up to 16 (UMMA N)
+    int OCp;                  // Cout rounded up to 16
+    int NQ;                   // UMMA N = FW * OCp
     int CG;                   // 32-channel groups of the packed filter
     int NCB;                  // ceil(Cin / 8) pipeline stages per tile
     int L;                    // image rows per line (32 / W)
     int LPI;                  // lines per image (H / L)
+    int shared_rows;          // 1: the FH taps of a tile share FH + 3 row blocks (W == 32); 0: FH * 4 blocks
+    int nblocks;              // row blocks per stage
     long long total_lines;    // N * LPI
     int tiles;                // ceil(total_lines / 4)
     int stages;
     int tmem_cols;
     uint32_t w_bytes;         // resident packed filter
-    uint32_t stage_bytes;     // FW * FH * 4 lines * 8 channels * 128 B
+    uint32_t stage_bytes;     // nblocks * 1 KB
     float* Out;
     const float* bias;
     int relu;
@@ -54,7 +60,6 @@ struct ConvParams {
 struct __align__(8) ConvSmem {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t xf[kMaxStages];
     uint64_t tfull[2];
     uint64_t tempty[2];
     uint64_t wbar;
@@ -69,44 +74,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lan
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-// Physical byte address of the 16-byte chunk `q` (0..7) of the 128-byte row at `row_addr` under the 128-byte
-// swizzle with 32-byte atoms: the 32-byte chunk index is XORed with bits [7,9) of the address.
-__device__ __forceinline__ uint32_t sw32_chunk(uint32_t row_addr, int q) {
-    const uint32_t phase = (row_addr >> 7) & 3u;
-    return row_addr + ((((uint32_t)q >> 1) ^ phase) << 5) + (((uint32_t)q & 1u) << 4);
-}
-
-template <int W>
-__device__ __forceinline__ void shift_row(uint32_t src_row, uint32_t left_row, uint32_t right_row) {
-    float v[32];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v[4 * q]), "=f"(v[4 * q + 1]), "=f"(v[4 * q + 2]), "=f"(v[4 * q + 3])
-                     : "r"(sw32_chunk(src_row, q)));
-    }
-    // left tap (fw = 0): out[x] = in[x - 1], zero where the column would be -1
-    // right tap (fw = 2): out[x] = in[x + 1], zero where the column would be W
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        float l[4], r[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int x = 4 * q + e;
-            const int col = x % W;
-            l[e] = (col >= 1) ? v[(x + 31) & 31] : 0.f;
-            r[e] = (col < W - 1) ? v[(x + 1) & 31] : 0.f;
-        }
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw32_chunk(left_row, q)), "f"(l[0]), "f"(l[1]),
-                     "f"(l[2]), "f"(l[3])
-                     : "memory");
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw32_chunk(right_row, q)), "f"(r[0]), "f"(r[1]),
-                     "f"(r[2]), "f"(r[3])
-                     : "memory");
-    }
-}
-
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(192, 1)
     umma_conv_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                      const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -117,16 +85,12 @@ __global__ void __launch_bounds__(320, 1)
 
     const uint32_t w_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t st_base = w_base + p.w_bytes;
-    const uint32_t set_bytes = (uint32_t)p.FH * 4u * kCB * kRowBytes;  // one horizontal tap: FH x 4 lines x 8 rows
-    const int taps = p.FH * p.FW;
-    const int centre = p.FW >> 1;  // set index of the unshifted copy
 
     if (threadIdx.x == 0) {
         cs.abort_flag = 0;
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(smem_u32(&cs.full[s]), 1);
             mbar_init(smem_u32(&cs.empty[s]), 1);
-            mbar_init(smem_u32(&cs.xf[s]), 128);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&cs.tfull[a]), 1);
@@ -151,12 +115,12 @@ __global__ void __launch_bounds__(320, 1)
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            // resident filter: one box [OCp rows][32 channels] per (tap, channel group)
+            // resident filter: one box [FW*OCp rows][32 channels] per (filter row, channel group)
             const uint32_t wbar = smem_u32(&cs.wbar);
             mbar_expect_tx(wbar, p.w_bytes);
-            const int boxes = taps * p.CG;
+            const int boxes = p.FH * p.CG;
             for (int b = 0; b < boxes; ++b)
-                tma_load_3d(w_base + (uint32_t)b * p.OCp * kRowBytes, &tmW, wbar, 0, b * p.OCp, 0);
+                tma_load_3d(w_base + (uint32_t)b * p.NQ * kRowBytes, &tmW, wbar, 0, b * p.NQ, 0);
         }
         __syncwarp();
         uint32_t s = 0, ph = 0;
@@ -167,16 +131,25 @@ __global__ void __launch_bounds__(320, 1)
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t full = smem_u32(&cs.full[s]);
-                    const uint32_t dst0 = st_base + s * p.stage_bytes + (uint32_t)centre * set_bytes;
-                    mbar_expect_tx(full, set_bytes);
-                    for (int fh = 0; fh < p.FH; ++fh) {
-                        for (int j = 0; j < 4; ++j) {
-                            const long long g = 4LL * tile + j;
-                            // lines past the end use an image index >= N: the whole box is zero-filled
-                            const int n = (int)(g / p.LPI);
-                            const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
-                            tma_load_4d(dst0 + (uint32_t)((fh * 4 + j) * kCB) * kRowBytes, &tmIn, full, 0,
-                                        h0 + fh - p.pH, cb * kCB, n);
+                    const uint32_t dst0 = st_base + s * p.stage_bytes;
+                    mbar_expect_tx(full, p.stage_bytes);
+                    if (p.shared_rows) {
+                        // W == 32: the tile is 4 consecutive rows of one image; block r = input row h0 - pH + r
+                        const long long g = 4LL * tile;
+                        const int n = (int)(g / p.LPI);
+                        const int h0 = (int)(g - (long long)n * p.LPI);
+                        for (int r = 0; r < p.nblocks; ++r)
+                            tma_load_3d(dst0 + (uint32_t)r * kBlockBytes, &tmIn, full, (h0 - p.pH + r) * p.W, cb * kCB, n);
+                    } else {
+                        for (int fh = 0; fh < p.FH; ++fh) {
+                            for (int j = 0; j < 4; ++j) {
+                                const long long g = 4LL * tile + j;
+                                // lines past the end use an image index >= N: the whole box is zero-filled
+                                const int n = (int)(g / p.LPI);
+                                const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
+                                tma_load_3d(dst0 + (uint32_t)(fh * 4 + j) * kBlockBytes, &tmIn, full,
+                                            (h0 + fh - p.pH) * p.W, cb * kCB, n);
+                            }
                         }
                     }
                 }
@@ -186,7 +159,7 @@ __global__ void __launch_bounds__(320, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.OCp, 1u, 0u);
+        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 1u, 0u);
         uint32_t s = 0, ph = 0, lt = 0;
         bool ok = warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
         for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
@@ -199,26 +172,19 @@ __global__ void __launch_bounds__(320, 1)
             for (int cb = 0; cb < p.NCB; ++cb) {
                 ok = warp_wait(smem_u32(&cs.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
                 if (!ok) break;
-                if (p.FW > 1) {
-                    ok = warp_wait(smem_u32(&cs.xf[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM);
-                    if (!ok) break;
-                }
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t stg = st_base + s * p.stage_bytes;
-                    const uint32_t wq = w_base + (uint32_t)(cb >> 2) * p.OCp * kRowBytes + (uint32_t)(cb & 3) * 32u;
+                    const uint32_t wq = w_base + (uint32_t)(cb >> 2) * p.NQ * kRowBytes + (uint32_t)(cb & 3) * 32u;
                     for (int fh = 0; fh < p.FH; ++fh) {
-                        for (int fw = 0; fw < p.FW; ++fw) {
-                            const int t = fh * p.FW + fw;
-                            // P: 4 lines x [8 channels][128 B], MN-major, 1024 B between lines, 512 B per 4 rows
-                            const uint64_t dP = umma_smem_desc(stg + (uint32_t)fw * set_bytes +
-                                                                   (uint32_t)fh * 4u * kCB * kRowBytes,
-                                                               1024u, 512u, UMMA_SW_128B_BASE32B);
-                            // Q: packed filter rows [oc][32 channels], K-major, 8 channels of this stage
-                            const uint64_t dQ = umma_smem_desc(wq + (uint32_t)t * p.CG * p.OCp * kRowBytes, 16u, 1024u,
-                                                               UMMA_SW_128B);
-                            umma_tf32(d_tmem, dP, dQ, idesc, (cb == 0 && t == 0) ? 0u : 1u);
-                        }
+                        // P: 4 lines x [8 channels][128 B], MN-major: 1024 B between lines, 512 B per 4 channel rows
+                        const uint32_t first_block = p.shared_rows ? (uint32_t)fh : (uint32_t)fh * 4u;
+                        const uint64_t dP = umma_smem_desc(stg + first_block * kBlockBytes, 1024u, 512u,
+                                                           UMMA_SW_128B_BASE32B);
+                        // Q: packed filter rows [(fw, oc)][32 channels], K-major, the 8 channels of this stage
+                        const uint64_t dQ = umma_smem_desc(wq + (uint32_t)fh * p.CG * p.NQ * kRowBytes, 16u, 1024u,
+                                                           UMMA_SW_128B);
+                        umma_tf32(d_tmem, dP, dQ, idesc, (cb == 0 && fh == 0) ? 0u : 1u);
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
                     if (cb == p.NCB - 1) tc_commit(smem_u32(&cs.tfull[a]));
@@ -227,12 +193,14 @@ __global__ void __launch_bounds__(320, 1)
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
             }
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------ epilogue
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;
         uint32_t lt = 0;
         bool ok = true;
         const long long plane = (long long)p.H * p.W;
+        const int col = lane & (p.W - 1);
+        const bool has_left = col > 0, has_right = col < p.W - 1;
         for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
             const uint32_t a = lt & 1u;
             ok = mbar_wait(smem_u32(&cs.tfull[a]), (lt >> 1) & 1u, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
@@ -247,50 +215,42 @@ __global__ void __launch_bounds__(320, 1)
             float* out = p.Out + ((long long)n * p.Cout * p.H + h0) * p.W + lane;
             const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
             for (int c = 0; c < p.OCp; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(t_row + (uint32_t)c, r);
-                tmem_ld_wait();
+                uint32_t r1[16];
+                float v[16];
+                if (p.FW == 3) {
+                    uint32_t r0[16], r2[16];
+                    tmem_ld16(t_row + (uint32_t)c, r0);
+                    tmem_ld16(t_row + (uint32_t)(p.OCp + c), r1);
+                    tmem_ld16(t_row + (uint32_t)(2 * p.OCp + c), r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        // tap fw = 0 reads column ow - 1: its partial sum sits one lane to the left; fw = 2 one to the right
+                        const float l = __shfl_up_sync(0xffffffffu, __uint_as_float(r0[e]), 1);
+                        const float rr = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[e]), 1);
+                        v[e] = __uint_as_float(r1[e]) + (has_left ? l : 0.f) + (has_right ? rr : 0.f);
+                    }
+                } else {
+                    tmem_ld16(t_row + (uint32_t)c, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r1[e]);
+                }
                 if (valid) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         const int oc = c + e;
                         if (oc < p.Cout) {
-                            float v = __uint_as_float(r[e]);
-                            if (p.bias) v += __ldg(p.bias + oc);
-                            if (p.relu) v = fmaxf(v, 0.f);
-                            out[(long long)oc * plane] = v;
+                            float y = v[e];
+                            if (p.bias) y += __ldg(p.bias + oc);
+                            if (p.relu) y = fmaxf(y, 0.f);
+                            out[(long long)oc * plane] = y;
                         }
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(smem_u32(&cs.tempty[a]));
-        }
-    } else {
-        // ------------------------------------------------------------ shift warps (horizontal taps)
-        if (p.FW > 1) {
-            const int t = threadIdx.x - 192;  // 0..127
-            const int rows = p.FH * 4 * kCB;  // centre rows per stage (<= 96)
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
-                for (int cb = 0; cb < p.NCB; ++cb) {
-                    ok = mbar_wait(smem_u32(&cs.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
-                    if (!ok) break;
-                    if (t < rows) {
-                        const uint32_t stg = st_base + s * p.stage_bytes;
-                        const uint32_t src = stg + set_bytes + (uint32_t)t * kRowBytes;
-                        const uint32_t lft = stg + (uint32_t)t * kRowBytes;
-                        const uint32_t rgt = stg + 2u * set_bytes + (uint32_t)t * kRowBytes;
-                        if (p.W == 32) shift_row<32>(src, lft, rgt);
-                        else if (p.W == 16) shift_row<16>(src, lft, rgt);
-                        else shift_row<8>(src, lft, rgt);
-                    }
-                    fence_proxy_async_smem();
-                    mbar_arrive(smem_u32(&cs.xf[s]));
-                    if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
-                }
-            }
         }
     }
 
@@ -302,9 +262,9 @@ __global__ void __launch_bounds__(320, 1)
     }
 }
 
-// Packs the filter for the kernel above. Wp row index = (tap * CG + cg) * OCp + o, 32 floats per row.
-//   forward:  Wp[tap=(fh,fw)][cg][o][c] = W[o][cg*32 + c][fh][fw]                 (W is OC x IC x FH x FW)
-//   dgrad:    Wp[tap=(fh,fw)][cg][o][c] = W[cg*32 + c][o][FH-1-fh][FW-1-fw]       (o = input channel of the conv)
+// Packs the filter for the kernel above. Row index = ((fh * CG + cg) * FW + fw) * OCp + o, 32 floats per row.
+//   forward:  row[c] = W[o][cg*32 + c][fh][fw]                 (W is OC x IC x FH x FW)
+//   dgrad:    row[c] = W[cg*32 + c][o][FH-1-fh][FW-1-fw]       (o = input channel of the convolution)
 __global__ void pack_filter_kernel(const float* __restrict__ W, float* __restrict__ Wp, int OC, int IC, int FH, int FW,
                                    int OCp, int CG, int dgrad, long long total) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -313,9 +273,10 @@ __global__ void pack_filter_kernel(const float* __restrict__ W, float* __restric
         long long r = i >> 5;
         const int o = (int)(r % OCp);
         r /= OCp;
+        const int fw = (int)(r % FW);
+        r /= FW;
         const int cg = (int)(r % CG);
-        const int tap = (int)(r / CG);
-        const int fh = tap / FW, fw = tap - fh * FW;
+        const int fh = (int)(r / CG);
         const int ch = cg * 32 + c;
         float v = 0.f;
         if (!dgrad) {
@@ -342,12 +303,14 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     const int Cin = dgrad_of ? OC : IC;
     const int Cout = dgrad_of ? IC : OC;
     const int OCp = (Cout + 15) / 16 * 16;
-    if (OCp > 256 || Cin < 1) return CB_EUNSUPPORTED;
+    const int NQ = FW * OCp;
+    if (NQ > 256 || Cin < 1) return CB_EUNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) != 0) return CB_EUNSUPPORTED;
     const int CG = (Cin + 31) / 32;
-    const int taps = FH * FW;
-    const size_t w_bytes = (size_t)taps * CG * OCp * kRowBytes;
-    const uint32_t stage_bytes = (uint32_t)FW * FH * 4 * kCB * kRowBytes;
+    const size_t w_bytes = (size_t)FH * CG * NQ * kRowBytes;
+    const int shared_rows = (L == 1 && IH % 4 == 0) ? 1 : 0;
+    const int nblocks = shared_rows ? FH + 3 : FH * 4;
+    const uint32_t stage_bytes = (uint32_t)nblocks * kBlockBytes;
     const long long smem_cap = (long long)ctx->max_smem_optin - 2048;
     long long stages = (smem_cap - (long long)w_bytes) / stage_bytes;
     if (stages < 2) return CB_EUNSUPPORTED;
@@ -369,13 +332,14 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     ConvParams p{};
     p.N = N; p.Cin = Cin; p.H = IH; p.W = IW; p.Cout = Cout;
     p.FH = FH; p.FW = FW; p.pH = pH;
-    p.OCp = OCp; p.CG = CG; p.NCB = (Cin + kCB - 1) / kCB;
+    p.OCp = OCp; p.NQ = NQ; p.CG = CG; p.NCB = (Cin + kCB - 1) / kCB;
     p.L = L; p.LPI = IH / L;
+    p.shared_rows = shared_rows; p.nblocks = nblocks;
     p.total_lines = (long long)N * p.LPI;
     p.tiles = (int)((p.total_lines + 3) / 4);
     p.stages = (int)stages;
     int cols = 32;
-    while (cols < 2 * OCp) cols <<= 1;
+    while (cols < 2 * NQ) cols <<= 1;
     p.tmem_cols = cols;
     p.w_bytes = (uint32_t)w_bytes;
     p.stage_bytes = stage_bytes;
@@ -384,17 +348,22 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
 
     CUtensorMap tmIn, tmW;
     {
-        // input planes: (W, H, C, N); box = one line of 8 channels; rows and channels out of range read as zero
-        uint64_t dims[4] = {(uint64_t)IW, (uint64_t)IH, (uint64_t)Cin, (uint64_t)N};
-        uint64_t str[3] = {(uint64_t)IW * 4, (uint64_t)IH * IW * 4, (uint64_t)Cin * IH * IW * 4};
-        uint32_t box[4] = {(uint32_t)IW, (uint32_t)L, (uint32_t)kCB, 1u};
-        rc = encode_tmap(ctx, &tmIn, X, 4, dims, str, box, nullptr, 129);
+        // input planes flattened to (H*W, C, N): a box is 32 consecutive floats of 8 channel planes, starting at
+        // pixel (row * W) — a multiple of 4 floats, as TMA requires of the innermost coordinate. Pixels before the
+        // plane's first row or after its last one, and channels >= C, are out of bounds and read as zero. (A box
+        // whose inner extent is below the 128-byte swizzle span would be padded to 128 bytes per inner row in
+        // shared memory, so the (W, H) plane is never used as two tensor-map dimensions here.)
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)Cin * IH * IW * 4};
+        uint32_t box[3] = {32u, (uint32_t)kCB, 1u};
+        rc = encode_tmap(ctx, &tmIn, X, 3, dims, str, box, nullptr, 129);
         if (rc != CB_OK) return rc;
     }
     {
-        uint64_t dims[3] = {32, (uint64_t)taps * CG * OCp, 1};
-        uint64_t str[2] = {128, (uint64_t)taps * CG * OCp * 128};
-        uint32_t box[3] = {32, (uint32_t)OCp, 1};
+        const uint64_t rows = (uint64_t)FH * CG * NQ;
+        uint64_t dims[3] = {32, rows, 1};
+        uint64_t str[2] = {128, rows * 128};
+        uint32_t box[3] = {32, (uint32_t)NQ, 1};
         rc = encode_tmap(ctx, &tmW, Wp, 3, dims, str, box, nullptr, 128);
         if (rc != CB_OK) return rc;
     }
@@ -402,7 +371,7 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_conv_kernel attribute");
     const int grid = p.tiles < ctx->sm_count ? p.tiles : ctx->sm_count;
-    umma_conv_kernel<<<grid, 320, smem, ctx->stream>>>(tmIn, tmW, p);
+    umma_conv_kernel<<<grid, 192, smem, ctx->stream>>>(tmIn, tmW, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_conv_kernel launch");
     ctx->launches += 1;
@@ -410,9 +379,306 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     return CB_OK;
 }
 
-int umma_conv_wgrad(cb_ctx*, const float*, const float*, float*, int, int, int, int, int, int, int, int, int, int,
-                    int, int) {
-    return CB_EUNSUPPORTED;
+namespace {
+
+// ------------------------------------------------------------------------------------------ weight gradient
+// dW[oc][c][fh][fw] = sum over output pixels of dY[oc][pix] * X[c][pix shifted by (fh-pH, fw-pW)]: a contraction
+// over pixels, so both operands are K-major (32 pixels of one channel plane = one 128-byte row, standard 128-byte
+// swizzle). Per line of 32 output pixels a stage holds
+//   A: FH blocks [Cp channel rows][32 px] of X, fetched at the vertically shifted pixel offsets (UMMA M side,
+//      rows stacked as (fh, c); 128 rows per M tile), and
+//   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
+//      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
+//      edges), written by four shift warps — shifting dY by -d is the same sum as shifting X by +d.
+// Every CTA walks its share of the lines accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs),
+// writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
+struct WgradParams {
+    int N, Cin, H, W, OC;
+    int FH, FW, pH;
+    int Cp, OCp, NQ, mtiles, rowsA;  // rowsA = FH * Cp valid accumulator rows
+    int L, LPI;
+    long long total_lines;
+    int stages, tmem_cols;
+    uint32_t stage_bytes, a_bytes;
+    float* partial;                  // [gridDim.x][mtiles * 128][NQ]
+    int* status;
+};
+
+struct __align__(8) WgradSmem {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t xf[kMaxStages];
+    uint64_t tfull;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// 16-byte chunk q of the 128-byte row at row_addr under the standard 128-byte swizzle (chunk ^= row index mod 8)
+__device__ __forceinline__ uint32_t sw128_chunk(uint32_t row_addr, int q) {
+    return row_addr + ((((uint32_t)q) ^ ((row_addr >> 7) & 7u)) << 4);
+}
+
+template <int W>
+__device__ __forceinline__ void shift_dy_row(uint32_t src_row, uint32_t set0_row, uint32_t set2_row) {
+    float v[32];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v[4 * q]), "=f"(v[4 * q + 1]), "=f"(v[4 * q + 2]), "=f"(v[4 * q + 3])
+                     : "r"(sw128_chunk(src_row, q)));
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        float a[4], b[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int x = 4 * q + e;
+            const int col = x % W;
+            a[e] = (col < W - 1) ? v[(x + 1) & 31] : 0.f;  // fw = 0: pairs X[px] with dY[px + 1]
+            b[e] = (col >= 1) ? v[(x + 31) & 31] : 0.f;    // fw = 2: pairs X[px] with dY[px - 1]
+        }
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(set0_row, q)), "f"(a[0]), "f"(a[1]),
+                     "f"(a[2]), "f"(a[3])
+                     : "memory");
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(set2_row, q)), "f"(b[0]), "f"(b[1]),
+                     "f"(b[2]), "f"(b[3])
+                     : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(320, 1)
+    umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmdY,
+                      const WgradParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ WgradSmem ws;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &ws.abort_flag;
+    const uint32_t st_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t set_bytes = (uint32_t)p.OCp * kRowBytes;
+    const int centre = p.FW >> 1;
+
+    if (threadIdx.x == 0) {
+        ws.abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&ws.full[s]), 1);
+            mbar_init(smem_u32(&ws.empty[s]), 1);
+            mbar_init(smem_u32(&ws.xf[s]), 128);
+        }
+        mbar_init(smem_u32(&ws.tfull), 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmX);
+        tma_prefetch_desc(&tmdY);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&ws.tmem_base), (uint32_t)p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ws.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+            ok = warp_wait(smem_u32(&ws.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
+            if (!ok) break;
+            if (lane == 0) {
+                const uint32_t full = smem_u32(&ws.full[s]);
+                const uint32_t stg = st_base + s * p.stage_bytes;
+                const int n = (int)(g / p.LPI);
+                const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
+                mbar_expect_tx(full, p.a_bytes + set_bytes);
+                for (int fh = 0; fh < p.FH; ++fh)
+                    tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
+                tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
+            }
+            __syncwarp();
+            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 0u, 0u);
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        bool first_line = true;
+        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+            ok = warp_wait(smem_u32(&ws.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
+            if (!ok) break;
+            if (p.FW > 1) {
+                ok = warp_wait(smem_u32(&ws.xf[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM);
+                if (!ok) break;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t stg = st_base + s * p.stage_bytes;
+                for (int m = 0; m < p.mtiles; ++m) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t dA = umma_smem_desc(stg + (uint32_t)m * 16384u + kk * 32u, 16u, 1024u, UMMA_SW_128B);
+                        const uint64_t dB = umma_smem_desc(stg + p.a_bytes + kk * 32u, 16u, 1024u, UMMA_SW_128B);
+                        umma_tf32(tmem_base + (uint32_t)m * p.NQ, dA, dB, idesc, (first_line && kk == 0) ? 0u : 1u);
+                    }
+                }
+                tc_commit(smem_u32(&ws.empty[s]));
+                if (g + gridDim.x >= p.total_lines) tc_commit(smem_u32(&ws.tfull));
+            }
+            __syncwarp();
+            first_line = false;
+            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue: partial sums to the workspace
+        const int quarter = warp & 3;
+        bool ok = mbar_wait(smem_u32(&ws.tfull), 0, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const int rows_tot = p.mtiles * 128;
+            for (int m = 0; m < p.mtiles; ++m) {
+                const int r = m * 128 + 32 * quarter + lane;
+                float* dst = p.partial + ((long long)blockIdx.x * rows_tot + r) * p.NQ;
+                const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
+                for (int c = 0; c < p.NQ; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_row + (uint32_t)c, v);
+                    tmem_ld_wait();
+                    if (r < p.rowsA) {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 4)
+                            *reinterpret_cast<float4*>(dst + c + e) =
+                                make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                            __uint_as_float(v[e + 3]));
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ shift warps: fw = 0 and fw = 2 copies of dY
+        if (p.FW > 1) {
+            const int t = threadIdx.x - 192;
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+                ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
+                if (!ok) break;
+                if (t < p.OCp) {
+                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)t * kRowBytes;
+                    if (p.W == 32) shift_dy_row<32>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
+                    else if (p.W == 16) shift_dy_row<16>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
+                    else shift_dy_row<8>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ws.xf[s]));
+                if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
+__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW, int nparts, int rows_tot,
+                                    int rowsA, int NQ, int Cp, int Cin, int OC, int OCp, int FH, int FW, int accumulate) {
+    const long long total = (long long)rowsA * NQ;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int col = (int)(i % NQ);
+        const int r = (int)(i / NQ);
+        const int fh = r / Cp, c = r - fh * Cp;
+        const int fw = col / OCp, oc = col - fw * OCp;
+        if (c >= Cin || oc >= OC) continue;
+        float s = 0.f;
+        const float* src = partial + (long long)r * NQ + col;
+        for (int q = 0; q < nparts; ++q) s += src[(long long)q * rows_tot * NQ];
+        float* dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+        *dst = accumulate ? *dst + s : s;
+    }
+}
+
+}  // namespace
+
+int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
+    if (sH != 1 || sW != 1) return CB_EUNSUPPORTED;
+    if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
+    if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+    if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
+    const int L = 32 / IW;
+    if (IH % L) return CB_EUNSUPPORTED;
+    const int Cp = (IC + 7) / 8 * 8;
+    const int OCp = (OC + 15) / 16 * 16;
+    const int NQ = FW * OCp;
+    const int rowsA = FH * Cp;
+    const int mtiles = (rowsA + 127) / 128;
+    if (NQ > 256 || Cp > 256 || OCp > 128 || mtiles * NQ > 512) return CB_EUNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(dY) & 15u)) return CB_EUNSUPPORTED;
+    int rows_stage = rowsA + NQ;
+    if (rows_stage < mtiles * 128) rows_stage = mtiles * 128;
+    const uint32_t stage_bytes = ((uint32_t)rows_stage * kRowBytes + 1023u) & ~1023u;
+    long long stages = ((long long)ctx->max_smem_optin - 2048) / stage_bytes;
+    if (stages < 2) return CB_EUNSUPPORTED;
+    if (stages > kMaxStages) stages = kMaxStages;
+
+    WgradParams p{};
+    p.N = N; p.Cin = IC; p.H = IH; p.W = IW; p.OC = OC;
+    p.FH = FH; p.FW = FW; p.pH = pH;
+    p.Cp = Cp; p.OCp = OCp; p.NQ = NQ; p.mtiles = mtiles; p.rowsA = rowsA;
+    p.L = L; p.LPI = IH / L;
+    p.total_lines = (long long)N * p.LPI;
+    p.stages = (int)stages;
+    int cols = 32;
+    while (cols < mtiles * NQ) cols <<= 1;
+    p.tmem_cols = cols;
+    p.stage_bytes = stage_bytes;
+    p.a_bytes = (uint32_t)rowsA * kRowBytes;
+    p.status = ctx->d_status;
+    const int grid = (int)(p.total_lines < ctx->sm_count ? p.total_lines : ctx->sm_count);
+    const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
+    int rc = ensure_workspace(ctx, part_bytes);
+    if (rc != CB_OK) return rc;
+    p.partial = static_cast<float*>(ctx->workspace);
+
+    CUtensorMap tmX, tmdY;
+    {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)IC, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)IC * IH * IW * 4};
+        uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
+        rc = encode_tmap(ctx, &tmX, X, 3, dims, str, box, nullptr, 128);
+        if (rc != CB_OK) return rc;
+    }
+    {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)OC * IH * IW * 4};
+        uint32_t box[3] = {32u, (uint32_t)OCp, 1u};
+        rc = encode_tmap(ctx, &tmdY, dY, 3, dims, str, box, nullptr, 128);
+        if (rc != CB_OK) return rc;
+    }
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
+    umma_wgrad_kernel<<<grid, 320, smem, ctx->stream>>>(tmX, tmdY, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
+    const long long total = (long long)rowsA * NQ;
+    int rgrid = (int)((total + 255) / 256);
+    wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, IC, OC, OCp, FH,
+                                                         FW, accumulate ? 1 : 0);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
+    ctx->launches += 2;
+    ctx->last_kernel = "umma_tf32";
+    return CB_OK;
 }
 
 }  // namespace cb
