@@ -57,6 +57,7 @@ SIGNATURES = {
     "cb_softmax": (_i, [_ctx, _f, _f, _i, _i]),
     "cb_cross_entropy": (_i, [_ctx, _f, _f, _f, _f, _ll]),
     "cb_momentum": (_i, [_ctx, _f, _f, _f, _ll, _fl, _fl, _fl, _i]),
+    "cb_conv_fwd_noalloc": (_i, [_i, C.c_void_p, _f, _f, _f, _f] + [_i] * 12 + [C.c_char_p, _i]),
     "cb_momentum_multi": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                C.POINTER(_ll), C.POINTER(C.c_ubyte), _fl, _fl, _fl]),
 }

@@ -23,6 +23,8 @@
 //
 // Covered geometry: stride 1, filter 1x1 (pad 0) or 3x3 (pad 1) per axis, W in {8,16,32}, (32/W) | H,
 // FW * OC(rounded to 16) <= 256, packed filter <= ~150 KB. Everything else is served by the CUDA-core kernels in conv_simt.cu.
+#include <cstdio>
+
 #include "cb_internal.h"
 #include "cb_ptx.cuh"
 
@@ -681,4 +683,141 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
     return CB_OK;
 }
 
+// ------------------------------------------------------------------------------------------ allocation-free forward
+// cb_conv_fwd_noalloc: the tensor-core forward convolution for callers that must not allocate device memory —
+// code running under a memory manager that has already claimed the whole GPU (so cudaMalloc would fail), code
+// on a latency-critical path where cudaMalloc's implicit device synchronisation is unacceptable, and code that
+// runs while a stream is being captured (allocation calls are not allowed there). The ordinary entry point keeps
+// its packed filter in a context workspace that grows with cudaMalloc; this one keeps it in the fixed array below,
+// which every GPU that loads the library holds from load to exit (160 KiB + one status word).
+namespace {
+
+constexpr int kNoAllocPackFloats = 40960;  // 160 KiB: enough for a 64 -> 64 channel 3x3 filter (147 456 bytes)
+static __device__ __align__(256) float g_noalloc_pack[kNoAllocPackFloats];
+static __device__ __align__(16) int g_noalloc_status;
+
+struct NoAllocDevice {
+    bool ready = false;
+    float* pack = nullptr;  // device address of g_noalloc_pack on this GPU (the symbol itself is a host stand-in)
+    int* status = nullptr;
+    int sm_count = 0;
+    int smem_optin = 0;
+};
+constexpr int kNoAllocMaxDevices = 64;
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+
+int noalloc_fail(char* err, int err_len, int code, const char* msg) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", msg);
+    return code;
+}
+
+}  // namespace
 }  // namespace cb
+
+extern "C" int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W, const float* X, float* Y,
+                                   const float* bias, int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH,
+                                   int sW, int pH, int pW, int relu, char* err, int err_len) {
+    using namespace cb;
+    if (err && err_len > 0) err[0] = 0;
+    if (device < 0 || device >= kNoAllocMaxDevices) return noalloc_fail(err, err_len, CB_EINVAL, "device index out of range");
+    if (N < 0 || IC < 1 || OC < 1 || IH < 1 || IW < 1) return noalloc_fail(err, err_len, CB_EINVAL, "bad extent");
+    if (!W || !X || !Y) return noalloc_fail(err, err_len, CB_EINVAL, "null operand");
+    if (sH != 1 || sW != 1 || !((FH == 1 && pH == 0) || (FH == 3 && pH == 1)) ||
+        !((FW == 1 && pW == 0) || (FW == 3 && pW == 1)) || (IW != 8 && IW != 16 && IW != 32) || (IH % (32 / IW)) ||
+        (reinterpret_cast<uintptr_t>(X) & 15u))
+        return noalloc_fail(err, err_len, CB_EUNSUPPORTED,
+                            "cb_conv_fwd_noalloc covers stride 1, 1x1 (pad 0) / 3x3 (pad 1) filters, map width 8, 16 or 32 "
+                            "and a 16-byte aligned input");
+    const int L = 32 / IW;
+    const int OCp = (OC + 15) / 16 * 16;
+    const int NQ = FW * OCp;
+    const int CG = (IC + 31) / 32;
+    if (NQ > 256) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "FW * OC (rounded up to 16) exceeds 256");
+    const size_t w_bytes = (size_t)FH * CG * NQ * kRowBytes;
+    if (w_bytes > sizeof(float) * (size_t)kNoAllocPackFloats) {
+        char msg[200];
+        snprintf(msg, sizeof(msg), "packed filter needs %zu bytes; the static scratch of cb_conv_fwd_noalloc holds %zu",
+                 w_bytes, sizeof(float) * (size_t)kNoAllocPackFloats);
+        return noalloc_fail(err, err_len, CB_EINVAL, msg);
+    }
+    if (N == 0) return CB_OK;
+
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    NoAllocDevice& d = g_noalloc_dev[device];
+    if (!d.ready) {
+        // once per device, with that device current: resolve the device addresses of the static arrays
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.pack), g_noalloc_pack);
+        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_noalloc_status);
+        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+        int major = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (major != 10) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "this library only carries sm_100a code");
+        cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
+        cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+        d.ready = true;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    const int shared_rows = (L == 1 && IH % 4 == 0) ? 1 : 0;
+    const int nblocks = shared_rows ? FH + 3 : FH * 4;
+    const uint32_t stage_bytes = (uint32_t)nblocks * kBlockBytes;
+    long long stages = ((long long)d.smem_optin - 2048 - (long long)w_bytes) / stage_bytes;
+    if (stages < 2) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "not enough shared memory for the pipeline");
+    if (stages > kMaxStages) stages = kMaxStages;
+
+    // the scratch keeps the previous call's contents: the pack kernel rewrites all w_bytes (padding included) and
+    // the status word is cleared, both in stream order
+    e = cudaMemsetAsync(d.status, 0, sizeof(int), stream);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    {
+        const long long total = (long long)w_bytes / 4;
+        int grid = (int)((total + 255) / 256);
+        if (grid > d.sm_count * 8) grid = d.sm_count * 8;
+        pack_filter_kernel<<<grid, 256, 0, stream>>>(W, d.pack, OC, IC, FH, FW, OCp, CG, 0, total);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    }
+    ConvParams p{};
+    p.N = N; p.Cin = IC; p.H = IH; p.W = IW; p.Cout = OC;
+    p.FH = FH; p.FW = FW; p.pH = pH;
+    p.OCp = OCp; p.NQ = NQ; p.CG = CG; p.NCB = (IC + kCB - 1) / kCB;
+    p.L = L; p.LPI = IH / L;
+    p.shared_rows = shared_rows; p.nblocks = nblocks;
+    p.total_lines = (long long)N * p.LPI;
+    p.tiles = (int)((p.total_lines + 3) / 4);
+    p.stages = (int)stages;
+    int cols = 32;
+    while (cols < 2 * NQ) cols <<= 1;
+    p.tmem_cols = cols;
+    p.w_bytes = (uint32_t)w_bytes;
+    p.stage_bytes = stage_bytes;
+    p.Out = Y; p.bias = bias; p.relu = relu;
+    p.status = d.status;
+
+    CUtensorMap tmIn, tmW;
+    {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)IC, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)IC * IH * IW * 4};
+        uint32_t box[3] = {32u, (uint32_t)kCB, 1u};
+        if (encode_tmap(nullptr, &tmIn, X, 3, dims, str, box, nullptr, 129) != CB_OK)
+            return noalloc_fail(err, err_len, CB_ECUDA, "tensor map encoding failed (input)");
+    }
+    {
+        const uint64_t rows = (uint64_t)FH * CG * NQ;
+        uint64_t dims[3] = {32, rows, 1};
+        uint64_t str[2] = {128, rows * 128};
+        uint32_t box[3] = {32, (uint32_t)NQ, 1};
+        if (encode_tmap(nullptr, &tmW, d.pack, 3, dims, str, box, nullptr, 128) != CB_OK)
+            return noalloc_fail(err, err_len, CB_ECUDA, "tensor map encoding failed (filter)");
+    }
+    const size_t smem = w_bytes + (size_t)p.stages * stage_bytes + 1024;
+    e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    const int grid = p.tiles < d.sm_count ? p.tiles : d.sm_count;
+    umma_conv_kernel<<<grid, 192, smem, stream>>>(tmIn, tmW, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    return CB_OK;
+}

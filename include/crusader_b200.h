@@ -158,6 +158,35 @@ int cb_momentum(cb_ctx* ctx, float* w, float* g, float* m, long long n, float lr
 int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
                       const long long* sizes, const unsigned char* is_weight, float lr, float beta, float l2);
 
+/* ---- allocation-free variant ---------------------------------------------------------------------- */
+
+/*
+ * Forward convolution for callers that must not allocate device memory: code that runs under a memory manager
+ * which has already claimed the whole GPU (cudaMalloc would fail), code on a latency-critical path that cannot
+ * afford cudaMalloc's implicit device synchronisation, and code that runs while a stream is being captured
+ * (allocation calls are not permitted there). It needs no cb_ctx and calls no cudaMalloc / cudaFree or any
+ * allocating library routine: the packed filter the tensor-core kernel reads lives in a fixed 160 KiB array (plus
+ * one status word) that every GPU holding this library keeps from load until exit.
+ * This entry point has no counterpart in the reference.
+ *
+ *  - Same arithmetic as cb_conv_fwd in CB_MATH_TF32 mode; Y (+ bias, then ReLU if relu != 0) is written
+ *    asynchronously on `cuda_stream` of `device`.
+ *  - Geometry: stride 1; 1x1 filters with padding 0 or 3x3 with padding 1 (per axis); map width 8, 16 or 32 with
+ *    (32 / width) dividing the height; FW * OC (OC rounded up to 16) <= 256; X 16-byte aligned. The packed filter,
+ *    FH * ceil(IC / 32) * FW * roundup16(OC) * 128 bytes, must fit in 163 840 bytes (a 64 -> 64 channel 3x3 filter
+ *    needs 147 456); larger requests are rejected with CB_EINVAL and a message, other geometries with
+ *    CB_EUNSUPPORTED.
+ *  - The first call on a device resolves the device address of the static array (cudaGetSymbolAddress) and reads
+ *    the device attributes; make that first call before any stream capture begins.
+ *  - Every call on a device shares the one array (it keeps the previous call's contents; each call rewrites the
+ *    part it uses and clears the status word in stream order). Calls that overlap on the GPU — different streams,
+ *    or different host threads — race on it: issue them on one stream.
+ *  - `err` (nullable) receives a message of at most err_len bytes when the return value is not CB_OK.
+ */
+int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W, const float* X, float* Y, const float* bias,
+                        int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW,
+                        int relu, char* err, int err_len);
+
 #ifdef __cplusplus
 }
 #endif
