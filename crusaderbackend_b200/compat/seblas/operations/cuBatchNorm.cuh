@@ -1,0 +1,3 @@
+// Same path as the reference header of this name; everything lives in ../seblas.cuh.
+#pragma once
+#include "../seblas.cuh"

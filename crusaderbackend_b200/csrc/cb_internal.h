@@ -64,4 +64,10 @@ bool umma_gemm_eligible(const GemmCall& g);
 int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3);
 int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g);
 
+// Momentum descriptor table resident on the device (see neighbours.cu).
+int momentum_table_build(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
+                         const long long* sizes, const unsigned char* is_weight, void** dev_table, long long* biggest);
+int momentum_table_launch(cb_ctx* ctx, const void* dev_table, int ntensors, long long biggest, float lr, float beta,
+                          float l2);
+
 }  // namespace cb

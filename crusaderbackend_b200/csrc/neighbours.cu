@@ -2,6 +2,8 @@
 // pooling, softmax + cross-entropy, bias add / bias gradient, Momentum-SGD and the in-place tensor arithmetic of
 // seblas::Tensor. All kernels stream HBM with 128-bit accesses where alignment allows, use grid-stride loops
 // sized to the SM count, and reduce with warp shuffles.
+#include <vector>
+
 #include "cb_internal.h"
 
 namespace cb {
@@ -603,6 +605,40 @@ int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* 
         static_cast<const MomentumTensor*>(ctx->workspace), lr, beta, l2);
     return done(ctx, "cb_momentum_multi");
 }
+
+}  // extern "C"
+
+namespace cb {
+// Descriptor table kept on the device by long-lived callers (the training-step executor), so that the update is a
+// single kernel launch with no host copy or synchronisation in the step.
+int momentum_table_build(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
+                         const long long* sizes, const unsigned char* is_weight, void** dev_table, long long* biggest) {
+    std::vector<MomentumTensor> host((size_t)ntensors);
+    *biggest = 1;
+    for (int i = 0; i < ntensors; ++i) {
+        host[i] = MomentumTensor{w[i], g[i], m[i], sizes[i], is_weight ? (int)is_weight[i] : 0};
+        if (sizes[i] > *biggest) *biggest = sizes[i];
+    }
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, sizeof(MomentumTensor) * (size_t)(ntensors > 0 ? ntensors : 1));
+    if (e == cudaSuccess) e = cudaMemcpy(d, host.data(), sizeof(MomentumTensor) * (size_t)ntensors, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "momentum table upload");
+    *dev_table = d;
+    return CB_OK;
+}
+int momentum_table_launch(cb_ctx* ctx, const void* dev_table, int ntensors, long long biggest, float lr, float beta,
+                          float l2) {
+    if (ntensors <= 0) return CB_OK;
+    int gx = (int)((biggest / 4 + kThreads - 1) / kThreads);
+    if (gx < 1) gx = 1;
+    if (gx > 64) gx = 64;
+    momentum_multi_kernel<<<dim3(gx, ntensors), kThreads, 0, ctx->stream>>>(static_cast<const MomentumTensor*>(dev_table), lr,
+                                                                           beta, l2);
+    return done(ctx, "momentum step");
+}
+}  // namespace cb
+
+extern "C" {
 
 int cb_momentum(cb_ctx* ctx, float* w, float* g, float* m, long long n, float lr, float beta, float l2,
                 int is_weight) {

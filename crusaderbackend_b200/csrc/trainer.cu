@@ -1,0 +1,414 @@
+// A compact training-step executor for the models of the specification (ResNet-56 and its shallower
+// siblings), written on top of the C ABI of this library. It replaces the inner loop of the reference's
+// Sequential::train (seann/containers/Sequential.cu:43-104: forward, backward, learn) for these models, with the
+// reference's training semantics:
+//   * gradients are summed over the batch (no 1/N), the loss gradient is softmax - onehot
+//     (seblas/operations/cuLoss.cu:231-234) and the reported loss is sum(-log(y + 1e-10) * label) / batch
+//     (cuLoss.cu:220-229 with seann/containers/Sequential.cu:125-130);
+//   * BatchNorm normalises every (c,h,w) position over the batch (seblas/operations/cuBatchNorm.cu:14-61);
+//   * a residual block is  x -> conv-BN-ReLU-conv-BN -> (+ shortcut) -> ReLU, the shortcut being the identity or a
+//     bare 1x1 stride-2 convolution (archive/Resnet56:8-15, :96);
+//   * Momentum: w *= (1 - l2) on weights, m = beta m + (1 - beta) g, w -= lr m, g = 0
+//     (seann/optimizers/Optimizers.cu:17-22, seblas/operations/cuOptim.cu:38-46).
+// Parameters, gradients and momentum live in three flat caller-owned device buffers (same layout), so a
+// data-parallel caller sum-allreduces ONE gradient buffer between cbt_backward and cbt_update.
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "cb_internal.h"
+
+namespace {
+
+enum OpKind { OP_CONV, OP_BN, OP_RELU, OP_ADD, OP_GAP, OP_LINEAR, OP_SOFTMAX_CE };
+
+struct TensorBuf {
+    int n = 0, c = 0, h = 0, w = 0;
+    float* a = nullptr;   // value
+    float* d = nullptr;   // gradient (allocated lazily for tensors that need one)
+    long long size() const { return (long long)n * c * h * w; }
+};
+
+struct Op {
+    OpKind kind;
+    int in0 = -1, in1 = -1, out = -1;  // tensor ids
+    // conv
+    int oc = 0, f = 0, stride = 1, pad = 0;
+    long long w_off = -1, b_off = -1;   // offsets into the flat parameter buffer (conv filter / BN gamma / FC weight; BN beta / FC bias)
+    int xhat = -1;                      // BN: tensor id of x-hat
+    bool in0_grad_accumulate = false;   // backward adds into in0's gradient instead of overwriting it
+};
+
+struct ParamEntry {
+    long long offset, size;
+    int is_weight;   // decayed by l2 (conv filters, FC weights): Optimizers.cuh:27 isWeight
+    int kind;        // 0 conv filter, 1 BN gamma, 2 BN beta, 3 FC weight, 4 FC bias
+    int d0, d1, d2, d3;
+};
+
+}  // namespace
+
+struct cbt_model {
+    cb_ctx* ctx = nullptr;
+    int batch = 0, classes = 0;
+    std::vector<TensorBuf> t;
+    std::vector<Op> ops;
+    std::vector<ParamEntry> params;
+    long long param_count = 0;
+    float* P = nullptr;   // caller-owned flat buffers
+    float* G = nullptr;
+    float* M = nullptr;
+    float* scratch = nullptr;      // one activation-sized temporary for accumulating data gradients
+    long long scratch_elems = 0;
+    float* labels = nullptr;       // device copy of the one-hot labels of the current step (caller-owned pointer)
+    float* loss_dev = nullptr;     // device word: summed loss of the current step
+    int input = -1, logits = -1, probs = -1;
+    std::vector<void*> owned;      // device allocations released by cbt_destroy
+    std::string err;
+    void* mom_table = nullptr;     // device descriptor table of the Momentum step, built by cbt_bind
+    long long mom_biggest = 1;
+};
+
+namespace {
+
+int new_tensor(cbt_model* m, int n, int c, int h, int w) {
+    TensorBuf b;
+    b.n = n; b.c = c; b.h = h; b.w = w;
+    m->t.push_back(b);
+    return (int)m->t.size() - 1;
+}
+
+long long add_param(cbt_model* m, long long size, int is_weight, int kind, int d0, int d1, int d2, int d3) {
+    // keep every tensor 16-byte aligned inside the flat buffers (128-bit kernels, TMA bases)
+    m->param_count = (m->param_count + 3) & ~3LL;
+    ParamEntry e{m->param_count, size, is_weight, kind, d0, d1, d2, d3};
+    m->params.push_back(e);
+    m->param_count += size;
+    return e.offset;
+}
+
+int add_conv(cbt_model* m, int in, int oc, int f, int stride, int pad) {
+    const TensorBuf& x = m->t[in];
+    const int oh = (x.h - f + 2 * pad) / stride + 1, ow = (x.w - f + 2 * pad) / stride + 1;
+    Op o{};
+    o.kind = OP_CONV; o.in0 = in; o.oc = oc; o.f = f; o.stride = stride; o.pad = pad;
+    o.w_off = add_param(m, (long long)oc * x.c * f * f, 1, 0, oc, x.c, f, f);
+    o.out = new_tensor(m, x.n, oc, oh, ow);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_bn(cbt_model* m, int in) {
+    const TensorBuf x = m->t[in];
+    Op o{};
+    o.kind = OP_BN; o.in0 = in;
+    const long long p = (long long)x.c * x.h * x.w;
+    o.w_off = add_param(m, p, 0, 1, 1, x.c, x.h, x.w);   // gamma, shape (1,C,H,W): BatchNorm.cuh:27-33
+    o.b_off = add_param(m, p, 0, 2, 1, x.c, x.h, x.w);   // beta
+    o.xhat = new_tensor(m, x.n, x.c, x.h, x.w);
+    o.out = new_tensor(m, x.n, x.c, x.h, x.w);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_relu(cbt_model* m, int in) {
+    const TensorBuf x = m->t[in];
+    Op o{};
+    o.kind = OP_RELU; o.in0 = in;
+    o.out = new_tensor(m, x.n, x.c, x.h, x.w);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_add(cbt_model* m, int a, int b) {
+    const TensorBuf x = m->t[a];
+    Op o{};
+    o.kind = OP_ADD; o.in0 = a; o.in1 = b;
+    o.out = new_tensor(m, x.n, x.c, x.h, x.w);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_gap(cbt_model* m, int in) {
+    const TensorBuf x = m->t[in];
+    Op o{};
+    o.kind = OP_GAP; o.in0 = in;
+    o.out = new_tensor(m, x.n, x.c, 1, 1);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_linear(cbt_model* m, int in, int out_features) {
+    const TensorBuf x = m->t[in];
+    const int in_features = x.c * x.h * x.w;
+    Op o{};
+    o.kind = OP_LINEAR; o.in0 = in; o.oc = out_features;
+    o.w_off = add_param(m, (long long)out_features * in_features, 1, 3, out_features, in_features, 1, 1);
+    o.b_off = add_param(m, out_features, 0, 4, out_features, 1, 1, 1);
+    o.out = new_tensor(m, x.n, out_features, 1, 1);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int dev_alloc(cbt_model* m, float** p, long long elems) {
+    void* q = nullptr;
+    if (cudaMalloc(&q, (size_t)(elems > 0 ? elems : 1) * sizeof(float)) != cudaSuccess) {
+        m->err = "cudaMalloc failed for an activation buffer";
+        return CB_ENOMEM;
+    }
+    cudaMemset(q, 0, (size_t)(elems > 0 ? elems : 1) * sizeof(float));
+    m->owned.push_back(q);
+    *p = static_cast<float*>(q);
+    return CB_OK;
+}
+
+#define CBT_TRY(expr)                                              \
+    do {                                                           \
+        int rc__ = (expr);                                         \
+        if (rc__ != CB_OK) {                                       \
+            m->err = cb_last_error(m->ctx);                        \
+            return rc__;                                           \
+        }                                                          \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+// ResNet of 6*blocks_per_stage + 2 layers on image_hw x image_hw RGB inputs (blocks_per_stage = 9: ResNet-56),
+// channel plan 16/32/64, global average pooling and a `classes`-way dense head.
+int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_stage, int image_hw, int classes) {
+    if (!out || !ctx || batch < 1 || blocks_per_stage < 1 || image_hw < 4 || classes < 1) return CB_EINVAL;
+    cbt_model* m = new cbt_model();
+    m->ctx = ctx; m->batch = batch; m->classes = classes;
+    int x = new_tensor(m, batch, 3, image_hw, image_hw);
+    m->input = x;
+    x = add_relu(m, add_bn(m, add_conv(m, x, 16, 3, 1, 1)));
+    int ch = 16;
+    for (int stage = 0; stage < 3; ++stage) {
+        const int oc = 16 << stage;
+        for (int b = 0; b < blocks_per_stage; ++b) {
+            const int stride = (stage > 0 && b == 0) ? 2 : 1;
+            int y = add_relu(m, add_bn(m, add_conv(m, x, oc, 3, stride, 1)));
+            y = add_bn(m, add_conv(m, y, oc, 3, 1, 1));
+            int sc = x;
+            if (stride != 1 || ch != oc) sc = add_conv(m, x, oc, 1, stride, 0);  // bare 1x1 projection
+            x = add_relu(m, add_add(m, y, sc));
+            ch = oc;
+        }
+    }
+    x = add_gap(m, x);
+    m->logits = add_linear(m, x, classes);
+    {
+        Op o{};
+        o.kind = OP_SOFTMAX_CE; o.in0 = m->logits;
+        o.out = new_tensor(m, batch, classes, 1, 1);
+        m->probs = o.out;
+        m->ops.push_back(o);
+    }
+    m->param_count = (m->param_count + 3) & ~3LL;
+    // activations, gradients, and the accumulate flags of tensors with two consumers
+    std::vector<int> consumers(m->t.size(), 0);
+    for (Op& o : m->ops) {
+        if (o.in0 >= 0) consumers[o.in0]++;
+        if (o.in1 >= 0) consumers[o.in1]++;
+    }
+    // in backward order the LAST forward consumer writes first; every earlier consumer must accumulate
+    std::vector<int> seen(m->t.size(), 0);
+    for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
+        Op& o = m->ops[i];
+        if (o.in0 >= 0) {
+            o.in0_grad_accumulate = seen[o.in0] > 0;
+            seen[o.in0]++;
+        }
+        if (o.in1 >= 0) seen[o.in1]++;  // OP_ADD writes its second input first (see backward)
+    }
+    long long biggest = 0;
+    for (size_t i = 0; i < m->t.size(); ++i) {
+        TensorBuf& b = m->t[i];
+        int rc = dev_alloc(m, &b.a, b.size());
+        if (rc == CB_OK && (int)i != m->input) rc = dev_alloc(m, &b.d, b.size());
+        if (rc != CB_OK) { *out = m; return rc; }
+        if (b.size() > biggest) biggest = b.size();
+    }
+    m->scratch_elems = biggest;
+    int rc = dev_alloc(m, &m->scratch, biggest);
+    if (rc == CB_OK) rc = dev_alloc(m, &m->loss_dev, 4);
+    *out = m;
+    return rc;
+}
+
+int cbt_destroy(cbt_model* m) {
+    if (!m) return CB_EINVAL;
+    cudaStreamSynchronize(m->ctx->stream);
+    for (void* p : m->owned) cudaFree(p);
+    if (m->mom_table) cudaFree(m->mom_table);
+    delete m;
+    return CB_OK;
+}
+
+const char* cbt_last_error(const cbt_model* m) { return m ? m->err.c_str() : "null model"; }
+long long cbt_param_count(const cbt_model* m) { return m ? m->param_count : 0; }
+int cbt_param_entries(const cbt_model* m) { return m ? (int)m->params.size() : 0; }
+// entry i: offset, size, is_weight, kind (0 conv filter, 1 BN gamma, 2 BN beta, 3 FC weight, 4 FC bias), dims[4]
+int cbt_param_entry(const cbt_model* m, int i, long long* offset, long long* size, int* is_weight, int* kind, int* dims) {
+    if (!m || i < 0 || i >= (int)m->params.size()) return CB_EINVAL;
+    const ParamEntry& e = m->params[i];
+    *offset = e.offset; *size = e.size; *is_weight = e.is_weight; *kind = e.kind;
+    dims[0] = e.d0; dims[1] = e.d1; dims[2] = e.d2; dims[3] = e.d3;
+    return CB_OK;
+}
+int cbt_op_count(const cbt_model* m) { return m ? (int)m->ops.size() : 0; }
+
+// Binds the three caller-owned flat device buffers (each cbt_param_count floats, 16-byte aligned).
+int cbt_bind(cbt_model* m, float* params, float* grads, float* momentum) {
+    if (!m || !params || !grads || !momentum) return CB_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(params) | reinterpret_cast<uintptr_t>(grads) | reinterpret_cast<uintptr_t>(momentum)) & 15u) {
+        m->err = "flat parameter buffers must be 16-byte aligned";
+        return CB_EINVAL;
+    }
+    m->P = params; m->G = grads; m->M = momentum;
+    const int n = (int)m->params.size();
+    std::vector<float*> w(n), g(n), mo(n);
+    std::vector<long long> sz(n);
+    std::vector<unsigned char> fl(n);
+    for (int i = 0; i < n; ++i) {
+        const ParamEntry& e = m->params[i];
+        w[i] = m->P + e.offset; g[i] = m->G + e.offset; mo[i] = m->M + e.offset;
+        sz[i] = e.size; fl[i] = (unsigned char)e.is_weight;
+    }
+    if (m->mom_table) cudaFree(m->mom_table);
+    m->mom_table = nullptr;
+    int rc = cb::momentum_table_build(m->ctx, n, w.data(), g.data(), mo.data(), sz.data(), fl.data(), &m->mom_table,
+                                      &m->mom_biggest);
+    if (rc != CB_OK) m->err = cb_last_error(m->ctx);
+    return rc;
+}
+
+// Forward pass on `images` (batch x 3 x H x W, device) with one-hot `labels` (batch x classes, device).
+// Leaves the softmax in the last tensor and the summed loss in the model's device loss word.
+int cbt_forward(cbt_model* m, const float* images, const float* labels) {
+    if (!m || !m->P) return CB_EINVAL;
+    cb_ctx* ctx = m->ctx;
+    TensorBuf& in = m->t[m->input];
+    cudaError_t e = cudaMemcpyAsync(in.a, images, (size_t)in.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    m->labels = const_cast<float*>(labels);
+    for (const Op& o : m->ops) {
+        const TensorBuf& x = m->t[o.in0];
+        TensorBuf& y = m->t[o.out];
+        switch (o.kind) {
+            case OP_CONV:
+                CBT_TRY(cb_conv_fwd(ctx, m->P + o.w_off, x.a, y.a, nullptr, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                    o.stride, o.pad, o.pad, 0));
+                break;
+            case OP_BN:
+                CBT_TRY(cb_bn_fwd(ctx, x.a, m->P + o.b_off, m->P + o.w_off, nullptr, nullptr, y.a, m->t[o.xhat].a, x.n,
+                                  (long long)x.c * x.h * x.w));
+                break;
+            case OP_RELU: CBT_TRY(cb_relu(ctx, x.a, y.a, x.size())); break;
+            case OP_ADD: {
+                // y = in0 + in1 (ShortcutEndpoint::forward, seann/operands/controlling/ShortcutEndpoint.cu:57-74)
+                e = cudaMemcpyAsync(y.a, x.a, (size_t)x.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, y.a, m->t[o.in1].a, 0.f, y.size()));
+                break;
+            }
+            case OP_GAP: CBT_TRY(cb_global_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h * x.w)); break;
+            case OP_LINEAR:
+                CBT_TRY(cb_linear_fwd(ctx, x.a, m->P + o.w_off, m->P + o.b_off, y.a, x.n, x.c * x.h * x.w, o.oc));
+                break;
+            case OP_SOFTMAX_CE:
+                CBT_TRY(cb_softmax(ctx, x.a, y.a, x.n, x.c));
+                CBT_TRY(cb_cross_entropy(ctx, y.a, labels, m->t[o.in0].d, m->loss_dev, y.size()));
+                break;
+        }
+    }
+    return CB_OK;
+}
+
+// Backward pass: fills the flat gradient buffer (accumulating into it, as every seblas parameter-gradient kernel
+// does; cbt_update zeroes it again).
+int cbt_backward(cbt_model* m) {
+    if (!m || !m->G) return CB_EINVAL;
+    cb_ctx* ctx = m->ctx;
+    for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
+        const Op& o = m->ops[i];
+        TensorBuf& x = m->t[o.in0];
+        TensorBuf& y = m->t[o.out];
+        // where this op's data gradient goes: straight into x.d, or into scratch followed by x.d += scratch
+        float* dx = o.in0_grad_accumulate ? m->scratch : x.d;
+        switch (o.kind) {
+            case OP_SOFTMAX_CE: break;  // the forward already wrote softmax - labels into the logits' gradient
+            case OP_LINEAR:
+                CBT_TRY(cb_linear_paramgrad(ctx, y.d, x.a, m->G + o.w_off, m->G + o.b_off, x.n, x.c * x.h * x.w, o.oc));
+                CBT_TRY(cb_linear_xgrad(ctx, y.d, m->P + o.w_off, dx, x.n, x.c * x.h * x.w, o.oc));
+                break;
+            case OP_GAP: CBT_TRY(cb_global_avgpool_back(ctx, dx, y.d, (long long)x.n * x.c, x.h * x.w)); break;
+            case OP_RELU: CBT_TRY(cb_relu_grad(ctx, x.a, y.d, dx, x.size())); break;
+            case OP_ADD: {
+                // both inputs receive dY (ShortcutEndpoint::xGrads routes the same gradient to the skip path)
+                TensorBuf& x1 = m->t[o.in1];
+                cudaError_t e = cudaMemcpyAsync(x1.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e == cudaSuccess && !o.in0_grad_accumulate)
+                    e = cudaMemcpyAsync(x.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                if (o.in0_grad_accumulate) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, y.d, 0.f, x.size()));
+                continue;
+            }
+            case OP_BN:
+                CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, m->G + o.w_off, m->G + o.b_off, x.n,
+                                        (long long)x.c * x.h * x.w));
+                CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, (long long)x.c * x.h * x.w));
+                break;
+            case OP_CONV:
+                CBT_TRY(cb_conv_wgrad(ctx, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                      o.stride, o.pad, o.pad, 1));
+                if (o.in0 != m->input)
+                    CBT_TRY(cb_conv_dgrad(ctx, m->P + o.w_off, y.d, dx, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                          o.stride, o.pad, o.pad));
+                break;
+        }
+        if (o.in0_grad_accumulate && o.in0 != m->input) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
+    }
+    return CB_OK;
+}
+
+// One Momentum step over every parameter tensor (one launch). BN parameter gradients are assigned, not
+// accumulated, by cb_bn_paramgrad, exactly like the reference kernel (cuBatchNorm.cu:128-147).
+int cbt_update(cbt_model* m, float lr, float beta, float l2) {
+    if (!m || !m->P || !m->mom_table) return CB_EINVAL;
+    CBT_TRY(cb::momentum_table_launch(m->ctx, m->mom_table, (int)m->params.size(), m->mom_biggest, lr, beta, l2));
+    return CB_OK;
+}
+
+// Mean loss per sample of the last forward pass (synchronises the stream).
+int cbt_loss(cbt_model* m, float* loss_mean) {
+    if (!m || !loss_mean) return CB_EINVAL;
+    float s = 0.f;
+    cudaError_t e = cudaStreamSynchronize(m->ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpy(&s, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    *loss_mean = s / (float)m->batch;
+    return CB_OK;
+}
+
+// Device pointers for tests: value (grad = 0) or gradient (grad = 1) of tensor `id`; -1 = logits, -2 = softmax.
+float* cbt_tensor_ptr(cbt_model* m, int id, int grad) {
+    if (!m) return nullptr;
+    if (id == -1) id = m->logits;
+    if (id == -2) id = m->probs;
+    if (id < 0 || id >= (int)m->t.size()) return nullptr;
+    return grad ? m->t[id].d : m->t[id].a;
+}
+float* cbt_loss_ptr(cbt_model* m) { return m ? m->loss_dev : nullptr; }
+// Copies n floats of a tensor (see cbt_tensor_ptr) into the caller's device buffer, in stream order.
+int cbt_copy_tensor(cbt_model* m, int id, int grad, float* dst, long long n) {
+    float* src = cbt_tensor_ptr(m, id, grad);
+    if (!src || !dst || n < 0) return CB_EINVAL;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, m->ctx->stream);
+    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    return CB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,139 @@
+"""Python face of the training-step executor (include/crusader_b200_train.h) for tests and bench.py.
+
+torch owns the flat parameter / gradient / momentum buffers and, under torchrun, performs the one collective of a
+data-parallel step: a sum-allreduce of the flat gradient buffer (NCCL) between backward and update."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from .api import Context, CrusaderError
+
+_i, _ll, _f, _fl = C.c_int, C.c_longlong, C.c_void_p, C.c_float
+TRAIN_SIGNATURES = {
+    "cbt_resnet_create": (_i, [C.POINTER(C.c_void_p), C.c_void_p, _i, _i, _i, _i]),
+    "cbt_destroy": (_i, [C.c_void_p]),
+    "cbt_last_error": (C.c_char_p, [C.c_void_p]),
+    "cbt_param_count": (_ll, [C.c_void_p]),
+    "cbt_param_entries": (_i, [C.c_void_p]),
+    "cbt_param_entry": (_i, [C.c_void_p, _i, C.POINTER(_ll), C.POINTER(_ll), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "cbt_op_count": (_i, [C.c_void_p]),
+    "cbt_bind": (_i, [C.c_void_p, _f, _f, _f]),
+    "cbt_forward": (_i, [C.c_void_p, _f, _f]),
+    "cbt_backward": (_i, [C.c_void_p]),
+    "cbt_update": (_i, [C.c_void_p, _fl, _fl, _fl]),
+    "cbt_loss": (_i, [C.c_void_p, C.POINTER(_fl)]),
+    "cbt_tensor_ptr": (C.c_void_p, [C.c_void_p, _i, _i]),
+    "cbt_loss_ptr": (C.c_void_p, [C.c_void_p]),
+    "cbt_copy_tensor": (_i, [C.c_void_p, _i, _i, _f, _ll]),
+}
+KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
+
+
+def _load():
+    lib = _lib.load()
+    for name, (res, args) in TRAIN_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+class ResNetTrainer:
+    """ResNet-(6*blocks+2) training step on one GPU; `group` (a torch.distributed group or True) enables the
+    gradient allreduce."""
+
+    def __init__(self, ctx: Context, batch: int, blocks_per_stage: int = 9, image_hw: int = 32, classes: int = 10,
+                 distributed: bool = False):
+        self.lib = _load()
+        self.ctx = ctx
+        self.batch, self.classes, self.image_hw = batch, classes, image_hw
+        self.distributed = distributed
+        h = C.c_void_p()
+        rc = self.lib.cbt_resnet_create(C.byref(h), ctx.h, batch, blocks_per_stage, image_hw, classes)
+        self.h = h
+        if rc != 0:
+            raise CrusaderError(rc, self.lib.cbt_last_error(h).decode() if h else "cbt_resnet_create failed")
+        self.n_params = int(self.lib.cbt_param_count(h))
+        dev = torch.device("cuda", ctx.device)
+        self.params = torch.zeros(self.n_params, device=dev)
+        self.grads = torch.zeros(self.n_params, device=dev)
+        self.momentum = torch.zeros(self.n_params, device=dev)
+        self._check(self.lib.cbt_bind(h, self.params.data_ptr(), self.grads.data_ptr(), self.momentum.data_ptr()))
+        self.entries = []
+        for i in range(self.lib.cbt_param_entries(h)):
+            off, size, isw, kind = _ll(), _ll(), _i(), _i()
+            dims = (_i * 4)()
+            self._check(self.lib.cbt_param_entry(h, i, C.byref(off), C.byref(size), C.byref(isw), C.byref(kind), dims))
+            self.entries.append(dict(offset=off.value, size=size.value, is_weight=bool(isw.value), kind=KINDS[kind.value],
+                                     dims=tuple(dims)))
+
+    def _check(self, rc):
+        if rc != 0:
+            raise CrusaderError(rc, self.lib.cbt_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.cbt_destroy(self.h)
+            self.h = None
+
+    # ---- parameters
+    def init_params(self, seed_key="init") -> np.ndarray:
+        """He-normal filters and dense weights, gamma = 1, beta = 0 — the reference's randFillNetParams
+        (seann/operands/seblas/Conv2D.cu:45-50, Linear.cu:42-46, BatchNorm.cu:8-11) with seeded draws."""
+        from oracle import oracle as orc  # seeded generators shared with the tests
+        host = np.zeros(self.n_params, dtype=np.float32)
+        for i, e in enumerate(self.entries):
+            sl = slice(e["offset"], e["offset"] + e["size"])
+            if e["kind"] == "conv":
+                oc, ic, fh, fw = e["dims"]
+                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / (ic * fh * fw))))
+            elif e["kind"] == "fc_weight":
+                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["dims"][1])))
+            elif e["kind"] == "fc_bias":
+                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["size"])))
+            elif e["kind"] == "bn_gamma":
+                host[sl] = 1.0
+        self.set_params(host)
+        return host
+
+    def set_params(self, host: np.ndarray):
+        self.params.copy_(torch.from_numpy(np.ascontiguousarray(host, dtype=np.float32)))
+        self.grads.zero_()
+        self.momentum.zero_()
+
+    # ---- step
+    def forward(self, images: torch.Tensor, labels_onehot: torch.Tensor):
+        self._check(self.lib.cbt_forward(self.h, images.data_ptr(), labels_onehot.data_ptr()))
+
+    def backward(self):
+        self._check(self.lib.cbt_backward(self.h))
+
+    def allreduce_grads(self):
+        if self.distributed:
+            import torch.distributed as dist
+            dist.all_reduce(self.grads, op=dist.ReduceOp.SUM)
+
+    def update(self, lr: float, beta: float = 0.9, l2: float = 1e-4):
+        self._check(self.lib.cbt_update(self.h, lr, beta, l2))
+
+    def step(self, images, labels_onehot, lr, beta=0.9, l2=1e-4):
+        self.forward(images, labels_onehot)
+        self.backward()
+        self.allreduce_grads()
+        self.update(lr, beta, l2)
+
+    def loss(self) -> float:
+        v = _fl()
+        self._check(self.lib.cbt_loss(self.h, C.byref(v)))
+        return float(v.value)
+
+    def tensor(self, tid: int, shape, grad=False) -> torch.Tensor:
+        """Copy of an internal activation (or its gradient) for tests."""
+        n = int(np.prod(shape))
+        out = torch.empty(n, device=self.params.device)
+        self._check(self.lib.cbt_copy_tensor(self.h, tid, int(grad), out.data_ptr(), n))
+        self.ctx.synchronize()
+        return out.view(*shape)

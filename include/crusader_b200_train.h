@@ -1,0 +1,54 @@
+/*
+ * crusader_b200 — training-step executor over the C ABI of crusader_b200.h.
+ *
+ * Replaces the inner loop of the reference's Sequential::train (seann/containers/Sequential.cu:43-104:
+ * forward / backward / learn) for the ResNet family of the specification, keeping the reference's training
+ * semantics: gradients summed over the batch, loss gradient softmax - onehot (seblas/operations/cuLoss.cu:231),
+ * BatchNorm per (c,h,w) position (cuBatchNorm.cu:14-61), residual blocks as in archive/Resnet56:8-15, Momentum with
+ * multiplicative weight decay (seann/optimizers/Optimizers.cu:17-22).
+ *
+ * Parameters, gradients and momentum are three flat caller-owned device buffers with one layout (cbt_param_entry),
+ * so a data-parallel caller sum-allreduces the one gradient buffer between cbt_backward and cbt_update.
+ */
+#ifndef CRUSADER_B200_TRAIN_H
+#define CRUSADER_B200_TRAIN_H
+
+#include "crusader_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cbt_model cbt_model;
+
+/* ResNet with 6*blocks_per_stage + 2 layers (9 -> ResNet-56) on batch x 3 x image_hw x image_hw inputs. */
+int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_stage, int image_hw, int classes);
+int cbt_destroy(cbt_model* m);
+const char* cbt_last_error(const cbt_model* m);
+
+/* Flat parameter layout: total floats, number of tensors, and entry i = (offset, size, is_weight,
+ * kind: 0 conv filter, 1 BN gamma, 2 BN beta, 3 FC weight, 4 FC bias, dims[4]). */
+long long cbt_param_count(const cbt_model* m);
+int cbt_param_entries(const cbt_model* m);
+int cbt_param_entry(const cbt_model* m, int i, long long* offset, long long* size, int* is_weight, int* kind, int* dims);
+int cbt_op_count(const cbt_model* m);
+
+/* Binds the flat device buffers (cbt_param_count floats each, 16-byte aligned; gradients start at zero). */
+int cbt_bind(cbt_model* m, float* params, float* grads, float* momentum);
+
+/* One training step in three asynchronous parts on the context's stream. */
+int cbt_forward(cbt_model* m, const float* images, const float* labels_onehot);
+int cbt_backward(cbt_model* m);
+int cbt_update(cbt_model* m, float lr, float beta, float l2);
+
+/* Mean cross-entropy per sample of the last forward pass (synchronises the stream), as Sequential::train logs it. */
+int cbt_loss(cbt_model* m, float* loss_mean);
+/* Device pointers for tests: value (grad = 0) / gradient (grad = 1) of tensor id; -1 = logits, -2 = softmax. */
+float* cbt_tensor_ptr(cbt_model* m, int id, int grad);
+float* cbt_loss_ptr(cbt_model* m);
+int cbt_copy_tensor(cbt_model* m, int id, int grad, float* dst, long long n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CRUSADER_B200_TRAIN_H */

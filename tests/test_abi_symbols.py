@@ -47,3 +47,25 @@ def test_no_gpu_means_loud_failure():
         lib.cb_destroy(h)
     else:
         assert rc != 0 and not h.value
+
+
+def test_trainer_header_symbols_are_exported_and_bound():
+    from crusaderbackend_b200 import train
+    text = open(os.path.join(ROOT, "include", "crusader_b200_train.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(cbt_[a-z0-9_]+)\s*\(", text)))
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    assert not [s for s in declared if not hasattr(lib, s)]
+    assert sorted(train.TRAIN_SIGNATURES) == declared
+
+
+def test_compat_shim_compiles_against_the_library():
+    """The header shim with the reference's seblas signatures builds into a program that links the C ABI."""
+    import subprocess
+    cb_build.build()
+    out = os.path.join(ROOT, "tests", "cpp", "compat_smoke")
+    cmd = ["nvcc", "-std=c++17", "-x", "cu", "-I", os.path.join(ROOT, "crusaderbackend_b200", "compat"), "-o", out,
+           os.path.join(ROOT, "tests", "cpp", "compat_smoke.cpp"), "-L", os.path.join(ROOT, "crusaderbackend_b200", "lib"),
+           "-lcrusader_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../crusaderbackend_b200/lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

@@ -1,0 +1,106 @@
+"""The ResNet training step on a B200 against the CPU oracle composed from the per-op fp64 oracle
+(tests/resnet_oracle.py), and loss tracking of the tensor-core modes against the CUDA-core fp32 run."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.resnet_oracle import ResNetOracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch
+
+
+def make_batch(torch, batch, hw, classes, key):
+    images = orc.normal((batch, 3, hw, hw), key, "img")
+    lab = orc.rng_for(key, "lab").integers(0, classes, batch)
+    onehot = np.zeros((batch, classes), dtype=np.float32)
+    onehot[np.arange(batch), lab] = 1
+    return images, onehot, torch.from_numpy(images).cuda(), torch.from_numpy(onehot).cuda()
+
+
+@pytest.mark.parametrize("math,tol", [("fp32", 2e-4), ("tf32", 5e-2)])
+def test_resnet8_step_matches_oracle(torch_cuda, math, tol):
+    """ResNet-8 (one block per stage), batch 8, 32x32: loss, logits and every parameter gradient. In fp32 mode every
+    gradient tensor matches the oracle to 2e-4. TF32 rounding is amplified by the batch-of-8 BatchNorm layers
+    (division by the spread of 8 samples), so there each gradient tensor is held to a cosine of 0.995 with the
+    oracle's and 5e-2 on loss and logits."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import ResNetTrainer
+    ctx = Context(0, math=math, sync=True)
+    tr = ResNetTrainer(ctx, batch=8, blocks_per_stage=1, image_hw=32, classes=10)
+    oracle = ResNetOracle(1, 32, 10)
+    shapes = oracle.param_shapes()
+    assert [e["kind"] for e in tr.entries] == [k for k, _ in shapes]
+    assert [e["size"] for e in tr.entries] == [int(np.prod(s)) for _, s in shapes]
+    host = tr.init_params("r8")
+    # perturb gamma / beta so their gradients are exercised away from (1, 0)
+    for i, e in enumerate(tr.entries):
+        if e["kind"].startswith("bn"):
+            host[e["offset"]:e["offset"] + e["size"]] += 0.1 * orc.uniform_pm1((e["size"],), "r8", "bnp", i)
+    tr.set_params(host)
+    P = [host[e["offset"]:e["offset"] + e["size"]].reshape(s) for e, (_, s) in zip(tr.entries, shapes)]
+    images, onehot, dimg, dlab = make_batch(torch, 8, 32, 10, "r8")
+    tr.forward(dimg, dlab)
+    tr.backward()
+    ctx.synchronize()
+    loss_ref, G_ref, logits_ref = oracle.run(P, images, onehot)
+    assert abs(tr.loss() - loss_ref) <= tol * max(1.0, abs(loss_ref))
+    logits = tr.tensor(-1, (8, 10)).cpu().numpy()
+    assert orc.max_err_norm(logits, logits_ref) <= tol
+    g = tr.grads.cpu().numpy()
+    for e, gr in zip(tr.entries, G_ref):
+        got = g[e["offset"]:e["offset"] + e["size"]].astype(np.float64)
+        want = np.asarray(gr, dtype=np.float64).ravel()
+        if math == "fp32":
+            assert orc.max_err_norm(got, want) <= tol, (e["kind"], e["dims"])
+        else:
+            cos = float(got @ want) / max(float(np.linalg.norm(got) * np.linalg.norm(want)), 1e-300)
+            assert cos >= 0.995, (e["kind"], e["dims"], cos)
+    # one Momentum step: identical to the oracle update applied to the GPU's own gradients
+    before_w, before_g = tr.params.cpu().numpy().copy(), g.copy()
+    tr.update(0.01 / 8, 0.9, 1e-4)
+    ctx.synchronize()
+    after = tr.params.cpu().numpy()
+    for e in tr.entries:
+        sl = slice(e["offset"], e["offset"] + e["size"])
+        w, m_, _ = orc.momentum(before_w[sl], before_g[sl], np.zeros(e["size"]), 0.01 / 8, 0.9, 1e-4, e["is_weight"])
+        assert orc.max_err_norm(after[sl], w) <= 1e-6
+    assert not tr.grads.any()
+    tr.close()
+    ctx.close()
+
+
+def test_resnet56_loss_tracks_fp32_run(torch_cuda):
+    """ResNet-56, batch 128 of N(0,1) CIFAR-shaped images, uniform labels, He init, momentum 0.9, lr 0.01/128:
+    the TF32 tensor-core run's loss stays within 1 % of the CUDA-core fp32 run over the first steps, and both
+    decrease on a repeated batch."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import ResNetTrainer
+    steps = 30
+    losses = {}
+    _, _, dimg, dlab = make_batch(torch, 128, 32, 10, "r56")
+    for math in ("fp32", "tf32"):
+        ctx = Context(0, math=math, sync=False)
+        tr = ResNetTrainer(ctx, batch=128, blocks_per_stage=9, image_hw=32, classes=10)
+        assert len([e for e in tr.entries if e["kind"] == "conv"]) == 57
+        tr.init_params("r56")
+        cur = []
+        for _ in range(steps):
+            tr.step(dimg, dlab, lr=0.01 / 128)
+            cur.append(tr.loss())
+        ctx.synchronize()
+        losses[math] = cur
+        tr.close()
+        ctx.close()
+    a, b = np.array(losses["fp32"]), np.array(losses["tf32"])
+    assert np.isfinite(a).all() and np.isfinite(b).all()
+    assert a[-1] < a[0] and b[-1] < b[0]
+    assert np.abs(a - b).max() / np.abs(a).max() <= 0.01
