@@ -238,11 +238,138 @@ def bench_ours(args):
             "tflops_by_shape": detail,
         }
         line["cpu_baseline"] = None if args.no_cpu else cpu_baseline_leg()
-        print(json.dumps(line), flush=True)
+    extra_conv = None
+    if not args.shapes or args.conv_shapes:
+        only = set(args.conv_shapes.split(",")) if args.conv_shapes else None
+        extra_conv = conv_section(ctx, torch, dev, flush, only)
     ctx.close()
+    extra_resnet = None
+    if not args.shapes and not args.no_resnet:
+        try:
+            extra_resnet = resnet56_section(torch, local, world, max(args.steps, 5), args.warmup)
+        except Exception as exc:  # keep the headline line even if the training section fails
+            extra_resnet = {"error": str(exc)[:300]}
+    if rank == 0:
+        line["conv"] = extra_conv
+        line["resnet56_train"] = extra_resnet
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------ conv shapes / ResNet-56
+CONV_SHAPES = [  # (name, N, IC, H, OC, F, stride, pad): config 3 and the ResNet-56 layer shapes
+    ("c3_64to64_3x3_s1_32x32", 128, 64, 32, 64, 3, 1, 1),
+    ("c3_32to64_3x3_s2_32x32", 128, 32, 32, 64, 3, 2, 1),
+    ("r56_16to16_3x3_s1_32x32", 128, 16, 32, 16, 3, 1, 1),
+    ("r56_32to32_3x3_s1_16x16", 128, 32, 16, 32, 3, 1, 1),
+    ("r56_64to64_3x3_s1_8x8", 128, 64, 8, 64, 3, 1, 1),
+]
+
+
+def conv_section(ctx, torch, dev, flush, only=None):
+    """Forward / data-gradient / weight-gradient of the convolution shapes: per-call CUDA-event time with the L2
+    flushed before each call, TFLOP/s on 2*N*OC*OH*OW*IC*FH*FW and GB/s on 4*(|X|+|W|+|Y|)."""
+    out = {}
+    for (name, N, IC, H, OC, F, s, p) in CONV_SHAPES:
+        if only and name not in only:
+            continue
+        OH = (H - F + 2 * p) // s + 1
+        X = torch.randn(N, IC, H, H, device=dev)
+        W = torch.randn(OC, IC, F, F, device=dev) * (2.0 / (IC * F * F)) ** 0.5
+        Y = torch.empty(N, OC, OH, OH, device=dev)
+        dY = torch.randn(N, OC, OH, OH, device=dev)
+        dX = torch.empty_like(X)
+        dW = torch.zeros_like(W)
+        fl = 2.0 * N * OC * OH * OH * IC * F * F
+        by = 4.0 * (X.numel() + W.numel() + Y.numel())
+        calls = {"fwd": lambda: ctx.conv(W, X, Y, s, s, p, p), "dgrad": lambda: ctx.convDerive(W, dY, dX, s, s, p, p),
+                 "wgrad": lambda: ctx.convError(dY, X, dW, s, s, p, p)}
+        for pname, fn in calls.items():
+            for _ in range(2):
+                fn()
+            ts = []
+            for _ in range(5):
+                flush.fill_(1.0)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ms = sorted(ts)[len(ts) // 2]
+            out[f"{name}_{pname}"] = {"us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1),
+                                      "gbs": round(by / ms / 1e6, 1), "kernel": ctx.last_kernel}
+    return out
+
+
+def resnet56_section(torch, local, world, steps, warmup):
+    """ResNet-56 training step (forward + backward + gradient allreduce + Momentum), global batch 128 split over the
+    ranks (strong scaling, the configuration of the specification), replayed as one CUDA graph. Each timed step
+    includes the host->device copy of that step's images and labels from pinned memory and ends with a device->host
+    read of the loss."""
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import ResNetTrainer
+    from crusaderbackend_b200 import dp
+    from oracle import oracle as orc
+    gb = 128
+    rank = int(os.environ.get("RANK", "0"))
+    start, count = dp.shard_batch(gb, world, rank)
+    ctx = Context(local, math="tf32", sync=False)
+    tr = ResNetTrainer(ctx, batch=count, blocks_per_stage=9, image_hw=32, classes=10, distributed=world > 1)
+    tr.init_params("bench")
+    h_img = torch.from_numpy(orc.normal((gb, 3, 32, 32), "bench", "img")[start:start + count].copy()).pin_memory()
+    lab = orc.rng_for("bench", "lab").integers(0, 10, gb)[start:start + count]
+    onehot = torch.zeros(count, 10)
+    onehot[torch.arange(count), torch.from_numpy(lab)] = 1
+    h_lab = onehot.pin_memory()
+    d_img = torch.empty(count, 3, 32, 32, device="cuda")
+    d_lab = torch.empty(count, 10, device="cuda")
+    d_img.copy_(h_img)
+    d_lab.copy_(h_lab)
+    lr = 0.01 / gb
+    launches0 = ctx.launches
+    tr.step(d_img, d_lab, lr)
+    launches = ctx.launches - launches0
+    graph = tr.capture_step(d_img, d_lab, lr, warmup=2)
+    loss_dev = torch.empty(1, device="cuda")
+    h_loss = torch.empty(1).pin_memory()
+
+    def one_step():
+        d_img.copy_(h_img, non_blocking=True)
+        d_lab.copy_(h_lab, non_blocking=True)
+        graph.replay()
+        tr.lib.cbt_copy_loss(tr.h, loss_dev.data_ptr())
+        h_loss.copy_(loss_dev, non_blocking=True)
+
+    for _ in range(max(3, warmup)):
+        one_step()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms = float(t.item())
+    res = {"images_per_s": round(gb / ms * 1e3, 1), "ms_per_step": round(ms, 3), "global_batch": gb,
+           "per_gpu_batch": count, "scaling": "strong", "math": "tf32", "kernels_per_step": int(launches),
+           "cuda_graph": True, "loss_mean_last": round(float(h_loss.item()) / count, 5),
+           "h2d_bytes_per_step": int(h_img.numel() * 4 + h_lab.numel() * 4), "d2h_bytes_per_step": 4,
+           "flops_per_step": 96.5e9,
+           "note": "forward+backward+allreduce+Momentum; BatchNorm statistics are per GPU shard"}
+    tr.close()
+    ctx.close()
+    return res
 
 
 # ------------------------------------------------------------------------------------------ CPU legs
@@ -315,8 +442,12 @@ def main():
     ap.add_argument("--math", default="tf32", choices=["tf32", "3xtf32"])
     ap.add_argument("--shapes", default="", help="comma list like 4096x4096x4096_NN: restrict the sweep (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--conv-shapes", default="", help="comma list of CONV_SHAPES names: restrict the convolution section")
+    ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-56 training section")
     args = ap.parse_args()
-    if args.shapes:
+    if args.shapes == "none":
+        SWEEP[:] = [(128, 10, 4096, "NN")]
+    elif args.shapes:
         keep = set(args.shapes.split(","))
         SWEEP[:] = [s for s in SWEEP if f"{s[0]}x{s[1]}x{s[2]}_{s[3]}" in keep]
         if not SWEEP:

@@ -31,10 +31,9 @@
 namespace cb {
 namespace {
 
-constexpr int kCB = 8;          // input channels per pipeline stage (= one UMMA K step per tap)
+constexpr int kCB = 8;          // input channels per UMMA K step
 constexpr int kMaxStages = 8;
 constexpr int kRowBytes = 128;  // one line of 32 floats
-constexpr uint32_t kBlockBytes = kCB * kRowBytes;  // one line of 8 channels
 
 struct ConvParams {
     int N, Cin, H, W, Cout;   // "input" and "output" of this pass (forward: X -> Y, dgrad: dY -> dX)
@@ -42,7 +41,8 @@ struct ConvParams {
     int OCp;                  // Cout rounded up to 16
     int NQ;                   // UMMA N = FW * OCp
     int CG;                   // 32-channel groups of the packed filter
-    int NCB;                  // ceil(Cin / 8) pipeline stages per tile
+    int KS;                   // UMMA K steps (8 channels each) per pipeline stage
+    int NCB;                  // ceil(Cin / (8 * KS)) pipeline stages per tile
     int L;                    // image rows per line (32 / W)
     int LPI;                  // lines per image (H / L)
     int shared_rows;          // 1: the FH taps of a tile share FH + 3 row blocks (W == 32); 0: FH * 4 blocks
@@ -52,7 +52,8 @@ struct ConvParams {
     int stages;
     int tmem_cols;
     uint32_t w_bytes;         // resident packed filter
-    uint32_t stage_bytes;     // nblocks * 1 KB
+    uint32_t block_bytes;     // one line of a stage: 8 * KS channels x 128 B
+    uint32_t stage_bytes;     // nblocks * block_bytes
     float* Out;
     const float* bias;
     int relu;
@@ -135,13 +136,14 @@ __global__ void __launch_bounds__(192, 1)
                     const uint32_t full = smem_u32(&cs.full[s]);
                     const uint32_t dst0 = st_base + s * p.stage_bytes;
                     mbar_expect_tx(full, p.stage_bytes);
+                    const int c0 = cb * p.KS * kCB;
                     if (p.shared_rows) {
-                        // W == 32: the tile is 4 consecutive rows of one image; block r = input row h0 - pH + r
+                        // W == 32: the tile is 4 consecutive rows of one image; ONE box (32 px, 8*KS channels, FH+3
+                        // rows) lands as [row][channel][128 B]; rows above / below the image are zero-filled
                         const long long g = 4LL * tile;
                         const int n = (int)(g / p.LPI);
                         const int h0 = (int)(g - (long long)n * p.LPI);
-                        for (int r = 0; r < p.nblocks; ++r)
-                            tma_load_3d(dst0 + (uint32_t)r * kBlockBytes, &tmIn, full, (h0 - p.pH + r) * p.W, cb * kCB, n);
+                        tma_load_4d(dst0, &tmIn, full, 0, c0, h0 - p.pH, n);
                     } else {
                         for (int fh = 0; fh < p.FH; ++fh) {
                             for (int j = 0; j < 4; ++j) {
@@ -149,8 +151,8 @@ __global__ void __launch_bounds__(192, 1)
                                 // lines past the end use an image index >= N: the whole box is zero-filled
                                 const int n = (int)(g / p.LPI);
                                 const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
-                                tma_load_3d(dst0 + (uint32_t)(fh * 4 + j) * kBlockBytes, &tmIn, full,
-                                            (h0 + fh - p.pH) * p.W, cb * kCB, n);
+                                tma_load_3d(dst0 + (uint32_t)(fh * 4 + j) * p.block_bytes, &tmIn, full,
+                                            (h0 + fh - p.pH) * p.W, c0, n);
                             }
                         }
                     }
@@ -177,16 +179,19 @@ __global__ void __launch_bounds__(192, 1)
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t stg = st_base + s * p.stage_bytes;
-                    const uint32_t wq = w_base + (uint32_t)(cb >> 2) * p.NQ * kRowBytes + (uint32_t)(cb & 3) * 32u;
                     for (int fh = 0; fh < p.FH; ++fh) {
-                        // P: 4 lines x [8 channels][128 B], MN-major: 1024 B between lines, 512 B per 4 channel rows
                         const uint32_t first_block = p.shared_rows ? (uint32_t)fh : (uint32_t)fh * 4u;
-                        const uint64_t dP = umma_smem_desc(stg + first_block * kBlockBytes, 1024u, 512u,
-                                                           UMMA_SW_128B_BASE32B);
-                        // Q: packed filter rows [(fw, oc)][32 channels], K-major, the 8 channels of this stage
-                        const uint64_t dQ = umma_smem_desc(wq + (uint32_t)fh * p.CG * p.NQ * kRowBytes, 16u, 1024u,
-                                                           UMMA_SW_128B);
-                        umma_tf32(d_tmem, dP, dQ, idesc, (cb == 0 && fh == 0) ? 0u : 1u);
+                        for (int kk = 0; kk < p.KS; ++kk) {
+                            const int ks = cb * p.KS + kk;  // global K step: channels [8 ks, 8 ks + 8)
+                            // P: 4 lines x [8 channels][128 B], MN-major: block_bytes between lines, 512 B per 4 rows
+                            const uint64_t dP = umma_smem_desc(stg + first_block * p.block_bytes + (uint32_t)kk * 1024u,
+                                                               p.block_bytes, 512u, UMMA_SW_128B_BASE32B);
+                            // Q: packed filter rows [(fw, oc)][32 channels], K-major
+                            const uint64_t dQ = umma_smem_desc(w_base + (uint32_t)(fh * p.CG + (ks >> 2)) * p.NQ * kRowBytes +
+                                                                   (uint32_t)(ks & 3) * 32u,
+                                                               16u, 1024u, UMMA_SW_128B);
+                            umma_tf32(d_tmem, dP, dQ, idesc, (cb == 0 && fh == 0 && kk == 0) ? 0u : 1u);
+                        }
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
                     if (cb == p.NCB - 1) tc_commit(smem_u32(&cs.tfull[a]));
@@ -290,93 +295,149 @@ __global__ void pack_filter_kernel(const float* __restrict__ W, float* __restric
     }
 }
 
-}  // namespace
+// Where a launch takes its stream, scratch and status word from: a cb_ctx (workspace grown with cudaMalloc) or the
+// static arrays of the allocation-free entry point.
+struct ConvEnv {
+    cudaStream_t stream;
+    int sm_count, smem_optin;
+    float* pack;   // scratch for the packed filter (>= pack_bytes)
+    int* status;
+};
 
-int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
-                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of) {
-    // geometry covered by the tensor-core path
+// Geometry the tensor-core forward / data-gradient kernel covers; fills the derived sizes.
+struct ConvPlan {
+    int Cin, Cout, OCp, NQ, CG, L, KS, shared_rows, nblocks, stages;
+    size_t w_bytes;
+    uint32_t block_bytes, stage_bytes;
+};
+
+static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int IC, int IH, int IW, int OC, int FH, int FW, int sH,
+                     int sW, int pH, int pW, bool dgrad_of) {
     if (sH != 1 || sW != 1) return CB_EUNSUPPORTED;
     if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
     if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
     if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
-    const int L = 32 / IW;
-    if (IH % L) return CB_EUNSUPPORTED;
+    q.L = 32 / IW;
+    if (IH % q.L) return CB_EUNSUPPORTED;
     // roles: forward reads X (IC channels) and writes OC planes; the data gradient reads dY (OC) and writes IC
-    const int Cin = dgrad_of ? OC : IC;
-    const int Cout = dgrad_of ? IC : OC;
-    const int OCp = (Cout + 15) / 16 * 16;
-    const int NQ = FW * OCp;
-    if (NQ > 256 || Cin < 1) return CB_EUNSUPPORTED;
+    q.Cin = dgrad_of ? OC : IC;
+    q.Cout = dgrad_of ? IC : OC;
+    q.OCp = (q.Cout + 15) / 16 * 16;
+    q.NQ = FW * q.OCp;
+    if (q.NQ > 256 || q.Cin < 1) return CB_EUNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) != 0) return CB_EUNSUPPORTED;
-    const int CG = (Cin + 31) / 32;
-    const size_t w_bytes = (size_t)FH * CG * NQ * kRowBytes;
-    const int shared_rows = (L == 1 && IH % 4 == 0) ? 1 : 0;
-    const int nblocks = shared_rows ? FH + 3 : FH * 4;
-    const uint32_t stage_bytes = (uint32_t)nblocks * kBlockBytes;
-    const long long smem_cap = (long long)ctx->max_smem_optin - 2048;
-    long long stages = (smem_cap - (long long)w_bytes) / stage_bytes;
-    if (stages < 2) return CB_EUNSUPPORTED;
-    if (stages > kMaxStages) stages = kMaxStages;
-
-    int rc = ensure_workspace(ctx, w_bytes);
-    if (rc != CB_OK) return rc;
-    float* Wp = static_cast<float*>(ctx->workspace);
-    {
-        const long long total = (long long)w_bytes / 4;
-        int grid = (int)((total + 255) / 256);
-        if (grid > ctx->sm_count * 8) grid = ctx->sm_count * 8;
-        pack_filter_kernel<<<grid, 256, 0, ctx->stream>>>(W, Wp, OC, IC, FH, FW, OCp, CG, dgrad_of ? 1 : 0, total);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return check_cuda(ctx, e, "pack_filter_kernel launch");
-        ctx->launches += 1;
+    q.CG = (q.Cin + 31) / 32;
+    q.w_bytes = (size_t)FH * q.CG * q.NQ * kRowBytes;
+    q.shared_rows = (q.L == 1 && IH % 4 == 0) ? 1 : 0;
+    q.nblocks = q.shared_rows ? FH + 3 : FH * 4;
+    const long long cap = (long long)smem_optin - 2048 - (long long)q.w_bytes;
+    // as many K steps per stage as leaves a pipeline of at least 4 stages (fewer, larger TMA boxes)
+    const int cin8 = (q.Cin + 7) / 8;
+    q.KS = 0;
+    for (int ks = 4; ks >= 1; ks >>= 1) {
+        if (ks > cin8 && ks > 1) continue;
+        const long long st = cap / ((long long)q.nblocks * ks * kCB * kRowBytes);
+        if (st >= 4 || (ks == 1 && st >= 2)) {
+            q.KS = ks;
+            q.stages = (int)(st > kMaxStages ? kMaxStages : st);
+            break;
+        }
     }
+    if (q.KS == 0) return CB_EUNSUPPORTED;
+    q.block_bytes = (uint32_t)q.KS * kCB * kRowBytes;
+    q.stage_bytes = (uint32_t)q.nblocks * q.block_bytes;
+    return CB_OK;
+}
 
+// Packs the filter into env.pack and launches the kernel. `err_ctx` may be null (allocation-free entry point).
+static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const float* W, const float* X, float* Y,
+                       const float* bias, int N, int IC, int IH, int IW, int OC, int FH, int FW, int pH, int relu,
+                       bool dgrad_of) {
+    {
+        const long long total = (long long)q.w_bytes / 4;
+        int grid = (int)((total + 255) / 256);
+        if (grid > env.sm_count * 8) grid = env.sm_count * 8;
+        pack_filter_kernel<<<grid, 256, 0, env.stream>>>(W, env.pack, OC, IC, FH, FW, q.OCp, q.CG, dgrad_of ? 1 : 0, total);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return check_cuda(err_ctx, e, "pack_filter_kernel launch");
+    }
     ConvParams p{};
-    p.N = N; p.Cin = Cin; p.H = IH; p.W = IW; p.Cout = Cout;
+    p.N = N; p.Cin = q.Cin; p.H = IH; p.W = IW; p.Cout = q.Cout;
     p.FH = FH; p.FW = FW; p.pH = pH;
-    p.OCp = OCp; p.NQ = NQ; p.CG = CG; p.NCB = (Cin + kCB - 1) / kCB;
-    p.L = L; p.LPI = IH / L;
-    p.shared_rows = shared_rows; p.nblocks = nblocks;
+    p.OCp = q.OCp; p.NQ = q.NQ; p.CG = q.CG; p.KS = q.KS;
+    p.NCB = (q.Cin + q.KS * kCB - 1) / (q.KS * kCB);
+    p.L = q.L; p.LPI = IH / q.L;
+    p.shared_rows = q.shared_rows; p.nblocks = q.nblocks;
     p.total_lines = (long long)N * p.LPI;
     p.tiles = (int)((p.total_lines + 3) / 4);
-    p.stages = (int)stages;
+    p.stages = q.stages;
     int cols = 32;
-    while (cols < 2 * NQ) cols <<= 1;
+    while (cols < 2 * q.NQ) cols <<= 1;
     p.tmem_cols = cols;
-    p.w_bytes = (uint32_t)w_bytes;
-    p.stage_bytes = stage_bytes;
+    p.w_bytes = (uint32_t)q.w_bytes;
+    p.block_bytes = q.block_bytes;
+    p.stage_bytes = q.stage_bytes;
     p.Out = Y; p.bias = bias; p.relu = relu;
-    p.status = ctx->d_status;
+    p.status = env.status;
 
     CUtensorMap tmIn, tmW;
-    {
-        // input planes flattened to (H*W, C, N): a box is 32 consecutive floats of 8 channel planes, starting at
-        // pixel (row * W) — a multiple of 4 floats, as TMA requires of the innermost coordinate. Pixels before the
-        // plane's first row or after its last one, and channels >= C, are out of bounds and read as zero. (A box
-        // whose inner extent is below the 128-byte swizzle span would be padded to 128 bytes per inner row in
-        // shared memory, so the (W, H) plane is never used as two tensor-map dimensions here.)
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)Cin * IH * IW * 4};
-        uint32_t box[3] = {32u, (uint32_t)kCB, 1u};
-        rc = encode_tmap(ctx, &tmIn, X, 3, dims, str, box, nullptr, 129);
-        if (rc != CB_OK) return rc;
+    int rc;
+    const uint64_t plane = (uint64_t)IH * IW;
+    if (q.shared_rows) {
+        // 32-wide maps: (w, channel, row, image) so that one box of FH+3 rows lands as [row][channel][128 B]
+        uint64_t dims[4] = {32, (uint64_t)q.Cin, (uint64_t)IH, (uint64_t)N};
+        uint64_t str[3] = {plane * 4, 128, (uint64_t)q.Cin * plane * 4};
+        uint32_t box[4] = {32u, (uint32_t)(q.KS * kCB), (uint32_t)q.nblocks, 1u};
+        rc = encode_tmap(err_ctx, &tmIn, X, 4, dims, str, box, nullptr, 129);
+    } else {
+        // planes flattened to (H*W, C, N): a box is 32 consecutive floats of 8*KS channel planes, starting at pixel
+        // (row * W) — a multiple of 4 floats, as TMA requires of the innermost coordinate. Pixels before the plane's
+        // first row or after its last one, and channels >= C, are out of bounds and read as zero. (A box whose inner
+        // extent is below the 128-byte swizzle span would be padded to 128 bytes per inner row in shared memory, so
+        // the (W, H) plane is never used as two tensor-map dimensions when W < 32.)
+        uint64_t dims[3] = {plane, (uint64_t)q.Cin, (uint64_t)N};
+        uint64_t str[2] = {plane * 4, (uint64_t)q.Cin * plane * 4};
+        uint32_t box[3] = {32u, (uint32_t)(q.KS * kCB), 1u};
+        rc = encode_tmap(err_ctx, &tmIn, X, 3, dims, str, box, nullptr, 129);
     }
+    if (rc != CB_OK) return rc;
     {
-        const uint64_t rows = (uint64_t)FH * CG * NQ;
+        const uint64_t rows = (uint64_t)FH * q.CG * q.NQ;
         uint64_t dims[3] = {32, rows, 1};
         uint64_t str[2] = {128, rows * 128};
-        uint32_t box[3] = {32, (uint32_t)NQ, 1};
-        rc = encode_tmap(ctx, &tmW, Wp, 3, dims, str, box, nullptr, 128);
+        uint32_t box[3] = {32, (uint32_t)q.NQ, 1};
+        rc = encode_tmap(err_ctx, &tmW, env.pack, 3, dims, str, box, nullptr, 128);
         if (rc != CB_OK) return rc;
     }
-    const size_t smem = w_bytes + (size_t)p.stages * stage_bytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_conv_kernel attribute");
-    const int grid = p.tiles < ctx->sm_count ? p.tiles : ctx->sm_count;
-    umma_conv_kernel<<<grid, 192, smem, ctx->stream>>>(tmIn, tmW, p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_conv_kernel launch");
-    ctx->launches += 1;
+    const size_t smem = q.w_bytes + (size_t)p.stages * q.stage_bytes + 1024;
+    static bool attr_set[64] = {};  // per device: the opt-in shared-memory size is raised to the maximum once
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
+        if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel attribute");
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    const int grid = p.tiles < env.sm_count ? p.tiles : env.sm_count;
+    umma_conv_kernel<<<grid, 192, smem, env.stream>>>(tmIn, tmW, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel launch");
+    return CB_OK;
+}
+
+}  // namespace
+
+int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
+                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of) {
+    ConvPlan q{};
+    int rc = plan_conv(q, ctx->max_smem_optin, X, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dgrad_of);
+    if (rc != CB_OK) return rc;
+    rc = ensure_workspace(ctx, q.w_bytes);
+    if (rc != CB_OK) return rc;
+    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, static_cast<float*>(ctx->workspace), ctx->d_status};
+    rc = launch_conv(ctx, env, q, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, pH, relu, dgrad_of);
+    if (rc != CB_OK) return rc;
+    ctx->launches += 2;
     ctx->last_kernel = "umma_tf32";
     return CB_OK;
 }
@@ -728,16 +789,12 @@ extern "C" int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W
         return noalloc_fail(err, err_len, CB_EUNSUPPORTED,
                             "cb_conv_fwd_noalloc covers stride 1, 1x1 (pad 0) / 3x3 (pad 1) filters, map width 8, 16 or 32 "
                             "and a 16-byte aligned input");
-    const int L = 32 / IW;
-    const int OCp = (OC + 15) / 16 * 16;
-    const int NQ = FW * OCp;
-    const int CG = (IC + 31) / 32;
-    if (NQ > 256) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "FW * OC (rounded up to 16) exceeds 256");
-    const size_t w_bytes = (size_t)FH * CG * NQ * kRowBytes;
-    if (w_bytes > sizeof(float) * (size_t)kNoAllocPackFloats) {
+    const size_t w_need = (size_t)FH * ((IC + 31) / 32) * FW * ((OC + 15) / 16 * 16) * kRowBytes;
+    if (FW * ((OC + 15) / 16 * 16) > 256) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "FW * OC (rounded up to 16) exceeds 256");
+    if (w_need > sizeof(float) * (size_t)kNoAllocPackFloats) {
         char msg[200];
         snprintf(msg, sizeof(msg), "packed filter needs %zu bytes; the static scratch of cb_conv_fwd_noalloc holds %zu",
-                 w_bytes, sizeof(float) * (size_t)kNoAllocPackFloats);
+                 w_need, sizeof(float) * (size_t)kNoAllocPackFloats);
         return noalloc_fail(err, err_len, CB_EINVAL, msg);
     }
     if (N == 0) return CB_OK;
@@ -760,64 +817,15 @@ extern "C" int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W
     }
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
-    const int shared_rows = (L == 1 && IH % 4 == 0) ? 1 : 0;
-    const int nblocks = shared_rows ? FH + 3 : FH * 4;
-    const uint32_t stage_bytes = (uint32_t)nblocks * kBlockBytes;
-    long long stages = ((long long)d.smem_optin - 2048 - (long long)w_bytes) / stage_bytes;
-    if (stages < 2) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "not enough shared memory for the pipeline");
-    if (stages > kMaxStages) stages = kMaxStages;
-
+    ConvPlan q{};
+    if (plan_conv(q, d.smem_optin, X, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, false) != CB_OK)
+        return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "geometry outside the tensor-core convolution kernel");
     // the scratch keeps the previous call's contents: the pack kernel rewrites all w_bytes (padding included) and
     // the status word is cleared, both in stream order
     e = cudaMemsetAsync(d.status, 0, sizeof(int), stream);
     if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-    {
-        const long long total = (long long)w_bytes / 4;
-        int grid = (int)((total + 255) / 256);
-        if (grid > d.sm_count * 8) grid = d.sm_count * 8;
-        pack_filter_kernel<<<grid, 256, 0, stream>>>(W, d.pack, OC, IC, FH, FW, OCp, CG, 0, total);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-    }
-    ConvParams p{};
-    p.N = N; p.Cin = IC; p.H = IH; p.W = IW; p.Cout = OC;
-    p.FH = FH; p.FW = FW; p.pH = pH;
-    p.OCp = OCp; p.NQ = NQ; p.CG = CG; p.NCB = (IC + kCB - 1) / kCB;
-    p.L = L; p.LPI = IH / L;
-    p.shared_rows = shared_rows; p.nblocks = nblocks;
-    p.total_lines = (long long)N * p.LPI;
-    p.tiles = (int)((p.total_lines + 3) / 4);
-    p.stages = (int)stages;
-    int cols = 32;
-    while (cols < 2 * NQ) cols <<= 1;
-    p.tmem_cols = cols;
-    p.w_bytes = (uint32_t)w_bytes;
-    p.stage_bytes = stage_bytes;
-    p.Out = Y; p.bias = bias; p.relu = relu;
-    p.status = d.status;
-
-    CUtensorMap tmIn, tmW;
-    {
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)IC, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)IC * IH * IW * 4};
-        uint32_t box[3] = {32u, (uint32_t)kCB, 1u};
-        if (encode_tmap(nullptr, &tmIn, X, 3, dims, str, box, nullptr, 129) != CB_OK)
-            return noalloc_fail(err, err_len, CB_ECUDA, "tensor map encoding failed (input)");
-    }
-    {
-        const uint64_t rows = (uint64_t)FH * CG * NQ;
-        uint64_t dims[3] = {32, rows, 1};
-        uint64_t str[2] = {128, rows * 128};
-        uint32_t box[3] = {32, (uint32_t)NQ, 1};
-        if (encode_tmap(nullptr, &tmW, d.pack, 3, dims, str, box, nullptr, 128) != CB_OK)
-            return noalloc_fail(err, err_len, CB_ECUDA, "tensor map encoding failed (filter)");
-    }
-    const size_t smem = w_bytes + (size_t)p.stages * stage_bytes + 1024;
-    e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-    const int grid = p.tiles < d.sm_count ? p.tiles : d.sm_count;
-    umma_conv_kernel<<<grid, 192, smem, stream>>>(tmIn, tmW, p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    ConvEnv env{stream, d.sm_count, d.smem_optin, d.pack, d.status};
+    if (launch_conv(nullptr, env, q, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, pH, relu, false) != CB_OK)
+        return noalloc_fail(err, err_len, CB_ECUDA, "kernel launch or tensor map encoding failed");
     return CB_OK;
 }

@@ -402,6 +402,13 @@ float* cbt_tensor_ptr(cbt_model* m, int id, int grad) {
     return grad ? m->t[id].d : m->t[id].a;
 }
 float* cbt_loss_ptr(cbt_model* m) { return m ? m->loss_dev : nullptr; }
+// Copies the summed loss word of the last forward pass to a caller-owned device float, in stream order.
+int cbt_copy_loss(cbt_model* m, float* dst) {
+    if (!m || !dst) return CB_EINVAL;
+    cudaError_t e = cudaMemcpyAsync(dst, m->loss_dev, sizeof(float), cudaMemcpyDeviceToDevice, m->ctx->stream);
+    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    return CB_OK;
+}
 // Copies n floats of a tensor (see cbt_tensor_ptr) into the caller's device buffer, in stream order.
 int cbt_copy_tensor(cbt_model* m, int id, int grad, float* dst, long long n) {
     float* src = cbt_tensor_ptr(m, id, grad);

@@ -29,6 +29,7 @@ TRAIN_SIGNATURES = {
     "cbt_tensor_ptr": (C.c_void_p, [C.c_void_p, _i, _i]),
     "cbt_loss_ptr": (C.c_void_p, [C.c_void_p]),
     "cbt_copy_tensor": (_i, [C.c_void_p, _i, _i, _f, _ll]),
+    "cbt_copy_loss": (_i, [C.c_void_p, _f]),
 }
 KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
 
@@ -124,6 +125,34 @@ class ResNetTrainer:
         self.backward()
         self.allreduce_grads()
         self.update(lr, beta, l2)
+
+    # ---- whole step as one CUDA graph (launch-bound otherwise: ~700 kernels per ResNet-56 step)
+    def capture_step(self, images, labels_onehot, lr, beta=0.9, l2=1e-4, warmup=2, include_allreduce=True):
+        """Runs `warmup` eager steps (workspace growth, NCCL set-up), then records forward + backward
+        (+ gradient allreduce) + update into a torch.cuda.CUDAGraph that reads the given static input tensors.
+        Returns the graph; call .replay() after refreshing images / labels in place."""
+        for _ in range(warmup):
+            self.step(images, labels_onehot, lr, beta, l2)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        old = self.ctx._stream
+        with torch.cuda.graph(graph):
+            cap = torch.cuda.current_stream(self.ctx.device)
+            self.ctx._check(self.ctx.lib.cb_set_stream(self.ctx.h, C.c_void_p(cap.cuda_stream)))
+            self.forward(images, labels_onehot)
+            self.backward()
+            if include_allreduce:
+                self.allreduce_grads()
+            self.update(lr, beta, l2)
+        self.ctx._check(self.ctx.lib.cb_set_stream(self.ctx.h, C.c_void_p(old.cuda_stream)))
+        torch.cuda.synchronize()
+        return graph
+
+    def loss_tensor(self) -> torch.Tensor:
+        """One-element device tensor holding a copy of the summed loss of the last forward pass."""
+        out = torch.empty(1, device=self.params.device)
+        self._check(self.lib.cbt_copy_loss(self.h, out.data_ptr()))
+        return out
 
     def loss(self) -> float:
         v = _fl()

@@ -46,6 +46,7 @@ int cbt_loss(cbt_model* m, float* loss_mean);
 /* Device pointers for tests: value (grad = 0) / gradient (grad = 1) of tensor id; -1 = logits, -2 = softmax. */
 float* cbt_tensor_ptr(cbt_model* m, int id, int grad);
 float* cbt_loss_ptr(cbt_model* m);
+int cbt_copy_loss(cbt_model* m, float* dst);
 int cbt_copy_tensor(cbt_model* m, int id, int grad, float* dst, long long n);
 
 #ifdef __cplusplus
