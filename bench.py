@@ -238,6 +238,11 @@ def bench_ours(args):
             "tflops_by_shape": detail,
         }
         line["cpu_baseline"] = None if args.no_cpu else cpu_baseline_leg()
+        if not args.no_cpu and world == 1:
+            try:
+                line["reference_cuda"] = reference_cuda_leg()
+            except Exception as exc:
+                line["reference_cuda"] = {"error": str(exc)[:200]}
     extra_conv = None
     if not args.shapes or args.conv_shapes:
         only = set(args.conv_shapes.split(",")) if args.conv_shapes else None
@@ -404,6 +409,56 @@ def cpu_baseline_leg():
         reps += 1
     return {"value": round(flops(CPU_SAMPLE) * reps / total / 1e12, 4), "unit": "TFLOP/s",
             "cores": orc.num_threads(), "kind": "port", "sample": f"{SAMPLE_TEXT}, {reps} passes"}
+
+
+def reference_cuda_leg():
+    """The reference's OWN CUDA kernels (seblas sgemm / conv / convDerive / convError, rebuilt for sm_100a into
+    oracle/_ref/libseblas_ref.so) timed on the same GPU, as a second baseline beside the CPU port. Each seblas call
+    ends in its own cudaDeviceSynchronize, so host wall-clock around the call is the reference's latency as its
+    operands see it. Returns None when the library was not built (the reference tree was not mounted at build time)."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libseblas_ref.so")
+    if not os.path.exists(path):
+        return None
+    import torch
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as exc:
+        return {"error": str(exc)[:200]}
+    out = {}
+
+    def timed(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return sorted(ts)[len(ts) // 2]
+
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    for n in (1024, 2048, 4096):
+        A = torch.rand(n, n, device="cuda") * 2 - 1
+        B = torch.rand(1, n, n, device="cuda") * 2 - 1
+        Cc = torch.zeros(1, n, n, device="cuda")
+        for form, name in ((0, "NN"), (1, "TN")):
+            dt = timed(lambda: lib.ref_gemm(form, p(A), p(B), p(Cc), n, n, n, 1))
+            out[f"sgemm_{n}_{name}_tflops"] = round(2.0 * n ** 3 / dt / 1e12, 2)
+    N, IC, H, OC = 128, 64, 32, 64
+    X = torch.randn(N, IC, H, H, device="cuda")
+    W = torch.randn(OC, IC, 3, 3, device="cuda") * 0.06
+    Y = torch.zeros(N, OC, H, H, device="cuda")
+    dX = torch.zeros_like(X)
+    dW = torch.zeros_like(W)
+    geo = (N, IC, H, H, OC, 3, 3, 1, 1, 1, 1)
+    fl = 2.0 * N * OC * H * H * IC * 9
+    out["conv_c3_fwd_us"] = round(timed(lambda: lib.ref_conv(p(W), p(X), p(Y), None, *geo)) * 1e6, 1)
+    out["conv_c3_dgrad_us"] = round(timed(lambda: lib.ref_conv_derive(p(W), p(Y), p(dX), *geo)) * 1e6, 1)
+    out["conv_c3_wgrad_us"] = round(timed(lambda: lib.ref_conv_error(p(Y), p(X), p(dW), *geo), reps=3) * 1e6, 1)
+    out["conv_c3_fwd_tflops"] = round(fl / out["conv_c3_fwd_us"] / 1e6, 2)
+    out["note"] = "reference seblas kernels (fp32 FFMA, sm_86 design) rebuilt for sm_100a; times include their own device sync"
+    return out
 
 
 def bench_reference(args):

@@ -37,7 +37,7 @@ constexpr int kRowBytes = 128;  // one line of 32 floats
 
 struct ConvParams {
     int N, Cin, H, W, Cout;   // "input" and "output" of this pass (forward: X -> Y, dgrad: dY -> dX)
-    int FH, FW, pH;           // vertical taps, horizontal taps, vertical padding
+    int FH, FW, pH, pW;       // taps and padding: tap (fh, fw) reads the input at offset (fh - pH, fw - pW), each in [-1, 1]
     int OCp;                  // Cout rounded up to 16
     int NQ;                   // UMMA N = FW * OCp
     int CG;                   // 32-channel groups of the packed filter
@@ -222,26 +222,32 @@ __global__ void __launch_bounds__(192, 1)
             float* out = p.Out + ((long long)n * p.Cout * p.H + h0) * p.W + lane;
             const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
             for (int c = 0; c < p.OCp; c += 16) {
-                uint32_t r1[16];
                 float v[16];
-                if (p.FW == 3) {
-                    uint32_t r0[16], r2[16];
-                    tmem_ld16(t_row + (uint32_t)c, r0);
-                    tmem_ld16(t_row + (uint32_t)(p.OCp + c), r1);
-                    tmem_ld16(t_row + (uint32_t)(2 * p.OCp + c), r2);
-                    tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        // tap fw = 0 reads column ow - 1: its partial sum sits one lane to the left; fw = 2 one to the right
-                        const float l = __shfl_up_sync(0xffffffffu, __uint_as_float(r0[e]), 1);
-                        const float rr = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[e]), 1);
-                        v[e] = __uint_as_float(r1[e]) + (has_left ? l : 0.f) + (has_right ? rr : 0.f);
+                for (int e = 0; e < 16; ++e) v[e] = 0.f;
+                // horizontal tap fw was accumulated at the unshifted pixel; it reads column ow + (fw - pW), so its
+                // partial sum sits (fw - pW) lanes away. Lanes that would read across a row edge take zero (padding).
+                for (int fw = 0; fw < p.FW; ++fw) {
+                    uint32_t r[16];
+                    tmem_ld16(t_row + (uint32_t)(fw * p.OCp + c), r);
+                    tmem_ld_wait();
+                    const int d = fw - p.pW;  // warp-uniform
+                    if (d == 0) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[e] += __uint_as_float(r[e]);
+                    } else if (d < 0) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(r[e]), 1);
+                            v[e] += has_left ? up : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(r[e]), 1);
+                            v[e] += has_right ? dn : 0.f;
+                        }
                     }
-                } else {
-                    tmem_ld16(t_row + (uint32_t)c, r1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r1[e]);
                 }
                 if (valid) {
 #pragma unroll
@@ -269,29 +275,115 @@ __global__ void __launch_bounds__(192, 1)
     }
 }
 
-// Packs the filter for the kernel above. Row index = ((fh * CG + cg) * FW + fw) * OCp + o, 32 floats per row.
-//   forward:  row[c] = W[o][cg*32 + c][fh][fw]                 (W is OC x IC x FH x FW)
-//   dgrad:    row[c] = W[cg*32 + c][o][FH-1-fh][FW-1-fw]       (o = input channel of the convolution)
-__global__ void pack_filter_kernel(const float* __restrict__ W, float* __restrict__ Wp, int OC, int IC, int FH, int FW,
-                                   int OCp, int CG, int dgrad, long long total) {
+// Source filter tap of the stride-2 convolution that lands on (input phase, tap of the 2x2 phase convolution):
+// with ih = 2 oh + fh - 1, tap fh = 0 reads phase 1 at row oh - 1, fh = 1 phase 0 at row oh, fh = 2 phase 1 at row oh.
+__device__ __forceinline__ int s2_tap(int phase, int t) { return phase == 1 ? (t == 0 ? 0 : 2) : (t == 1 ? 1 : -1); }
+
+enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3 };
+
+// Packs the filter for the kernel above. Row index = ((fh * CG + cg) * FWc + fw) * OCp + o, 32 floats per row; W is the
+// caller's OC x IC x FHs x FWs filter, (FHc, FWc) the taps of the convolution the kernel runs.
+//   PACK_FWD:      row[c] = W[o][cg*32 + c][fh][fw]
+//   PACK_DGRAD:    row[c] = W[cg*32 + c][o][FH-1-fh][FW-1-fw]          (o = input channel of the convolution)
+//   PACK_S2_FWD:   the stride-2 3x3 convolution as a 2x2 convolution over the 4 input phases stacked as channels
+//                  c' = phase*IC + c: row[c'] = W[o][c][s2_tap(ph, fh)][s2_tap(pw, fw)] (zero where no tap lands)
+//   PACK_S2_DGRAD: its adjoint: input channels are the OC planes of dY, output o' = out_first + o indexes (phase, c),
+//                  taps flipped: row[oc] = W[oc][c][s2_tap(ph, 1-fh)][s2_tap(pw, 1-fw)]
+__global__ void pack_filter_kernel(const float* __restrict__ W, float* __restrict__ Wp, int OC, int IC, int FHs, int FWs,
+                                   int FHc, int FWc, int OCp, int CG, int mode, int out_first, int out_count,
+                                   long long total) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int c = (int)(i & 31);
         long long r = i >> 5;
         const int o = (int)(r % OCp);
         r /= OCp;
-        const int fw = (int)(r % FW);
-        r /= FW;
+        const int fw = (int)(r % FWc);
+        r /= FWc;
         const int cg = (int)(r % CG);
         const int fh = (int)(r / CG);
         const int ch = cg * 32 + c;
         float v = 0.f;
-        if (!dgrad) {
-            if (o < OC && ch < IC) v = W[(((long long)o * IC + ch) * FH + fh) * FW + fw];
+        if (mode == PACK_FWD) {
+            if (o < OC && ch < IC) v = W[(((long long)o * IC + ch) * FHs + fh) * FWs + fw];
+        } else if (mode == PACK_DGRAD) {
+            if (o < IC && ch < OC) v = W[(((long long)ch * IC + o) * FHs + (FHs - 1 - fh)) * FWs + (FWs - 1 - fw)];
+        } else if (mode == PACK_S2_FWD) {
+            if (o < OC && ch < 4 * IC) {
+                const int phase = ch / IC, cc = ch - phase * IC;
+                const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
+                if (sh >= 0 && sw >= 0) v = W[(((long long)o * IC + cc) * FHs + sh) * FWs + sw];
+            }
         } else {
-            if (o < IC && ch < OC) v = W[(((long long)ch * IC + o) * FH + (FH - 1 - fh)) * FW + (FW - 1 - fw)];
+            if (o < out_count && ch < OC) {
+                const int og = out_first + o;
+                const int phase = og / IC, cc = og - phase * IC;
+                const int sh = s2_tap(phase >> 1, 1 - fh), sw = s2_tap(phase & 1, 1 - fw);
+                if (sh >= 0 && sw >= 0) v = W[(((long long)ch * IC + cc) * FHs + sh) * FWs + sw];
+            }
         }
         Wp[i] = v;
+    }
+}
+
+// ---- re-layout kernels of the stride-2 path (memory-bound, one element per thread, coalesced on the write side)
+// Xs[n][phase*C + c][i][j] = X[n][c][2i + (phase >> 1)][2j + (phase & 1)]
+__global__ void space_to_depth2_kernel(const float* __restrict__ X, float* __restrict__ Xs, int C, int H, int W,
+                                       long long total) {
+    const int H2 = H / 2, W2 = W / 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % W2);
+        long long r = i / W2;
+        const int ii = (int)(r % H2);
+        r /= H2;
+        const int cp = (int)(r % (4 * C));
+        const long long n = r / (4 * C);
+        const int phase = cp / C, c = cp - phase * C;
+        Xs[i] = X[((n * C + c) * H + 2 * ii + (phase >> 1)) * W + 2 * j + (phase & 1)];
+    }
+}
+// dX[n][c][y][x] = dXs[group][n][o][y/2][x/2] with phase*C + c = group*per_group + o
+__global__ void depth_to_space2_kernel(const float* __restrict__ dXs, float* __restrict__ dX, int N, int C, int H, int W,
+                                       int per_group, long long total) {
+    const int H2 = H / 2, W2 = W / 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int x = (int)(i % W);
+        long long r = i / W;
+        const int y = (int)(r % H);
+        r /= H;
+        const int c = (int)(r % C);
+        const long long n = r / C;
+        const int og = ((y & 1) * 2 + (x & 1)) * C + c;
+        const int g = og / per_group, o = og - g * per_group;
+        dX[i] = dXs[((((long long)g * N + n) * per_group + o) * H2 + (y >> 1)) * W2 + (x >> 1)];
+    }
+}
+// Xsub[nc][i][j] = X[nc][2i][2j]
+__global__ void subsample2_kernel(const float* __restrict__ X, float* __restrict__ Xsub, long long NC, int H, int W,
+                                  long long total) {
+    const int H2 = H / 2, W2 = W / 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int j = (int)(i % W2);
+        const long long r = i / W2;
+        const int ii = (int)(r % H2);
+        const long long nc = r / H2;
+        Xsub[i] = X[(nc * H + 2 * ii) * W + 2 * j];
+    }
+}
+// dX[nc][y][x] = (y, x both even) ? dXsub[nc][y/2][x/2] : 0
+__global__ void upsample2_zero_kernel(const float* __restrict__ dXsub, float* __restrict__ dX, int H, int W,
+                                      long long total) {
+    const int H2 = H / 2, W2 = W / 2;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int x = (int)(i % W);
+        const long long r = i / W;
+        const int y = (int)(r % H);
+        const long long nc = r / H;
+        dX[i] = ((x | y) & 1) ? 0.f : dXsub[(nc * H2 + (y >> 1)) * W2 + (x >> 1)];
     }
 }
 
@@ -311,17 +403,16 @@ struct ConvPlan {
     uint32_t block_bytes, stage_bytes;
 };
 
-static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int IC, int IH, int IW, int OC, int FH, int FW, int sH,
-                     int sW, int pH, int pW, bool dgrad_of) {
-    if (sH != 1 || sW != 1) return CB_EUNSUPPORTED;
-    if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
-    if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int Cin, int Cout, int IH, int IW, int FH, int FW,
+                     int pH, int pW) {
+    // every tap must read within one pixel of the output position: offsets fh - pH and fw - pW in [-1, 1]
+    if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
+    if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
     if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
     q.L = 32 / IW;
     if (IH % q.L) return CB_EUNSUPPORTED;
-    // roles: forward reads X (IC channels) and writes OC planes; the data gradient reads dY (OC) and writes IC
-    q.Cin = dgrad_of ? OC : IC;
-    q.Cout = dgrad_of ? IC : OC;
+    q.Cin = Cin;
+    q.Cout = Cout;
     q.OCp = (q.Cout + 15) / 16 * 16;
     q.NQ = FW * q.OCp;
     if (q.NQ > 256 || q.Cin < 1) return CB_EUNSUPPORTED;
@@ -349,21 +440,28 @@ static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int IC, int IH
     return CB_OK;
 }
 
-// Packs the filter into env.pack and launches the kernel. `err_ctx` may be null (allocation-free entry point).
-static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const float* W, const float* X, float* Y,
-                       const float* bias, int N, int IC, int IH, int IW, int OC, int FH, int FW, int pH, int relu,
-                       bool dgrad_of) {
+// How the caller's filter becomes the packed filter of the convolution the kernel runs.
+struct PackSpec {
+    int mode, OC, IC, FHs, FWs, out_first, out_count;
+};
+
+// Packs the filter into env.pack and launches the kernel: Y (N x q.Cout x IH x IW) = taps (FH, FW, pH, pW) over
+// X (N x q.Cin x IH x IW). `err_ctx` may be null (allocation-free entry point).
+static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const PackSpec& ps, const float* W,
+                       const float* X, float* Y, const float* bias, int N, int IH, int IW, int FH, int FW, int pH, int pW,
+                       int relu) {
     {
         const long long total = (long long)q.w_bytes / 4;
         int grid = (int)((total + 255) / 256);
         if (grid > env.sm_count * 8) grid = env.sm_count * 8;
-        pack_filter_kernel<<<grid, 256, 0, env.stream>>>(W, env.pack, OC, IC, FH, FW, q.OCp, q.CG, dgrad_of ? 1 : 0, total);
+        pack_filter_kernel<<<grid, 256, 0, env.stream>>>(W, env.pack, ps.OC, ps.IC, ps.FHs, ps.FWs, FH, FW, q.OCp, q.CG,
+                                                         ps.mode, ps.out_first, ps.out_count, total);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return check_cuda(err_ctx, e, "pack_filter_kernel launch");
     }
     ConvParams p{};
     p.N = N; p.Cin = q.Cin; p.H = IH; p.W = IW; p.Cout = q.Cout;
-    p.FH = FH; p.FW = FW; p.pH = pH;
+    p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
     p.OCp = q.OCp; p.NQ = q.NQ; p.CG = q.CG; p.KS = q.KS;
     p.NCB = (q.Cin + q.KS * kCB - 1) / (q.KS * kCB);
     p.L = q.L; p.LPI = IH / q.L;
@@ -429,15 +527,112 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
 
 int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
                   int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of) {
+    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, nullptr, ctx->d_status};
     ConvPlan q{};
-    int rc = plan_conv(q, ctx->max_smem_optin, X, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dgrad_of);
+    int rc;
+    if (sH == 1 && sW == 1) {
+        // ---- stride 1: 1x1 (pad 0) or 3x3 (pad 1) per axis
+        if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
+        if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+        rc = plan_conv(q, ctx->max_smem_optin, X, dgrad_of ? OC : IC, dgrad_of ? IC : OC, IH, IW, FH, FW, pH, pW);
+        if (rc != CB_OK) return rc;
+        rc = ensure_workspace(ctx, q.w_bytes);
+        if (rc != CB_OK) return rc;
+        env.pack = static_cast<float*>(ctx->workspace);
+        const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, FH, FW, 0, 0};
+        rc = launch_conv(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
+        if (rc != CB_OK) return rc;
+        ctx->launches += 2;
+        ctx->last_kernel = "umma_tf32";
+        return CB_OK;
+    }
+    // ---- stride 2 (square): 3x3 pad 1 through the 4 input phases, 1x1 pad 0 through phase (0,0)
+    if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
+    if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;
+    const int H2 = IH / 2, W2 = IW / 2;
+    const long long plane2 = (long long)H2 * W2;
+    const int launch_threads = 256;
+    auto grid_of = [&](long long n) {
+        long long g = (n + launch_threads - 1) / launch_threads;
+        const long long cap = (long long)ctx->sm_count * 16;
+        return (int)(g > cap ? cap : (g < 1 ? 1 : g));
+    };
+    if (FH == 1) {
+        // Y = W * X[:, :, ::2, ::2]  /  dX[:, :, ::2, ::2] = W^T dY, zero elsewhere
+        rc = plan_conv(q, ctx->max_smem_optin, dgrad_of ? X : nullptr /* the sub-sampled copy is aligned */, dgrad_of ? OC : IC,
+                       dgrad_of ? IC : OC, H2, W2, 1, 1, 0, 0);
+        if (rc != CB_OK) return rc;
+        const size_t sub_bytes = (size_t)N * IC * plane2 * sizeof(float);
+        rc = ensure_workspace2(ctx, sub_bytes);
+        if (rc == CB_OK) rc = ensure_workspace(ctx, q.w_bytes);
+        if (rc != CB_OK) return rc;
+        env.pack = static_cast<float*>(ctx->workspace);
+        float* sub = static_cast<float*>(ctx->workspace2);
+        const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, 1, 1, 0, 0};
+        const long long n_sub = (long long)N * IC * plane2;
+        if (!dgrad_of) {
+            subsample2_kernel<<<grid_of(n_sub), launch_threads, 0, ctx->stream>>>(X, sub, (long long)N * IC, IH, IW, n_sub);
+            rc = launch_conv(ctx, env, q, ps, W, sub, Y, bias, N, H2, W2, 1, 1, 0, 0, relu);
+        } else {
+            rc = launch_conv(ctx, env, q, ps, W, X /* = dY */, sub, nullptr, N, H2, W2, 1, 1, 0, 0, 0);
+            const long long n_full = (long long)N * IC * IH * IW;
+            if (rc == CB_OK)
+                upsample2_zero_kernel<<<grid_of(n_full), launch_threads, 0, ctx->stream>>>(sub, Y /* = dX */, IH, IW, n_full);
+        }
+        if (rc != CB_OK) return rc;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return check_cuda(ctx, e, "stride-2 1x1 convolution");
+        ctx->launches += 3;
+        ctx->last_kernel = "umma_tf32";
+        return CB_OK;
+    }
+    const int C4 = 4 * IC;
+    const size_t s2d_bytes = (size_t)N * C4 * plane2 * sizeof(float);
+    if (!dgrad_of) {
+        // Xs[n][phase*IC + c] = X[n][c][phase rows / cols]; Y = 2x2 convolution (taps at -1, 0) over the 4*IC planes
+        rc = ensure_workspace2(ctx, s2d_bytes);
+        if (rc != CB_OK) return rc;
+        float* Xs = static_cast<float*>(ctx->workspace2);
+        rc = plan_conv(q, ctx->max_smem_optin, Xs, C4, OC, H2, W2, 2, 2, 1, 1);
+        if (rc != CB_OK) return rc;
+        rc = ensure_workspace(ctx, q.w_bytes);
+        if (rc != CB_OK) return rc;
+        env.pack = static_cast<float*>(ctx->workspace);
+        const long long n_el = (long long)N * C4 * plane2;
+        space_to_depth2_kernel<<<grid_of(n_el), launch_threads, 0, ctx->stream>>>(X, Xs, IC, IH, IW, n_el);
+        const PackSpec ps{PACK_S2_FWD, OC, IC, 3, 3, 0, 0};
+        rc = launch_conv(ctx, env, q, ps, W, Xs, Y, bias, N, H2, W2, 2, 2, 1, 1, relu);
+        if (rc != CB_OK) return rc;
+        ctx->launches += 3;
+        ctx->last_kernel = "umma_tf32";
+        return CB_OK;
+    }
+    // data gradient: dXs (4*IC phase planes) = adjoint 2x2 convolution (taps at 0, +1) over dY, in channel groups small
+    // enough for the accumulator (FW * roundup16(channels) <= 256), then interleaved back into dX
+    int groups = 1;
+    while (groups <= 4 && 2 * ((C4 / groups + 15) / 16 * 16) > 256) groups *= 2;
+    if (groups > 4) return CB_EUNSUPPORTED;
+    const int per_group = C4 / groups;
+    rc = ensure_workspace2(ctx, s2d_bytes);
+    if (rc != CB_OK) return rc;
+    float* dXs = static_cast<float*>(ctx->workspace2);
+    rc = plan_conv(q, ctx->max_smem_optin, X /* = dY */, OC, per_group, H2, W2, 2, 2, 0, 0);
     if (rc != CB_OK) return rc;
     rc = ensure_workspace(ctx, q.w_bytes);
     if (rc != CB_OK) return rc;
-    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, static_cast<float*>(ctx->workspace), ctx->d_status};
-    rc = launch_conv(ctx, env, q, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, pH, relu, dgrad_of);
-    if (rc != CB_OK) return rc;
-    ctx->launches += 2;
+    env.pack = static_cast<float*>(ctx->workspace);
+    for (int g = 0; g < groups; ++g) {
+        const PackSpec ps{PACK_S2_DGRAD, OC, IC, 3, 3, g * per_group, per_group};
+        rc = launch_conv(ctx, env, q, ps, W, X /* = dY */, dXs + (size_t)g * N * per_group * plane2, nullptr, N, H2, W2, 2, 2,
+                         0, 0, 0);
+        if (rc != CB_OK) return rc;
+    }
+    const long long n_full = (long long)N * IC * IH * IW;
+    depth_to_space2_kernel<<<grid_of(n_full), launch_threads, 0, ctx->stream>>>(dXs, Y /* = dX */, N, IC, IH, IW, per_group,
+                                                                                 n_full);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "depth_to_space2_kernel launch");
+    ctx->launches += 2 * groups + 1;
     ctx->last_kernel = "umma_tf32";
     return CB_OK;
 }
@@ -457,7 +652,7 @@ namespace {
 // writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
 struct WgradParams {
     int N, Cin, H, W, OC;
-    int FH, FW, pH;
+    int FH, FW, pH, pW;
     int Cp, OCp, NQ, mtiles, rowsA;  // rowsA = FH * Cp valid accumulator rows
     int L, LPI;
     long long total_lines;
@@ -481,8 +676,10 @@ __device__ __forceinline__ uint32_t sw128_chunk(uint32_t row_addr, int q) {
     return row_addr + ((((uint32_t)q) ^ ((row_addr >> 7) & 7u)) << 4);
 }
 
+// Builds the horizontally shifted copies of one dY row: row_m1 (tap offset -1: pairs X[px] with dY[px + 1]) and
+// row_p1 (tap offset +1: pairs X[px] with dY[px - 1]); an address of 0 skips that copy.
 template <int W>
-__device__ __forceinline__ void shift_dy_row(uint32_t src_row, uint32_t set0_row, uint32_t set2_row) {
+__device__ __forceinline__ void shift_dy_row(uint32_t src_row, uint32_t row_m1, uint32_t row_p1) {
     float v[32];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -497,15 +694,17 @@ __device__ __forceinline__ void shift_dy_row(uint32_t src_row, uint32_t set0_row
         for (int e = 0; e < 4; ++e) {
             const int x = 4 * q + e;
             const int col = x % W;
-            a[e] = (col < W - 1) ? v[(x + 1) & 31] : 0.f;  // fw = 0: pairs X[px] with dY[px + 1]
-            b[e] = (col >= 1) ? v[(x + 31) & 31] : 0.f;    // fw = 2: pairs X[px] with dY[px - 1]
+            a[e] = (col < W - 1) ? v[(x + 1) & 31] : 0.f;
+            b[e] = (col >= 1) ? v[(x + 31) & 31] : 0.f;
         }
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(set0_row, q)), "f"(a[0]), "f"(a[1]),
-                     "f"(a[2]), "f"(a[3])
-                     : "memory");
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(set2_row, q)), "f"(b[0]), "f"(b[1]),
-                     "f"(b[2]), "f"(b[3])
-                     : "memory");
+        if (row_m1)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_m1, q)), "f"(a[0]), "f"(a[1]),
+                         "f"(a[2]), "f"(a[3])
+                         : "memory");
+        if (row_p1)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_p1, q)), "f"(b[0]), "f"(b[1]),
+                         "f"(b[2]), "f"(b[3])
+                         : "memory");
     }
 }
 
@@ -519,7 +718,7 @@ __global__ void __launch_bounds__(320, 1)
     volatile int* abort_flag = &ws.abort_flag;
     const uint32_t st_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t set_bytes = (uint32_t)p.OCp * kRowBytes;
-    const int centre = p.FW >> 1;
+    const int centre = p.pW;  // (fw, oc) rows of the N side: the unshifted copy is the tap with fw - pW == 0
 
     if (threadIdx.x == 0) {
         ws.abort_flag = 0;
@@ -631,9 +830,12 @@ __global__ void __launch_bounds__(320, 1)
                 if (!ok) break;
                 if (t < p.OCp) {
                     const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)t * kRowBytes;
-                    if (p.W == 32) shift_dy_row<32>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
-                    else if (p.W == 16) shift_dy_row<16>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
-                    else shift_dy_row<8>(b0 + set_bytes, b0, b0 + 2u * set_bytes);
+                    const uint32_t src = b0 + (uint32_t)centre * set_bytes;
+                    const uint32_t m1 = centre >= 1 ? src - set_bytes : 0u;             // tap fw = pW - 1
+                    const uint32_t p1 = centre + 1 < p.FW ? src + set_bytes : 0u;       // tap fw = pW + 1
+                    if (p.W == 32) shift_dy_row<32>(src, m1, p1);
+                    else if (p.W == 16) shift_dy_row<16>(src, m1, p1);
+                    else shift_dy_row<8>(src, m1, p1);
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&ws.xf[s]));
@@ -651,8 +853,10 @@ __global__ void __launch_bounds__(320, 1)
 }
 
 // dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
+// s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
 __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW, int nparts, int rows_tot,
-                                    int rowsA, int NQ, int Cp, int Cin, int OC, int OCp, int FH, int FW, int accumulate) {
+                                    int rowsA, int NQ, int Cp, int Cin, int OC, int OCp, int FH, int FW, int accumulate,
+                                    int s2, int IC_src) {
     const long long total = (long long)rowsA * NQ;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -661,25 +865,36 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __
         const int fh = r / Cp, c = r - fh * Cp;
         const int fw = col / OCp, oc = col - fw * OCp;
         if (c >= Cin || oc >= OC) continue;
+        float* dst;
+        if (!s2) {
+            dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+        } else {
+            const int phase = c / IC_src, cc = c - phase * IC_src;
+            const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
+            if (sh < 0 || sw < 0) continue;
+            dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
+        }
         float s = 0.f;
         const float* src = partial + (long long)r * NQ + col;
-        for (int q = 0; q < nparts; ++q) s += src[(long long)q * rows_tot * NQ];
-        float* dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+        const long long pstride = (long long)rows_tot * NQ;
+#pragma unroll 8
+        for (int q = 0; q < nparts; ++q) s += __ldg(src + q * pstride);  // fixed order: deterministic
         *dst = accumulate ? *dst + s : s;
     }
 }
 
 }  // namespace
 
-int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
-    if (sH != 1 || sW != 1) return CB_EUNSUPPORTED;
-    if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
-    if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+// dW (+)= contraction over the pixels of N x Cin x IH x IW planes `X` and N x OC x IH x IW planes `dY` with taps
+// (FH, FW, pH, pW) in the same-size convention of the forward kernel. s2 / IC_src: see wgrad_reduce_kernel.
+static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int Cin, int IH, int IW, int OC, int FH,
+                      int FW, int pH, int pW, int accumulate, int s2, int IC_src) {
+    if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
+    if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
     if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
     const int L = 32 / IW;
     if (IH % L) return CB_EUNSUPPORTED;
-    const int Cp = (IC + 7) / 8 * 8;
+    const int Cp = (Cin + 7) / 8 * 8;
     const int OCp = (OC + 15) / 16 * 16;
     const int NQ = FW * OCp;
     const int rowsA = FH * Cp;
@@ -694,8 +909,8 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
     if (stages > kMaxStages) stages = kMaxStages;
 
     WgradParams p{};
-    p.N = N; p.Cin = IC; p.H = IH; p.W = IW; p.OC = OC;
-    p.FH = FH; p.FW = FW; p.pH = pH;
+    p.N = N; p.Cin = Cin; p.H = IH; p.W = IW; p.OC = OC;
+    p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
     p.Cp = Cp; p.OCp = OCp; p.NQ = NQ; p.mtiles = mtiles; p.rowsA = rowsA;
     p.L = L; p.LPI = IH / L;
     p.total_lines = (long long)N * p.LPI;
@@ -714,8 +929,8 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
 
     CUtensorMap tmX, tmdY;
     {
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)IC, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)IC * IH * IW * 4};
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)Cin * IH * IW * 4};
         uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
         rc = encode_tmap(ctx, &tmX, X, 3, dims, str, box, nullptr, 128);
         if (rc != CB_OK) return rc;
@@ -735,13 +950,49 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
     const long long total = (long long)rowsA * NQ;
     int rgrid = (int)((total + 255) / 256);
-    wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, IC, OC, OCp, FH,
-                                                         FW, accumulate ? 1 : 0);
+    wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
+                                                         accumulate ? 1 : 0, s2, IC_src);
     e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
     ctx->launches += 2;
     ctx->last_kernel = "umma_tf32";
     return CB_OK;
+}
+
+int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
+    if (sH == 1 && sW == 1) {
+        if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
+        if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+        return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC);
+    }
+    if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
+    if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;
+    const int H2 = IH / 2, W2 = IW / 2;
+    if (W2 != 8 && W2 != 16 && W2 != 32) return CB_EUNSUPPORTED;
+    const long long plane2 = (long long)H2 * W2;
+    auto grid_of = [&](long long n) {
+        long long g = (n + 255) / 256;
+        const long long cap = (long long)ctx->sm_count * 16;
+        return (int)(g > cap ? cap : (g < 1 ? 1 : g));
+    };
+    if (FH == 1) {
+        const long long n_sub = (long long)N * IC * plane2;
+        int rc = ensure_workspace2(ctx, (size_t)n_sub * sizeof(float));
+        if (rc != CB_OK) return rc;
+        float* sub = static_cast<float*>(ctx->workspace2);
+        subsample2_kernel<<<grid_of(n_sub), 256, 0, ctx->stream>>>(X, sub, (long long)N * IC, IH, IW, n_sub);
+        ctx->launches += 1;
+        return wgrad_core(ctx, dY, sub, dW, N, IC, H2, W2, OC, 1, 1, 0, 0, accumulate, 0, IC);
+    }
+    if (4 * IC > 256) return CB_EUNSUPPORTED;
+    const long long n_el = (long long)N * 4 * IC * plane2;
+    int rc = ensure_workspace2(ctx, (size_t)n_el * sizeof(float));
+    if (rc != CB_OK) return rc;
+    float* Xs = static_cast<float*>(ctx->workspace2);
+    space_to_depth2_kernel<<<grid_of(n_el), 256, 0, ctx->stream>>>(X, Xs, IC, IH, IW, n_el);
+    ctx->launches += 1;
+    return wgrad_core(ctx, dY, Xs, dW, N, 4 * IC, H2, W2, OC, 2, 2, 1, 1, accumulate, 1, IC);
 }
 
 // ------------------------------------------------------------------------------------------ allocation-free forward
@@ -818,14 +1069,15 @@ extern "C" int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
     ConvPlan q{};
-    if (plan_conv(q, d.smem_optin, X, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, false) != CB_OK)
+    if (plan_conv(q, d.smem_optin, X, IC, OC, IH, IW, FH, FW, pH, pW) != CB_OK)
         return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "geometry outside the tensor-core convolution kernel");
     // the scratch keeps the previous call's contents: the pack kernel rewrites all w_bytes (padding included) and
     // the status word is cleared, both in stream order
     e = cudaMemsetAsync(d.status, 0, sizeof(int), stream);
     if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
     ConvEnv env{stream, d.sm_count, d.smem_optin, d.pack, d.status};
-    if (launch_conv(nullptr, env, q, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, pH, relu, false) != CB_OK)
+    const PackSpec ps{PACK_FWD, OC, IC, FH, FW, 0, 0};
+    if (launch_conv(nullptr, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu) != CB_OK)
         return noalloc_fail(err, err_len, CB_ECUDA, "kernel launch or tensor map encoding failed");
     return CB_OK;
 }

@@ -20,7 +20,7 @@
 
 namespace {
 
-enum OpKind { OP_CONV, OP_BN, OP_RELU, OP_ADD, OP_GAP, OP_LINEAR, OP_SOFTMAX_CE };
+enum OpKind { OP_CONV, OP_BN, OP_RELU, OP_ADD, OP_GAP, OP_LINEAR, OP_SOFTMAX_CE, OP_CONCAT, OP_AVGPOOL };
 
 struct TensorBuf {
     int n = 0, c = 0, h = 0, w = 0;
@@ -129,6 +129,26 @@ int add_add(cbt_model* m, int a, int b) {
     return o.out;
 }
 
+// channel concatenation [in0 ; in1] (seblas concat, seblas/operations/cuConcat.cu:9-60, as ChannelConcatenater uses it)
+int add_concat(cbt_model* m, int a, int b) {
+    const TensorBuf x = m->t[a];
+    const TensorBuf y = m->t[b];
+    Op o{};
+    o.kind = OP_CONCAT; o.in0 = a; o.in1 = b;
+    o.out = new_tensor(m, x.n, x.c + y.c, x.h, x.w);
+    m->ops.push_back(o);
+    return o.out;
+}
+
+int add_avgpool2(cbt_model* m, int in) {
+    const TensorBuf x = m->t[in];
+    Op o{};
+    o.kind = OP_AVGPOOL; o.in0 = in;
+    o.out = new_tensor(m, x.n, x.c, x.h / 2, x.w / 2);
+    m->ops.push_back(o);
+    return o.out;
+}
+
 int add_gap(cbt_model* m, int in) {
     const TensorBuf x = m->t[in];
     Op o{};
@@ -160,6 +180,48 @@ int dev_alloc(cbt_model* m, float** p, long long elems) {
     m->owned.push_back(q);
     *p = static_cast<float*>(q);
     return CB_OK;
+}
+
+// Head (global average pooling, dense layer, softmax cross-entropy), gradient-accumulation flags and buffers.
+int finalize_model(cbt_model* m, int x, int classes) {
+    x = add_gap(m, x);
+    m->logits = add_linear(m, x, classes);
+    {
+        Op o{};
+        o.kind = OP_SOFTMAX_CE; o.in0 = m->logits;
+        o.out = new_tensor(m, m->batch, classes, 1, 1);
+        m->probs = o.out;
+        m->ops.push_back(o);
+    }
+    m->param_count = (m->param_count + 3) & ~3LL;
+    // activations, gradients, and the accumulate flags of tensors with two consumers
+    std::vector<int> consumers(m->t.size(), 0);
+    for (Op& o : m->ops) {
+        if (o.in0 >= 0) consumers[o.in0]++;
+        if (o.in1 >= 0) consumers[o.in1]++;
+    }
+    // in backward order the LAST forward consumer writes first; every earlier consumer must accumulate
+    std::vector<int> seen(m->t.size(), 0);
+    for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
+        Op& o = m->ops[i];
+        if (o.in0 >= 0) {
+            o.in0_grad_accumulate = seen[o.in0] > 0;
+            seen[o.in0]++;
+        }
+        if (o.in1 >= 0) seen[o.in1]++;  // OP_ADD writes its second input first (see backward)
+    }
+    long long biggest = 0;
+    for (size_t i = 0; i < m->t.size(); ++i) {
+        TensorBuf& b = m->t[i];
+        int rc = dev_alloc(m, &b.a, b.size());
+        if (rc == CB_OK && (int)i != m->input) rc = dev_alloc(m, &b.d, b.size());
+        if (rc != CB_OK) return rc;
+        if (b.size() > biggest) biggest = b.size();
+    }
+    m->scratch_elems = biggest;
+    int rc = dev_alloc(m, &m->scratch, biggest);
+    if (rc == CB_OK) rc = dev_alloc(m, &m->loss_dev, 4);
+    return rc;
 }
 
 #define CBT_TRY(expr)                                              \
@@ -197,45 +259,35 @@ int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_st
             ch = oc;
         }
     }
-    x = add_gap(m, x);
-    m->logits = add_linear(m, x, classes);
-    {
-        Op o{};
-        o.kind = OP_SOFTMAX_CE; o.in0 = m->logits;
-        o.out = new_tensor(m, batch, classes, 1, 1);
-        m->probs = o.out;
-        m->ops.push_back(o);
-    }
-    m->param_count = (m->param_count + 3) & ~3LL;
-    // activations, gradients, and the accumulate flags of tensors with two consumers
-    std::vector<int> consumers(m->t.size(), 0);
-    for (Op& o : m->ops) {
-        if (o.in0 >= 0) consumers[o.in0]++;
-        if (o.in1 >= 0) consumers[o.in1]++;
-    }
-    // in backward order the LAST forward consumer writes first; every earlier consumer must accumulate
-    std::vector<int> seen(m->t.size(), 0);
-    for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
-        Op& o = m->ops[i];
-        if (o.in0 >= 0) {
-            o.in0_grad_accumulate = seen[o.in0] > 0;
-            seen[o.in0]++;
-        }
-        if (o.in1 >= 0) seen[o.in1]++;  // OP_ADD writes its second input first (see backward)
-    }
-    long long biggest = 0;
-    for (size_t i = 0; i < m->t.size(); ++i) {
-        TensorBuf& b = m->t[i];
-        int rc = dev_alloc(m, &b.a, b.size());
-        if (rc == CB_OK && (int)i != m->input) rc = dev_alloc(m, &b.d, b.size());
-        if (rc != CB_OK) { *out = m; return rc; }
-        if (b.size() > biggest) biggest = b.size();
-    }
-    m->scratch_elems = biggest;
-    int rc = dev_alloc(m, &m->scratch, biggest);
-    if (rc == CB_OK) rc = dev_alloc(m, &m->loss_dev, 4);
     *out = m;
-    return rc;
+    return finalize_model(m, x, classes);
+}
+
+// DenseNet-BC (growth k, `layers` bottleneck layers per dense block, compression 0.5): stem 3x3 conv to 2k, three dense
+// blocks of [BN-ReLU-1x1 conv to 4k-BN-ReLU-3x3 conv to k, concatenated with the block input], transitions
+// BN-ReLU-1x1 conv-2x2 average pooling, then BN-ReLU-global average pooling-dense head (layers = 16, k = 12:
+// DenseNet-BC-100). Built from the reference's operand vocabulary (seann/operands/prefabs/DenseBlock.cuh:36-65).
+int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int layers, int image_hw, int classes) {
+    if (!out || !ctx || batch < 1 || growth < 1 || layers < 1 || image_hw < 8 || (image_hw & 3) || classes < 1) return CB_EINVAL;
+    cbt_model* m = new cbt_model();
+    m->ctx = ctx; m->batch = batch; m->classes = classes;
+    int x = new_tensor(m, batch, 3, image_hw, image_hw);
+    m->input = x;
+    x = add_conv(m, x, 2 * growth, 3, 1, 1);
+    for (int block = 0; block < 3; ++block) {
+        for (int l = 0; l < layers; ++l) {
+            int y = add_conv(m, add_relu(m, add_bn(m, x)), 4 * growth, 1, 1, 0);
+            y = add_conv(m, add_relu(m, add_bn(m, y)), growth, 3, 1, 1);
+            x = add_concat(m, x, y);
+        }
+        if (block < 2) {
+            const int ch = m->t[x].c;
+            x = add_avgpool2(m, add_conv(m, add_relu(m, add_bn(m, x)), ch / 2, 1, 1, 0));
+        }
+    }
+    x = add_relu(m, add_bn(m, x));
+    *out = m;
+    return finalize_model(m, x, classes);
 }
 
 int cbt_destroy(cbt_model* m) {
@@ -314,6 +366,18 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                 CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, y.a, m->t[o.in1].a, 0.f, y.size()));
                 break;
             }
+            case OP_CONCAT: {
+                const TensorBuf& x1 = m->t[o.in1];
+                const size_t pl = (size_t)x.h * x.w * 4;
+                e = cudaMemcpy2DAsync(y.a, (size_t)y.c * pl, x.a, (size_t)x.c * pl, (size_t)x.c * pl, x.n,
+                                      cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e == cudaSuccess)
+                    e = cudaMemcpy2DAsync(y.a + (size_t)x.c * x.h * x.w, (size_t)y.c * pl, x1.a, (size_t)x1.c * pl,
+                                          (size_t)x1.c * pl, x.n, cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                break;
+            }
+            case OP_AVGPOOL: CBT_TRY(cb_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h, x.w, 2, 2)); break;
             case OP_GAP: CBT_TRY(cb_global_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h * x.w)); break;
             case OP_LINEAR:
                 CBT_TRY(cb_linear_fwd(ctx, x.a, m->P + o.w_off, m->P + o.b_off, y.a, x.n, x.c * x.h * x.w, o.oc));
@@ -344,6 +408,19 @@ int cbt_backward(cbt_model* m) {
                 CBT_TRY(cb_linear_paramgrad(ctx, y.d, x.a, m->G + o.w_off, m->G + o.b_off, x.n, x.c * x.h * x.w, o.oc));
                 CBT_TRY(cb_linear_xgrad(ctx, y.d, m->P + o.w_off, dx, x.n, x.c * x.h * x.w, o.oc));
                 break;
+            case OP_CONCAT: {
+                // split dY: the new features (in1) take their slice directly, the carried input (in0) its own
+                TensorBuf& x1 = m->t[o.in1];
+                const size_t pl = (size_t)x.h * x.w * 4;
+                cudaError_t e = cudaMemcpy2DAsync(x1.d, (size_t)x1.c * pl, y.d + (size_t)x.c * x.h * x.w, (size_t)y.c * pl,
+                                                  (size_t)x1.c * pl, x.n, cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e == cudaSuccess)
+                    e = cudaMemcpy2DAsync(dx, (size_t)x.c * pl, y.d, (size_t)y.c * pl, (size_t)x.c * pl, x.n,
+                                          cudaMemcpyDeviceToDevice, ctx->stream);
+                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                break;
+            }
+            case OP_AVGPOOL: CBT_TRY(cb_avgpool_back(ctx, dx, y.d, (long long)x.n * x.c, x.h, x.w, 2, 2)); break;
             case OP_GAP: CBT_TRY(cb_global_avgpool_back(ctx, dx, y.d, (long long)x.n * x.c, x.h * x.w)); break;
             case OP_RELU: CBT_TRY(cb_relu_grad(ctx, x.a, y.d, dx, x.size())); break;
             case OP_ADD: {

@@ -15,6 +15,7 @@ from .api import Context, CrusaderError
 _i, _ll, _f, _fl = C.c_int, C.c_longlong, C.c_void_p, C.c_float
 TRAIN_SIGNATURES = {
     "cbt_resnet_create": (_i, [C.POINTER(C.c_void_p), C.c_void_p, _i, _i, _i, _i]),
+    "cbt_densenet_create": (_i, [C.POINTER(C.c_void_p), C.c_void_p, _i, _i, _i, _i, _i]),
     "cbt_destroy": (_i, [C.c_void_p]),
     "cbt_last_error": (C.c_char_p, [C.c_void_p]),
     "cbt_param_count": (_ll, [C.c_void_p]),
@@ -47,16 +48,19 @@ class ResNetTrainer:
     gradient allreduce."""
 
     def __init__(self, ctx: Context, batch: int, blocks_per_stage: int = 9, image_hw: int = 32, classes: int = 10,
-                 distributed: bool = False):
+                 distributed: bool = False, _create=None):
         self.lib = _load()
         self.ctx = ctx
         self.batch, self.classes, self.image_hw = batch, classes, image_hw
         self.distributed = distributed
         h = C.c_void_p()
-        rc = self.lib.cbt_resnet_create(C.byref(h), ctx.h, batch, blocks_per_stage, image_hw, classes)
+        if _create is None:
+            rc = self.lib.cbt_resnet_create(C.byref(h), ctx.h, batch, blocks_per_stage, image_hw, classes)
+        else:
+            rc = _create(self.lib, h)
         self.h = h
         if rc != 0:
-            raise CrusaderError(rc, self.lib.cbt_last_error(h).decode() if h else "cbt_resnet_create failed")
+            raise CrusaderError(rc, self.lib.cbt_last_error(h).decode() if h else "model creation failed")
         self.n_params = int(self.lib.cbt_param_count(h))
         dev = torch.device("cuda", ctx.device)
         self.params = torch.zeros(self.n_params, device=dev)
@@ -166,3 +170,13 @@ class ResNetTrainer:
         self._check(self.lib.cbt_copy_tensor(self.h, tid, int(grad), out.data_ptr(), n))
         self.ctx.synchronize()
         return out.view(*shape)
+
+
+class DenseNetTrainer(ResNetTrainer):
+    """DenseNet-BC (growth k, `layers` bottleneck layers per block; k = 12, layers = 16 is DenseNet-BC-100)."""
+
+    def __init__(self, ctx: Context, batch: int, growth: int = 12, layers: int = 16, image_hw: int = 32, classes: int = 10,
+                 distributed: bool = False):
+        super().__init__(ctx, batch, image_hw=image_hw, classes=classes, distributed=distributed,
+                         _create=lambda lib, h: lib.cbt_densenet_create(C.byref(h), ctx.h, batch, growth, layers, image_hw,
+                                                                        classes))

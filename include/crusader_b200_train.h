@@ -23,6 +23,9 @@ typedef struct cbt_model cbt_model;
 
 /* ResNet with 6*blocks_per_stage + 2 layers (9 -> ResNet-56) on batch x 3 x image_hw x image_hw inputs. */
 int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_stage, int image_hw, int classes);
+/* DenseNet-BC with growth k and `layers` bottleneck layers per dense block (k = 12, layers = 16: DenseNet-BC-100),
+ * compression 0.5, 2x2 average-pool transitions, on batch x 3 x image_hw x image_hw inputs. */
+int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int layers, int image_hw, int classes);
 int cbt_destroy(cbt_model* m);
 const char* cbt_last_error(const cbt_model* m);
 

@@ -104,3 +104,65 @@ def test_resnet56_loss_tracks_fp32_run(torch_cuda):
     assert np.isfinite(a).all() and np.isfinite(b).all()
     assert a[-1] < a[0] and b[-1] < b[0]
     assert np.abs(a - b).max() / np.abs(a).max() <= 0.01
+
+
+@pytest.mark.parametrize("math,tol", [("fp32", 2e-4), ("tf32", 5e-2)])
+def test_small_densenet_step_matches_oracle(torch_cuda, math, tol):
+    """DenseNet-BC with growth 4 and 2 layers per block on 16x16 inputs, batch 16: loss, logits, every gradient
+    (fp32: 2e-4 per tensor; TF32: cosine >= 0.98 — fourteen small-batch BatchNorm layers amplify TF32 rounding)."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import DenseNetTrainer
+    from tests.model_oracle import densenet_param_shapes, densenet_run
+    growth, layers, hw, classes, batch = 4, 2, 16, 10, 16
+    ctx = Context(0, math=math, sync=True)
+    tr = DenseNetTrainer(ctx, batch=batch, growth=growth, layers=layers, image_hw=hw, classes=classes)
+    shapes = densenet_param_shapes(growth, layers, hw, classes)
+    assert [e["kind"] for e in tr.entries] == [k for k, _ in shapes]
+    assert [e["size"] for e in tr.entries] == [int(np.prod(s)) for _, s in shapes]
+    host = tr.init_params("dn")
+    for i, e in enumerate(tr.entries):
+        if e["kind"].startswith("bn"):
+            host[e["offset"]:e["offset"] + e["size"]] += 0.1 * orc.uniform_pm1((e["size"],), "dn", "bnp", i)
+    tr.set_params(host)
+    P = [host[e["offset"]:e["offset"] + e["size"]].reshape(s) for e, (_, s) in zip(tr.entries, shapes)]
+    images, onehot, dimg, dlab = make_batch(torch, batch, hw, classes, "dn")
+    tr.forward(dimg, dlab)
+    tr.backward()
+    ctx.synchronize()
+    loss_ref, G_ref, logits_ref = densenet_run(P, images, onehot, growth, layers)
+    assert abs(tr.loss() - loss_ref) <= tol * max(1.0, abs(loss_ref))
+    assert orc.max_err_norm(tr.tensor(-1, (batch, classes)).cpu().numpy(), logits_ref) <= tol
+    g = tr.grads.cpu().numpy()
+    for e, gr in zip(tr.entries, G_ref):
+        got = g[e["offset"]:e["offset"] + e["size"]].astype(np.float64)
+        want = np.asarray(gr, dtype=np.float64).ravel()
+        if math == "fp32":
+            assert orc.max_err_norm(got, want) <= tol, (e["kind"], e["dims"])
+        else:
+            cos = float(got @ want) / max(float(np.linalg.norm(got) * np.linalg.norm(want)), 1e-300)
+            assert cos >= 0.98, (e["kind"], e["dims"], cos)
+    tr.close()
+    ctx.close()
+
+
+def test_densenet_bc_100_forward_backward(torch_cuda):
+    """Config 5: DenseNet-BC-100 (k = 12, 3 x 16 bottleneck layers, compression 0.5), batch 64 of 3x32x32 N(0,1)
+    images: forward + backward run, the loss is finite and the TF32 loss agrees with the CUDA-core fp32 run."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import DenseNetTrainer
+    _, _, dimg, dlab = make_batch(torch, 64, 32, 10, "dn100")
+    losses = {}
+    for math in ("fp32", "tf32"):
+        ctx = Context(0, math=math, sync=False)
+        tr = DenseNetTrainer(ctx, batch=64, growth=12, layers=16, image_hw=32, classes=10)
+        assert len([e for e in tr.entries if e["kind"] == "conv"]) == 99
+        tr.init_params("dn100")
+        tr.forward(dimg, dlab)
+        tr.backward()
+        losses[math] = tr.loss()
+        assert torch.isfinite(tr.grads).all()
+        tr.close()
+        ctx.close()
+    assert np.isfinite(losses["fp32"]) and abs(losses["fp32"] - losses["tf32"]) <= 0.01 * abs(losses["fp32"])
