@@ -249,7 +249,7 @@ def bench_ours(args):
         extra_conv = conv_section(ctx, torch, dev, flush, only)
     ctx.close()
     extra_resnet = None
-    if not args.shapes and not args.no_resnet:
+    if (not args.shapes or args.resnet) and not args.no_resnet:
         try:
             extra_resnet = resnet56_section(torch, local, world, max(args.steps, 5), args.warmup)
         except Exception as exc:  # keep the headline line even if the training section fails
@@ -499,6 +499,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--conv-shapes", default="", help="comma list of CONV_SHAPES names: restrict the convolution section")
     ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-56 training section")
+    ap.add_argument("--resnet", action="store_true", help="run the ResNet-56 section even with --shapes (profiling runs)")
     args = ap.parse_args()
     if args.shapes == "none":
         SWEEP[:] = [(128, 10, 4096, "NN")]

@@ -86,6 +86,23 @@ int ensure_workspace2(cb_ctx* ctx, size_t bytes) {
     return CB_OK;
 }
 
+int ensure_workspace3(cb_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->workspace3_bytes) return CB_OK;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "workspace growth sync");
+    if (ctx->workspace3) cudaFree(ctx->workspace3);
+    ctx->workspace3 = nullptr;
+    ctx->workspace3_bytes = 0;
+    size_t want = (bytes + 255) & ~size_t(255);
+    e = cudaMalloc(&ctx->workspace3, want);
+    if (e != cudaSuccess) {
+        check_cuda(ctx, e, "workspace cudaMalloc");
+        return CB_ENOMEM;
+    }
+    ctx->workspace3_bytes = want;
+    return CB_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -180,6 +197,7 @@ int cb_destroy(cb_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->workspace2) cudaFree(ctx->workspace2);
+    if (ctx->workspace3) cudaFree(ctx->workspace3);
     if (ctx->d_status) cudaFree(ctx->d_status);
     delete ctx;
     return CB_OK;

@@ -20,6 +20,8 @@ struct cb_ctx {
     size_t workspace_bytes = 0;
     void* workspace2 = nullptr;    // scratch: re-laid-out activations / gradients of the stride-2 convolutions
     size_t workspace2_bytes = 0;
+    void* workspace3 = nullptr;    // scratch: lo parts and partial results of the 3xTF32 convolutions
+    size_t workspace3_bytes = 0;
     long long launches = 0;
     int sm_count = 148;
     int max_smem_optin = 0;
@@ -37,6 +39,7 @@ int finish(cb_ctx* ctx, const char* what);
 // because growth synchronises the stream before freeing the old block).
 int ensure_workspace(cb_ctx* ctx, size_t bytes);
 int ensure_workspace2(cb_ctx* ctx, size_t bytes);
+int ensure_workspace3(cb_ctx* ctx, size_t bytes);
 
 // Encodes a tiled fp32 tensor map. dims/box are innermost-first; strides_bytes has rank-1 entries
 // (the innermost stride is 4 bytes). swizzle_bytes in {0, 32, 64, 128}, or 129 for

@@ -167,6 +167,34 @@ int after_launch(cb_ctx* ctx, const char* what) {
     return finish(ctx, what);
 }
 
+// ---- 3xTF32 composition: x = hi + lo with hi = the 19 bits the tensor core reads, lo = rna_tf32(x - hi).
+__global__ void tf32_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+        uint32_t r;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v - hi));
+        lo[i] = __uint_as_float(r);
+    }
+}
+// y = y + a + b (+ bias[channel]) (ReLU): the sum of the three tensor-core passes
+__global__ void sum3_kernel(float* __restrict__ y, const float* __restrict__ a, const float* __restrict__ b,
+                            const float* __restrict__ bias, long long n, int C, long long plane, int relu) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = a[i] + b[i];  // the two small cross terms first, then the leading term
+        v += y[i];
+        if (bias) v += bias[(i / plane) % C];
+        if (relu) v = fmaxf(v, 0.f);
+        y[i] = v;
+    }
+}
+
+int grid_el(const cb_ctx* ctx, long long n) {
+    long long g = (n + 255) / 256;
+    const long long cap = (long long)ctx->sm_count * 16;
+    return (int)(g > cap ? cap : (g < 1 ? 1 : g));
+}
+
 }  // namespace
 
 // Tensor-core paths (conv_sm100.cu). Each returns CB_EUNSUPPORTED when the geometry is outside what it covers.
@@ -174,6 +202,62 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
                   int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of);
 int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate);
+
+
+// 3xTF32 forward / data gradient on the tensor cores: out = pass(W_hi, In_lo) + pass(W_lo, In_hi) + pass(W_hi, In_hi),
+// where every pass is the TF32 kernel (it reads the hi parts by truncation). The dropped lo*lo term is < 2^-20 relative.
+// Scratch (workspace3): In_lo, W_lo and the two cross-term outputs. Returns CB_EUNSUPPORTED when the TF32 kernel does
+// not cover the geometry, before any work was queued.
+static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out, const float* bias, int N, int IC, int IH,
+                       int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of,
+                       long long in_elems, long long out_elems, int out_channels, long long out_plane) {
+    const long long w_elems = (long long)OC * IC * FH * FW;
+    auto up = [](long long n) { return (n + 63) & ~63LL; };
+    const size_t need = (size_t)(up(in_elems) + up(w_elems) + 2 * up(out_elems)) * sizeof(float);
+    int rc = ensure_workspace3(ctx, need);
+    if (rc != CB_OK) return rc;
+    float* in_lo = static_cast<float*>(ctx->workspace3);
+    float* w_lo = in_lo + up(in_elems);
+    float* t1 = w_lo + up(w_elems);
+    float* t2 = t1 + up(out_elems);
+    // leading term first: it also tells whether the geometry is covered
+    rc = umma_conv_fwd(ctx, W, In, Out, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
+    if (rc != CB_OK) return rc;
+    tf32_lo_kernel<<<grid_el(ctx, in_elems), 256, 0, ctx->stream>>>(In, in_lo, in_elems);
+    tf32_lo_kernel<<<grid_el(ctx, w_elems), 256, 0, ctx->stream>>>(W, w_lo, w_elems);
+    rc = umma_conv_fwd(ctx, W, in_lo, t1, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
+    if (rc == CB_OK) rc = umma_conv_fwd(ctx, w_lo, In, t2, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
+    if (rc != CB_OK) return rc;
+    sum3_kernel<<<grid_el(ctx, out_elems), 256, 0, ctx->stream>>>(Out, t1, t2, bias, out_elems, out_channels, out_plane,
+                                                                 relu ? 1 : 0);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "3xTF32 convolution");
+    ctx->launches += 3;
+    ctx->last_kernel = "umma_3xtf32";
+    return CB_OK;
+}
+
+// 3xTF32 weight gradient: three accumulating TF32 passes (dY_hi X_lo, dY_lo X_hi, dY_hi X_hi).
+static int wgrad_3xtf32(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC, int FH,
+                        int FW, int sH, int sW, int pH, int pW, int accumulate, long long x_elems, long long dy_elems) {
+    auto up = [](long long n) { return (n + 63) & ~63LL; };
+    int rc = ensure_workspace3(ctx, (size_t)(up(x_elems) + up(dy_elems)) * sizeof(float));
+    if (rc != CB_OK) return rc;
+    float* x_lo = static_cast<float*>(ctx->workspace3);
+    float* dy_lo = x_lo + up(x_elems);
+    rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate);
+    if (rc != CB_OK) return rc;
+    tf32_lo_kernel<<<grid_el(ctx, x_elems), 256, 0, ctx->stream>>>(X, x_lo, x_elems);
+    tf32_lo_kernel<<<grid_el(ctx, dy_elems), 256, 0, ctx->stream>>>(dY, dy_lo, dy_elems);
+    rc = umma_conv_wgrad(ctx, dY, x_lo, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1);
+    if (rc == CB_OK) rc = umma_conv_wgrad(ctx, dy_lo, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1);
+    if (rc != CB_OK) return rc;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "3xTF32 weight gradient");
+    ctx->launches += 2;
+    ctx->last_kernel = "umma_3xtf32";
+    return CB_OK;
+}
 
 }  // namespace cb
 
@@ -190,8 +274,12 @@ int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const flo
     const long long npix = (long long)N * g.OH * g.OW;
     if (npix == 0 || OC == 0) return CB_OK;
     if (!W || !X || !Y) return fail(ctx, CB_EINVAL, "cb_conv_fwd: null operand");
-    if (ctx->math == CB_MATH_TF32) {  // the tensor-core kernels are TF32; 3xTF32 and FP32 requests keep fp32 accuracy on CUDA cores
+    if (ctx->math == CB_MATH_TF32) {  // tensor cores; 3xTF32 = three such passes; FP32 (and uncovered geometries) = CUDA cores
         rc = umma_conv_fwd(ctx, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, relu, false);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_fwd") : rc;
+    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = conv_3xtf32(ctx, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, relu, false,
+                         (long long)N * IC * IH * IW, npix * OC, OC, (long long)g.OH * g.OW);
         if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_fwd") : rc;
     }
     dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((OC + kOcTile - 1) / kOcTile));
@@ -210,6 +298,10 @@ int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N
     if (!W || !dY || !dX) return fail(ctx, CB_EINVAL, "cb_conv_dgrad: null operand");
     if (ctx->math == CB_MATH_TF32) {
         rc = umma_conv_fwd(ctx, W, dY, dX, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, true);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_dgrad") : rc;
+    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = conv_3xtf32(ctx, W, dY, dX, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, true,
+                         (long long)N * OC * g.OH * g.OW, npix * IC, IC, (long long)IH * IW);
         if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_dgrad") : rc;
     }
     dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((IC + kOcTile - 1) / kOcTile));
@@ -236,6 +328,10 @@ int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N
     if (!dY || !X) return fail(ctx, CB_EINVAL, "cb_conv_wgrad: null operand");
     if (ctx->math == CB_MATH_TF32) {
         rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_wgrad") : rc;
+    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = wgrad_3xtf32(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate,
+                          (long long)N * IC * IH * IW, (long long)N * OC * g.OH * g.OW);
         if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_wgrad") : rc;
     }
     if (OC > 65535 || IC > 65535) return fail(ctx, CB_EUNSUPPORTED, "cb_conv_wgrad: more than 65535 channels");

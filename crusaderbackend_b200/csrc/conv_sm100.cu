@@ -15,11 +15,15 @@
 //    fw*OCp + oc holds the partial sum of tap fw evaluated at the UNSHIFTED pixel), and the epilogue adds
 //    D0[x-1] + D1[x] + D2[x+1] with two warp shuffles per value; lanes at a row edge take zero instead, which is
 //    the horizontal padding. A pipeline stage is therefore only the centre copy of the input rows.
-//  * The filter is packed once per call into [fh][32-channel group][fw][oc][32 channels] (K-major rows of 128 bytes,
-//    zero padded) in the context workspace and stays resident in shared memory for the whole persistent CTA.
+//  * The filter is packed once per CTA into [fh][32-channel group][fw][oc][32 channels] (K-major rows of 128 bytes,
+//    zero padded, 128-byte swizzle) and stays resident in shared memory for the whole persistent CTA. The sixteen
+//    epilogue warps, idle until the first tile completes, build it straight from the caller's filter (coalesced
+//    reads, scattered 4-byte shared-memory writes), so forward and data gradient need no scratch buffer. (The
+//    allocation-free entry point keeps the older route: a pack kernel writes a scratch copy that TMA then loads.)
 //    For the data gradient the pack transposes the channel roles and rotates the filter by 180 degrees
 //    (seblas/operations/cuConv.cu:321-326 does the same rotation on the fly).
-//  * Epilogue: tcgen05.ld, + bias, ReLU, and stores in which the 32 lanes of a warp write 128 contiguous bytes.
+//  * Epilogue (16 warps, 4 per TMEM lane quarter): tcgen05.ld, tap combine, + bias, ReLU, and stores in which the 32
+//    lanes of a warp write 128 contiguous bytes.
 //
 // Covered geometry: stride 1, filter 1x1 (pad 0) or 3x3 (pad 1) per axis, W in {8,16,32}, (32/W) | H,
 // FW * OC(rounded to 16) <= 256, packed filter <= ~150 KB. Everything else is served by the CUDA-core kernels in conv_simt.cu.
@@ -58,6 +62,9 @@ struct ConvParams {
     const float* bias;
     int relu;
     int* status;
+    // filter packing done by the CTA itself (0: the packed filter is fetched by TMA from a scratch buffer)
+    int pack_in_kernel, pack_mode, OCs, ICs, FHs, FWs, out_first, out_count;
+    const float* Wsrc;
 };
 
 struct __align__(8) ConvSmem {
@@ -77,7 +84,72 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lan
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-__global__ void __launch_bounds__(192, 1)
+// Source filter tap of the stride-2 convolution that lands on (input phase, tap of the 2x2 phase convolution):
+// with ih = 2 oh + fh - 1, tap fh = 0 reads phase 1 at row oh - 1, fh = 1 phase 0 at row oh, fh = 2 phase 1 at row oh.
+__device__ __forceinline__ int s2_tap(int phase, int t) { return phase == 1 ? (t == 0 ? 0 : 2) : (t == 1 ? 1 : -1); }
+
+enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3 };
+
+// Inverse of s2_tap: source tap f of the 3x3 stride-2 filter -> (input phase, tap of the 2x2 phase convolution).
+__device__ __forceinline__ void s2_untap(int f, int& phase, int& t) {
+    phase = (f == 1) ? 0 : 1;
+    t = (f == 0) ? 0 : 1;
+}
+
+constexpr int kEpiWarps = 16;  // epilogue warps: 4 per TMEM lane quarter, each taking every 4th chunk of 8 channels
+
+template <int CH>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[CH]) {
+    if constexpr (CH == 32) tmem_ld32(taddr, r);
+    else if constexpr (CH == 16) tmem_ld16(taddr, r);
+    else tmem_ld8(taddr, r);
+}
+
+// One chunk of CH output channels of a tile's epilogue: the FW horizontal taps were accumulated at the unshifted
+// pixel in column blocks fw*OCp + oc; tap fw reads column ow + (fw - pW), so its partial sum sits (fw - pW) lanes
+// away. Lanes that would read across a row edge take zero instead (the horizontal padding).
+template <int CH>
+__device__ __forceinline__ void conv_epilogue_chunk(const ConvParams& p, uint32_t t_row, int c, float* out,
+                                                    long long plane, bool valid, bool has_left, bool has_right) {
+    uint32_t r0[CH], r1[CH], r2[CH];
+    tmem_ld_n<CH>(t_row + (uint32_t)c, r0);
+    if (p.FW > 1) tmem_ld_n<CH>(t_row + (uint32_t)(p.OCp + c), r1);
+    if (p.FW > 2) tmem_ld_n<CH>(t_row + (uint32_t)(2 * p.OCp + c), r2);
+    tmem_ld_wait();
+    float v[CH];
+#pragma unroll
+    for (int e = 0; e < CH; ++e) v[e] = 0.f;
+    for (int fw = 0; fw < p.FW; ++fw) {
+        const int d = fw - p.pW;  // warp-uniform
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            const float x = __uint_as_float(fw == 0 ? r0[e] : (fw == 1 ? r1[e] : r2[e]));
+            if (d == 0) {
+                v[e] += x;
+            } else if (d < 0) {
+                const float up = __shfl_up_sync(0xffffffffu, x, 1);
+                v[e] += has_left ? up : 0.f;
+            } else {
+                const float dn = __shfl_down_sync(0xffffffffu, x, 1);
+                v[e] += has_right ? dn : 0.f;
+            }
+        }
+    }
+    if (valid) {
+#pragma unroll
+        for (int e = 0; e < CH; ++e) {
+            const int oc = c + e;
+            if (oc < p.Cout) {
+                float y = v[e];
+                if (p.bias) y += __ldg(p.bias + oc);
+                if (p.relu) y = fmaxf(y, 0.f);
+                out[(long long)oc * plane] = y;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
     umma_conv_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                      const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -97,12 +169,12 @@ __global__ void __launch_bounds__(192, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&cs.tfull[a]), 1);
-            mbar_init(smem_u32(&cs.tempty[a]), 128);
+            mbar_init(smem_u32(&cs.tempty[a]), 32 * kEpiWarps);
         }
-        mbar_init(smem_u32(&cs.wbar), 1);
+        mbar_init(smem_u32(&cs.wbar), p.pack_in_kernel ? 32 * kEpiWarps : 1);
         mbar_fence_init();
         tma_prefetch_desc(&tmIn);
-        tma_prefetch_desc(&tmW);
+        if (!p.pack_in_kernel) tma_prefetch_desc(&tmW);
     }
     __syncthreads();
     if (warp == 1) {
@@ -117,7 +189,7 @@ __global__ void __launch_bounds__(192, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (lane == 0 && !p.pack_in_kernel) {
             // resident filter: one box [FW*OCp rows][32 channels] per (filter row, channel group)
             const uint32_t wbar = smem_u32(&cs.wbar);
             mbar_expect_tx(wbar, p.w_bytes);
@@ -140,17 +212,17 @@ __global__ void __launch_bounds__(192, 1)
                     if (p.shared_rows) {
                         // W == 32: the tile is 4 consecutive rows of one image; ONE box (32 px, 8*KS channels, FH+3
                         // rows) lands as [row][channel][128 B]; rows above / below the image are zero-filled
-                        const long long g = 4LL * tile;
-                        const int n = (int)(g / p.LPI);
-                        const int h0 = (int)(g - (long long)n * p.LPI);
+                        const int g = 4 * tile;  // 32-bit: a 64-bit division costs ~100 cycles on this path
+                        const int n = g / p.LPI;
+                        const int h0 = g - n * p.LPI;
                         tma_load_4d(dst0, &tmIn, full, 0, c0, h0 - p.pH, n);
                     } else {
                         for (int fh = 0; fh < p.FH; ++fh) {
                             for (int j = 0; j < 4; ++j) {
-                                const long long g = 4LL * tile + j;
+                                const int g = 4 * tile + j;
                                 // lines past the end use an image index >= N: the whole box is zero-filled
-                                const int n = (int)(g / p.LPI);
-                                const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
+                                const int n = g / p.LPI;
+                                const int h0 = (g - n * p.LPI) * p.L;
                                 tma_load_3d(dst0 + (uint32_t)(fh * 4 + j) * p.block_bytes, &tmIn, full,
                                             (h0 + fh - p.pH) * p.W, c0, n);
                             }
@@ -201,8 +273,54 @@ __global__ void __launch_bounds__(192, 1)
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..17)
+        // One scheduler cannot hide the shuffle and store latencies of a single warp, so every TMEM lane quarter is
+        // served by four warps that split the channel chunks between them.
         const int quarter = warp & 3;
+        const int slot = (warp - 2) >> 2;
+        if (p.pack_in_kernel) {
+            // The epilogue warps are idle until the first tile completes: they build the resident packed filter
+            // straight from the caller's OC x IC x FH x FW filter (coalesced reads, scattered 4-byte writes into the
+            // 128-byte-swizzled K-major rows), so no separate pack kernel or scratch buffer is needed.
+            const int te = threadIdx.x - 64, ne = 32 * kEpiWarps;
+            for (uint32_t v = (uint32_t)te; v < (p.w_bytes >> 4); v += (uint32_t)ne)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(w_base + v * 16u), "r"(0u) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+            const int taps_s = p.FHs * p.FWs;
+            const int total_src = p.OCs * p.ICs * taps_s;
+#pragma unroll 4
+            for (int j = te; j < total_src; j += ne) {
+                const int tap = j % taps_s, r = j / taps_s;
+                const int ch_s = r % p.ICs, o_s = r / p.ICs;
+                const int fh_s = tap / p.FWs, fw_s = tap - fh_s * p.FWs;
+                int fh, fw, o, ch;
+                bool keep = true;
+                if (p.pack_mode == PACK_FWD) {
+                    fh = fh_s; fw = fw_s; o = o_s; ch = ch_s;
+                } else if (p.pack_mode == PACK_DGRAD) {
+                    fh = p.FHs - 1 - fh_s; fw = p.FWs - 1 - fw_s; o = ch_s; ch = o_s;
+                } else {
+                    int ph, pw, th, tw;
+                    s2_untap(fh_s, ph, th);
+                    s2_untap(fw_s, pw, tw);
+                    const int og = (ph * 2 + pw) * p.ICs + ch_s;
+                    if (p.pack_mode == PACK_S2_FWD) {
+                        fh = th; fw = tw; o = o_s; ch = og;
+                    } else {
+                        fh = 1 - th; fw = 1 - tw; o = og - p.out_first; ch = o_s;
+                        keep = o >= 0 && o < p.out_count;
+                    }
+                }
+                if (keep) {
+                    const uint32_t R = (uint32_t)(((fh * p.CG + (ch >> 5)) * p.FW + fw) * p.OCp + o);
+                    const uint32_t c = (uint32_t)ch & 31u;
+                    const uint32_t addr = w_base + R * kRowBytes + (((c >> 2) ^ (R & 7u)) << 4) + ((c & 3u) << 2);
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(__ldg(p.Wsrc + j)) : "memory");
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&cs.wbar));
+        }
         uint32_t lt = 0;
         bool ok = true;
         const long long plane = (long long)p.H * p.W;
@@ -214,54 +332,15 @@ __global__ void __launch_bounds__(192, 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const long long g = 4LL * tile + quarter;
-            const bool valid = g < p.total_lines;
-            const int n = (int)(g / p.LPI);
-            const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
+            const int g = 4 * tile + quarter;
+            const bool valid = g < (int)p.total_lines;
+            const int n = g / p.LPI;
+            const int h0 = (g - n * p.LPI) * p.L;
             // lane x of the line is pixel (h0 + x / W, x % W): 32 consecutive floats of the output plane
             float* out = p.Out + ((long long)n * p.Cout * p.H + h0) * p.W + lane;
             const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
-            for (int c = 0; c < p.OCp; c += 16) {
-                float v[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) v[e] = 0.f;
-                // horizontal tap fw was accumulated at the unshifted pixel; it reads column ow + (fw - pW), so its
-                // partial sum sits (fw - pW) lanes away. Lanes that would read across a row edge take zero (padding).
-                for (int fw = 0; fw < p.FW; ++fw) {
-                    uint32_t r[16];
-                    tmem_ld16(t_row + (uint32_t)(fw * p.OCp + c), r);
-                    tmem_ld_wait();
-                    const int d = fw - p.pW;  // warp-uniform
-                    if (d == 0) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) v[e] += __uint_as_float(r[e]);
-                    } else if (d < 0) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(r[e]), 1);
-                            v[e] += has_left ? up : 0.f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(r[e]), 1);
-                            v[e] += has_right ? dn : 0.f;
-                        }
-                    }
-                }
-                if (valid) {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const int oc = c + e;
-                        if (oc < p.Cout) {
-                            float y = v[e];
-                            if (p.bias) y += __ldg(p.bias + oc);
-                            if (p.relu) y = fmaxf(y, 0.f);
-                            out[(long long)oc * plane] = y;
-                        }
-                    }
-                }
-            }
+            for (int c = slot * 8; c < p.OCp; c += 8 * (kEpiWarps / 4))
+                conv_epilogue_chunk<8>(p, t_row, c, out, plane, valid, has_left, has_right);
             tc_fence_before();
             mbar_arrive(smem_u32(&cs.tempty[a]));
         }
@@ -274,12 +353,6 @@ __global__ void __launch_bounds__(192, 1)
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
 }
-
-// Source filter tap of the stride-2 convolution that lands on (input phase, tap of the 2x2 phase convolution):
-// with ih = 2 oh + fh - 1, tap fh = 0 reads phase 1 at row oh - 1, fh = 1 phase 0 at row oh, fh = 2 phase 1 at row oh.
-__device__ __forceinline__ int s2_tap(int phase, int t) { return phase == 1 ? (t == 0 ? 0 : 2) : (t == 1 ? 1 : -1); }
-
-enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3 };
 
 // Packs the filter for the kernel above. Row index = ((fh * CG + cg) * FWc + fw) * OCp + o, 32 floats per row; W is the
 // caller's OC x IC x FHs x FWs filter, (FHc, FWc) the taps of the convolution the kernel runs.
@@ -450,7 +523,8 @@ struct PackSpec {
 static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const PackSpec& ps, const float* W,
                        const float* X, float* Y, const float* bias, int N, int IH, int IW, int FH, int FW, int pH, int pW,
                        int relu) {
-    {
+    const bool in_kernel = env.pack == nullptr;  // no scratch given: the CTAs pack the filter themselves
+    if (!in_kernel) {
         const long long total = (long long)q.w_bytes / 4;
         int grid = (int)((total + 255) / 256);
         if (grid > env.sm_count * 8) grid = env.sm_count * 8;
@@ -467,6 +541,7 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
     p.L = q.L; p.LPI = IH / q.L;
     p.shared_rows = q.shared_rows; p.nblocks = q.nblocks;
     p.total_lines = (long long)N * p.LPI;
+    if (p.total_lines > (1LL << 29)) return fail(err_ctx, CB_EUNSUPPORTED, "convolution: more than 2^29 lines of 32 pixels");
     p.tiles = (int)((p.total_lines + 3) / 4);
     p.stages = q.stages;
     int cols = 32;
@@ -477,6 +552,10 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
     p.stage_bytes = q.stage_bytes;
     p.Out = Y; p.bias = bias; p.relu = relu;
     p.status = env.status;
+    p.pack_in_kernel = in_kernel ? 1 : 0;
+    p.pack_mode = ps.mode; p.OCs = ps.OC; p.ICs = ps.IC; p.FHs = ps.FHs; p.FWs = ps.FWs;
+    p.out_first = ps.out_first; p.out_count = ps.out_count;
+    p.Wsrc = W;
 
     CUtensorMap tmIn, tmW;
     int rc;
@@ -499,7 +578,9 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
         rc = encode_tmap(err_ctx, &tmIn, X, 3, dims, str, box, nullptr, 129);
     }
     if (rc != CB_OK) return rc;
-    {
+    if (in_kernel) {
+        tmW = tmIn;  // unused by the kernel in this mode; any valid map will do
+    } else {
         const uint64_t rows = (uint64_t)FH * q.CG * q.NQ;
         uint64_t dims[3] = {32, rows, 1};
         uint64_t str[2] = {128, rows * 128};
@@ -517,13 +598,28 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int grid = p.tiles < env.sm_count ? p.tiles : env.sm_count;
-    umma_conv_kernel<<<grid, 192, smem, env.stream>>>(tmIn, tmW, p);
+    umma_conv_kernel<<<grid, 64 + 32 * kEpiWarps, smem, env.stream>>>(tmIn, tmW, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel launch");
     return CB_OK;
 }
 
 }  // namespace
+
+// Small filters are packed by the CTAs themselves (no extra launch, no scratch); large ones (a CTA would spend longer
+// packing than computing its first tile) by the pack kernel into the context workspace, fetched by TMA.
+static int launch_conv_auto(cb_ctx* ctx, ConvEnv env, const ConvPlan& q, const PackSpec& ps, const float* W, const float* X,
+                            float* Y, const float* bias, int N, int IH, int IW, int FH, int FW, int pH, int pW, int relu) {
+    const long long src = (long long)ps.OC * ps.IC * ps.FHs * ps.FWs;
+    env.pack = nullptr;
+    if (src > 12288) {
+        int rc = ensure_workspace(ctx, q.w_bytes);
+        if (rc != CB_OK) return rc;
+        env.pack = static_cast<float*>(ctx->workspace);
+        ctx->launches += 1;
+    }
+    return launch_conv(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
+}
 
 int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
                   int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of) {
@@ -536,13 +632,10 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
         if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
         rc = plan_conv(q, ctx->max_smem_optin, X, dgrad_of ? OC : IC, dgrad_of ? IC : OC, IH, IW, FH, FW, pH, pW);
         if (rc != CB_OK) return rc;
-        rc = ensure_workspace(ctx, q.w_bytes);
-        if (rc != CB_OK) return rc;
-        env.pack = static_cast<float*>(ctx->workspace);
         const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, FH, FW, 0, 0};
-        rc = launch_conv(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
+        rc = launch_conv_auto(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
         if (rc != CB_OK) return rc;
-        ctx->launches += 2;
+        ctx->launches += 1;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
@@ -564,17 +657,15 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
         if (rc != CB_OK) return rc;
         const size_t sub_bytes = (size_t)N * IC * plane2 * sizeof(float);
         rc = ensure_workspace2(ctx, sub_bytes);
-        if (rc == CB_OK) rc = ensure_workspace(ctx, q.w_bytes);
         if (rc != CB_OK) return rc;
-        env.pack = static_cast<float*>(ctx->workspace);
         float* sub = static_cast<float*>(ctx->workspace2);
         const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, 1, 1, 0, 0};
         const long long n_sub = (long long)N * IC * plane2;
         if (!dgrad_of) {
             subsample2_kernel<<<grid_of(n_sub), launch_threads, 0, ctx->stream>>>(X, sub, (long long)N * IC, IH, IW, n_sub);
-            rc = launch_conv(ctx, env, q, ps, W, sub, Y, bias, N, H2, W2, 1, 1, 0, 0, relu);
+            rc = launch_conv_auto(ctx, env, q, ps, W, sub, Y, bias, N, H2, W2, 1, 1, 0, 0, relu);
         } else {
-            rc = launch_conv(ctx, env, q, ps, W, X /* = dY */, sub, nullptr, N, H2, W2, 1, 1, 0, 0, 0);
+            rc = launch_conv_auto(ctx, env, q, ps, W, X /* = dY */, sub, nullptr, N, H2, W2, 1, 1, 0, 0, 0);
             const long long n_full = (long long)N * IC * IH * IW;
             if (rc == CB_OK)
                 upsample2_zero_kernel<<<grid_of(n_full), launch_threads, 0, ctx->stream>>>(sub, Y /* = dX */, IH, IW, n_full);
@@ -582,7 +673,7 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
         if (rc != CB_OK) return rc;
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return check_cuda(ctx, e, "stride-2 1x1 convolution");
-        ctx->launches += 3;
+        ctx->launches += 2;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
@@ -595,15 +686,12 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
         float* Xs = static_cast<float*>(ctx->workspace2);
         rc = plan_conv(q, ctx->max_smem_optin, Xs, C4, OC, H2, W2, 2, 2, 1, 1);
         if (rc != CB_OK) return rc;
-        rc = ensure_workspace(ctx, q.w_bytes);
-        if (rc != CB_OK) return rc;
-        env.pack = static_cast<float*>(ctx->workspace);
         const long long n_el = (long long)N * C4 * plane2;
         space_to_depth2_kernel<<<grid_of(n_el), launch_threads, 0, ctx->stream>>>(X, Xs, IC, IH, IW, n_el);
         const PackSpec ps{PACK_S2_FWD, OC, IC, 3, 3, 0, 0};
-        rc = launch_conv(ctx, env, q, ps, W, Xs, Y, bias, N, H2, W2, 2, 2, 1, 1, relu);
+        rc = launch_conv_auto(ctx, env, q, ps, W, Xs, Y, bias, N, H2, W2, 2, 2, 1, 1, relu);
         if (rc != CB_OK) return rc;
-        ctx->launches += 3;
+        ctx->launches += 2;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
@@ -618,12 +706,9 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     float* dXs = static_cast<float*>(ctx->workspace2);
     rc = plan_conv(q, ctx->max_smem_optin, X /* = dY */, OC, per_group, H2, W2, 2, 2, 0, 0);
     if (rc != CB_OK) return rc;
-    rc = ensure_workspace(ctx, q.w_bytes);
-    if (rc != CB_OK) return rc;
-    env.pack = static_cast<float*>(ctx->workspace);
     for (int g = 0; g < groups; ++g) {
         const PackSpec ps{PACK_S2_DGRAD, OC, IC, 3, 3, g * per_group, per_group};
-        rc = launch_conv(ctx, env, q, ps, W, X /* = dY */, dXs + (size_t)g * N * per_group * plane2, nullptr, N, H2, W2, 2, 2,
+        rc = launch_conv_auto(ctx, env, q, ps, W, X /* = dY */, dXs + (size_t)g * N * per_group * plane2, nullptr, N, H2, W2, 2, 2,
                          0, 0, 0);
         if (rc != CB_OK) return rc;
     }
@@ -632,7 +717,7 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
                                                                                  n_full);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "depth_to_space2_kernel launch");
-    ctx->launches += 2 * groups + 1;
+    ctx->launches += groups + 1;
     ctx->last_kernel = "umma_tf32";
     return CB_OK;
 }
@@ -647,7 +732,7 @@ namespace {
 //      rows stacked as (fh, c); 128 rows per M tile), and
 //   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
 //      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
-//      edges), written by four shift warps — shifting dY by -d is the same sum as shifting X by +d.
+//      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
 // Every CTA walks its share of the lines accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs),
 // writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
 struct WgradParams {
@@ -676,39 +761,31 @@ __device__ __forceinline__ uint32_t sw128_chunk(uint32_t row_addr, int q) {
     return row_addr + ((((uint32_t)q) ^ ((row_addr >> 7) & 7u)) << 4);
 }
 
-// Builds the horizontally shifted copies of one dY row: row_m1 (tap offset -1: pairs X[px] with dY[px + 1]) and
-// row_p1 (tap offset +1: pairs X[px] with dY[px - 1]); an address of 0 skips that copy.
-template <int W>
-__device__ __forceinline__ void shift_dy_row(uint32_t src_row, uint32_t row_m1, uint32_t row_p1) {
-    float v[32];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v[4 * q]), "=f"(v[4 * q + 1]), "=f"(v[4 * q + 2]), "=f"(v[4 * q + 3])
-                     : "r"(sw128_chunk(src_row, q)));
+constexpr int kShiftWarps = 8;  // one scheduler cannot hide the shared-memory latencies of a single warp
+
+// One 16-byte chunk (pixels 4q .. 4q+3) of the horizontally shifted copies of a dY row: row_m1 (tap offset -1: pairs
+// X[px] with dY[px + 1]) and row_p1 (tap offset +1: pairs X[px] with dY[px - 1]); zeros enter at the edges of the
+// W-wide image rows packed in the line; an address of 0 skips that copy.
+__device__ __forceinline__ void shift_dy_chunk(uint32_t src_row, uint32_t row_m1, uint32_t row_p1, int q, int W) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(sw128_chunk(src_row, q)));
+    float left = 0.f, right = 0.f;
+    if (q > 0) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(left) : "r"(sw128_chunk(src_row, q - 1) + 12u));
+    if (q < 7) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(right) : "r"(sw128_chunk(src_row, q + 1)));
+    const int x0 = 4 * q, wm = W - 1;
+    if (row_m1) {
+        const float a0 = ((x0 & wm) < wm) ? v.y : 0.f, a1 = (((x0 + 1) & wm) < wm) ? v.z : 0.f;
+        const float a2 = (((x0 + 2) & wm) < wm) ? v.w : 0.f, a3 = (((x0 + 3) & wm) < wm) ? right : 0.f;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_m1, q)), "f"(a0), "f"(a1), "f"(a2), "f"(a3) : "memory");
     }
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        float a[4], b[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int x = 4 * q + e;
-            const int col = x % W;
-            a[e] = (col < W - 1) ? v[(x + 1) & 31] : 0.f;
-            b[e] = (col >= 1) ? v[(x + 31) & 31] : 0.f;
-        }
-        if (row_m1)
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_m1, q)), "f"(a[0]), "f"(a[1]),
-                         "f"(a[2]), "f"(a[3])
-                         : "memory");
-        if (row_p1)
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_p1, q)), "f"(b[0]), "f"(b[1]),
-                         "f"(b[2]), "f"(b[3])
-                         : "memory");
+    if (row_p1) {
+        const float b0 = ((x0 & wm) >= 1) ? left : 0.f, b1 = (((x0 + 1) & wm) >= 1) ? v.x : 0.f;
+        const float b2 = (((x0 + 2) & wm) >= 1) ? v.y : 0.f, b3 = (((x0 + 3) & wm) >= 1) ? v.z : 0.f;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_p1, q)), "f"(b0), "f"(b1), "f"(b2), "f"(b3) : "memory");
     }
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmdY,
                       const WgradParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -725,7 +802,7 @@ __global__ void __launch_bounds__(320, 1)
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(smem_u32(&ws.full[s]), 1);
             mbar_init(smem_u32(&ws.empty[s]), 1);
-            mbar_init(smem_u32(&ws.xf[s]), 128);
+            mbar_init(smem_u32(&ws.xf[s]), 32 * kShiftWarps);
         }
         mbar_init(smem_u32(&ws.tfull), 1);
         mbar_fence_init();
@@ -752,8 +829,9 @@ __global__ void __launch_bounds__(320, 1)
             if (lane == 0) {
                 const uint32_t full = smem_u32(&ws.full[s]);
                 const uint32_t stg = st_base + s * p.stage_bytes;
-                const int n = (int)(g / p.LPI);
-                const int h0 = (int)(g - (long long)n * p.LPI) * p.L;
+                const int gi = (int)g;  // total_lines < 2^29 (checked on the host)
+                const int n = gi / p.LPI;
+                const int h0 = (gi - n * p.LPI) * p.L;
                 mbar_expect_tx(full, p.a_bytes + set_bytes);
                 for (int fh = 0; fh < p.FH; ++fh)
                     tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
@@ -828,14 +906,13 @@ __global__ void __launch_bounds__(320, 1)
             for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
                 ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
                 if (!ok) break;
-                if (t < p.OCp) {
-                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)t * kRowBytes;
+                for (int item = t; item < p.OCp * 8; item += 32 * kShiftWarps) {
+                    const int row = item >> 3, q = item & 7;
+                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)row * kRowBytes;
                     const uint32_t src = b0 + (uint32_t)centre * set_bytes;
                     const uint32_t m1 = centre >= 1 ? src - set_bytes : 0u;             // tap fw = pW - 1
                     const uint32_t p1 = centre + 1 < p.FW ? src + set_bytes : 0u;       // tap fw = pW + 1
-                    if (p.W == 32) shift_dy_row<32>(src, m1, p1);
-                    else if (p.W == 16) shift_dy_row<16>(src, m1, p1);
-                    else shift_dy_row<8>(src, m1, p1);
+                    shift_dy_chunk(src, m1, p1, q, p.W);
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&ws.xf[s]));
@@ -854,33 +931,44 @@ __global__ void __launch_bounds__(320, 1)
 
 // dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
 // s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
-__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW, int nparts, int rows_tot,
-                                    int rowsA, int NQ, int Cp, int Cin, int OC, int OCp, int FH, int FW, int accumulate,
-                                    int s2, int IC_src) {
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+                                                           int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
+                                                           int OC, int OCp, int FH, int FW, int accumulate, int s2,
+                                                           int IC_src) {
+    // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
+    // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
+    __shared__ float red[8][33];
     const long long total = (long long)rowsA * NQ;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int col = (int)(i % NQ);
-        const int r = (int)(i / NQ);
-        const int fh = r / Cp, c = r - fh * Cp;
-        const int fw = col / OCp, oc = col - fw * OCp;
-        if (c >= Cin || oc >= OC) continue;
-        float* dst;
-        if (!s2) {
-            dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
-        } else {
-            const int phase = c / IC_src, cc = c - phase * IC_src;
-            const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
-            if (sh < 0 || sw < 0) continue;
-            dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
-        }
-        float s = 0.f;
-        const float* src = partial + (long long)r * NQ + col;
+    const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
+    const int grp = threadIdx.y;
+    float s = 0.f;
+    if (i < total) {
         const long long pstride = (long long)rows_tot * NQ;
-#pragma unroll 8
-        for (int q = 0; q < nparts; ++q) s += __ldg(src + q * pstride);  // fixed order: deterministic
-        *dst = accumulate ? *dst + s : s;
+        const float* src = partial + i;  // (r, col) of the partial layout is exactly element i
+#pragma unroll 4
+        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * pstride);
     }
+    red[grp][threadIdx.x] = s;
+    __syncthreads();
+    if (grp != 0 || i >= total) return;
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) sum += red[g][threadIdx.x];
+    const int col = (int)(i % NQ);
+    const int r = (int)(i / NQ);
+    const int fh = r / Cp, c = r - fh * Cp;
+    const int fw = col / OCp, oc = col - fw * OCp;
+    if (c >= Cin || oc >= OC) return;
+    float* dst;
+    if (!s2) {
+        dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+    } else {
+        const int phase = c / IC_src, cc = c - phase * IC_src;
+        const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
+        if (sh < 0 || sw < 0) return;
+        dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
+    }
+    *dst = accumulate ? *dst + sum : sum;
 }
 
 }  // namespace
@@ -914,6 +1002,7 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     p.Cp = Cp; p.OCp = OCp; p.NQ = NQ; p.mtiles = mtiles; p.rowsA = rowsA;
     p.L = L; p.LPI = IH / L;
     p.total_lines = (long long)N * p.LPI;
+    if (p.total_lines > (1LL << 29)) return CB_EUNSUPPORTED;
     p.stages = (int)stages;
     int cols = 32;
     while (cols < mtiles * NQ) cols <<= 1;
@@ -945,12 +1034,12 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
-    umma_wgrad_kernel<<<grid, 320, smem, ctx->stream>>>(tmX, tmdY, p);
+    umma_wgrad_kernel<<<grid, 192 + 32 * kShiftWarps, smem, ctx->stream>>>(tmX, tmdY, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
     const long long total = (long long)rowsA * NQ;
-    int rgrid = (int)((total + 255) / 256);
-    wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
+    int rgrid = (int)((total + 31) / 32);
+    wgrad_reduce_kernel<<<rgrid, dim3(32, 8), 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
                                                          accumulate ? 1 : 0, s2, IC_src);
     e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");

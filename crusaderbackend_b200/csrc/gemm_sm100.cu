@@ -17,6 +17,9 @@
 //
 // 3xTF32: a = hi + lo with hi = the 19 high bits the tensor core reads from the fp32 word, lo = a - hi
 // (exact), rounded to TF32. D = P_hi*Q_lo + P_lo*Q_hi + P_hi*Q_hi; the dropped lo*lo term is < 2^-20 |p q|.
+#include <cstdlib>
+#include <utility>
+
 #include "cb_internal.h"
 #include "cb_ptx.cuh"
 
@@ -36,6 +39,7 @@ struct GemmParams {
     int num_kb, splits, kb_per_split;
     int kc;                // k-blocks per accumulation chunk: the accumulator is drained to C every kc blocks
     int tmem_cols;         // allocated TMEM columns (power of two >= 2*bn)
+    int nsplit;            // 2: every UMMA is issued as two half-N instructions into disjoint accumulator columns
     int p_batched, q_batched;
     float* C;
     long long ldc, strideC;
@@ -190,7 +194,8 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.bn, P_MN ? 1u : 0u, Q_MN ? 1u : 0u);
+        const uint32_t nh = (uint32_t)p.bn / (uint32_t)p.nsplit;  // UMMA N per instruction
+        const uint32_t idesc = umma_idesc_tf32(128, nh, P_MN ? 1u : 0u, Q_MN ? 1u : 0u);
         uint32_t s = 0, ph = 0;
         uint32_t sub = 0;  // running accumulator sub-tile counter
         bool ok = true;
@@ -229,14 +234,20 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                             const uint64_t dP = P_MN ? desc_mn(pm + p_off) : desc_k(pm + p_off);
                             const uint64_t dQ = Q_MN ? desc_mn(sQ + q_off) : desc_k(sQ + q_off);
                             const uint32_t first = (chunk_first && kk == 0) ? 0u : 1u;
-                            if (X3) {
-                                const uint64_t dPl = P_MN ? desc_mn(pm + hi_bytes + p_off) : desc_k(pm + hi_bytes + p_off);
-                                const uint64_t dQl = Q_MN ? desc_mn(sQ + hi_bytes + q_off) : desc_k(sQ + hi_bytes + q_off);
-                                umma_tf32(d_tmem, dP, dQl, idesc, first);
-                                umma_tf32(d_tmem, dPl, dQ, idesc, 1u);
-                                umma_tf32(d_tmem, dP, dQ, idesc, 1u);
-                            } else {
-                                umma_tf32(d_tmem, dP, dQ, idesc, first);
+                            // Consecutive UMMAs into the same accumulator columns serialise on that accumulator; two
+                            // half-N instructions into disjoint column ranges alternate and overlap.
+                            for (uint32_t h = 0; h < (uint32_t)p.nsplit; ++h) {
+                                const uint32_t dh = d_tmem + h * nh;
+                                const uint64_t qh = (uint64_t)((h * nh * 128u) >> 4);  // rows h*nh of the Q tile
+                                if (X3) {
+                                    const uint64_t dPl = P_MN ? desc_mn(pm + hi_bytes + p_off) : desc_k(pm + hi_bytes + p_off);
+                                    const uint64_t dQl = Q_MN ? desc_mn(sQ + hi_bytes + q_off) : desc_k(sQ + hi_bytes + q_off);
+                                    umma_tf32(dh, dP, dQl + qh, idesc, first);
+                                    umma_tf32(dh, dPl, dQ + qh, idesc, 1u);
+                                    umma_tf32(dh, dP, dQ + qh, idesc, 1u);
+                                } else {
+                                    umma_tf32(dh, dP, dQ + qh, idesc, first);
+                                }
                             }
                         }
                     }
@@ -452,6 +463,58 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
         }
 }
 
+// Thin products (I <= 16, e.g. the 128 x 10 x 4096 dense-layer shape): HBM/latency-bound, so K is split over many CTAs,
+// one warp per output row j with lanes striding k (128-bit-coalesced reads of Q when it is K-major), the I thin
+// outputs per lane reduced with warp shuffles and added atomically into C (or stored when K is not split).
+__global__ void __launch_bounds__(256) skinny_gemm_kernel(const SimtParams p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = blockIdx.x * 8 + warp;
+    if (j >= p.J) return;
+    const int split = blockIdx.y;
+    const int k0 = split * p.k_per_split, k1 = min(p.K, k0 + p.k_per_split);
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int k = k0 + lane; k < k1; k += 32) {
+        const float q = p.q_mn ? p.Q[(long long)k * p.ldq + j] : p.Q[(long long)j * p.ldq + k];
+        if (p.p_mn) {
+            const float* pr = p.P + (long long)k * p.ldp;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < p.I) acc[i] = fmaf(q, pr[i], acc[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < p.I) acc[i] = fmaf(q, p.P[(long long)i * p.ldp + k], acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float v = acc[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        acc[i] = v;
+    }
+    if (lane < p.I) {
+        float v = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (i == lane) v = acc[i];
+        if (split == 0) {
+            if (p.bias_i) v += p.bias_i[lane];
+            if (p.bias_j) v += p.bias_j[j];
+        }
+        float* dst = p.out_mode == 0 ? p.C + (long long)j * p.ldc + lane : p.C + (long long)lane * p.ldc + j;
+        if (p.atomic_out) {
+            atomicAdd(dst, v);
+        } else {
+            if (p.accumulate) v += *dst;
+            if (p.relu) v = fmaxf(v, 0.f);
+            *dst = v;
+        }
+    }
+}
+
 int zero_output(cb_ctx* ctx, const GemmCall& g) {
     // rows of the output as laid out in memory: out_mode 0 -> J rows of I floats, 1 -> I rows of J floats
     const size_t width = (size_t)(g.out_mode == 0 ? g.I : g.J) * 4;
@@ -556,6 +619,7 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     int cols = 32;
     while (cols < 2 * gp.bn) cols <<= 1;
     gp.tmem_cols = cols;
+    { const char* e = getenv("CB_NSPLIT"); gp.nsplit = (e && atoi(e) == 2 && gp.bn % 64 == 0) ? 2 : 1; }
     gp.p_batched = (g.batch > 1 && g.strideP != 0) ? 1 : 0;
     gp.q_batched = (g.batch > 1 && g.strideQ != 0) ? 1 : 0;
     gp.C = g.C; gp.ldc = g.ldc; gp.strideC = g.strideC;
@@ -612,7 +676,44 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     return CB_OK;
 }
 
-int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g) {
+int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g_in) {
+    GemmCall g = g_in;
+    if (g.J <= 16 && g.I > 16) {  // put the thin extent on the I side: D'[j][i] with the operands' roles swapped
+        std::swap(g.I, g.J);
+        std::swap(g.P, g.Q); std::swap(g.ldp, g.ldq); std::swap(g.strideP, g.strideQ); std::swap(g.p_mn, g.q_mn);
+        std::swap(g.ep.bias_i, g.ep.bias_j);
+        g.out_mode ^= 1;
+    }
+    if (g.I <= 16 && g.batch == 1 && g.J >= 32 && g.K >= 256) {
+        SimtParams sp{};
+        sp.I = g.I; sp.J = g.J; sp.K = g.K; sp.batch = 1;
+        sp.P = g.P; sp.ldp = g.ldp; sp.p_mn = g.p_mn;
+        sp.Q = g.Q; sp.ldq = g.ldq; sp.q_mn = g.q_mn;
+        sp.C = g.C; sp.ldc = g.ldc; sp.out_mode = g.out_mode; sp.accumulate = g.accumulate;
+        sp.bias_i = g.ep.bias_i; sp.bias_j = g.ep.bias_j; sp.relu = g.ep.relu;
+        const int jblocks = (g.J + 7) / 8;
+        int splits = 1;
+        if (!ctx->deterministic && g.ep.relu == 0) {
+            splits = (2 * ctx->sm_count + jblocks - 1) / jblocks;
+            if (splits > g.K / 128) splits = g.K / 128;
+            if (splits < 1) splits = 1;
+        }
+        int kps = (g.K + splits - 1) / splits;
+        kps = ((kps + 31) / 32) * 32;
+        splits = (g.K + kps - 1) / kps;
+        sp.splits = splits; sp.k_per_split = kps;
+        sp.atomic_out = splits > 1 ? 1 : 0;
+        if (sp.atomic_out && !g.accumulate) {
+            int rc = zero_output(ctx, g);
+            if (rc != CB_OK) return rc;
+        }
+        skinny_gemm_kernel<<<dim3(jblocks, splits), 256, 0, ctx->stream>>>(sp);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return check_cuda(ctx, e, "skinny_gemm_kernel launch");
+        ctx->launches += 1;
+        ctx->last_kernel = "simt_fp32";
+        return CB_OK;
+    }
     SimtParams sp{};
     sp.I = g.I; sp.J = g.J; sp.K = g.K; sp.batch = g.batch;
     sp.P = g.P; sp.ldp = g.ldp; sp.strideP = g.strideP; sp.p_mn = g.p_mn;
