@@ -191,6 +191,12 @@ class Context:
         self._check(self.lib.cb_bn_paramgrad(self.h, _ptr(dY), _ptr(xHat), _ptr(dGamma), _ptr(dBeta), N,
                                              dY.numel() // N))
 
+    def batchNormGradFused(self, dY, gamma, X, dX, dGamma, dBeta):
+        N = X.shape[0]
+        self._check(self.lib.cb_bn_bwd_fused(self.h, _ptr(dY), _ptr(gamma), _ptr(X), _ptr(dX), _ptr(dGamma), _ptr(dBeta), N,
+                                             X.numel() // N))
+        return dX
+
     def relu(self, X, Y):
         self._check(self.lib.cb_relu(self.h, _ptr(X), _ptr(Y), X.numel()))
         return Y

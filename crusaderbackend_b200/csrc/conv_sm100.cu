@@ -235,7 +235,15 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
+        // One thread feeds the tensor core: descriptor constants are hoisted and each UMMA costs a few integer adds.
         const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 1u, 0u);
+        // P: 4 lines x [8 channels][128 B], MN-major: block_bytes between lines (LBO), 512 B per 4 channel rows (SBO)
+        const uint64_t descP0 = umma_smem_desc(0, p.block_bytes, 512u, UMMA_SW_128B_BASE32B);
+        // Q: packed filter rows [(fw, oc)][32 channels], K-major 128-byte rows
+        const uint64_t descQ0 = umma_smem_desc(w_base, 16u, 1024u, UMMA_SW_128B);
+        const uint32_t blk_units = p.block_bytes >> 4;               // descriptor address units (16 B) per line block
+        const uint32_t fh_blocks = p.shared_rows ? 1u : 4u;          // blocks between consecutive filter rows
+        const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
         uint32_t s = 0, ph = 0, lt = 0;
         bool ok = warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
         for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
@@ -250,19 +258,16 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t stg = st_base + s * p.stage_bytes;
+                    const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
+                    uint32_t accumulate = cb == 0 ? 0u : 1u;
                     for (int fh = 0; fh < p.FH; ++fh) {
-                        const uint32_t first_block = p.shared_rows ? (uint32_t)fh : (uint32_t)fh * 4u;
+                        const uint64_t dPf = pbase + (uint64_t)((uint32_t)fh * fh_blocks * blk_units);
+                        const uint32_t q_fh = (uint32_t)(fh * p.CG) * q_group_units;
                         for (int kk = 0; kk < p.KS; ++kk) {
-                            const int ks = cb * p.KS + kk;  // global K step: channels [8 ks, 8 ks + 8)
-                            // P: 4 lines x [8 channels][128 B], MN-major: block_bytes between lines, 512 B per 4 rows
-                            const uint64_t dP = umma_smem_desc(stg + first_block * p.block_bytes + (uint32_t)kk * 1024u,
-                                                               p.block_bytes, 512u, UMMA_SW_128B_BASE32B);
-                            // Q: packed filter rows [(fw, oc)][32 channels], K-major
-                            const uint64_t dQ = umma_smem_desc(w_base + (uint32_t)(fh * p.CG + (ks >> 2)) * p.NQ * kRowBytes +
-                                                                   (uint32_t)(ks & 3) * 32u,
-                                                               16u, 1024u, UMMA_SW_128B);
-                            umma_tf32(d_tmem, dP, dQ, idesc, (cb == 0 && fh == 0 && kk == 0) ? 0u : 1u);
+                            const uint32_t ks = (uint32_t)(cb * p.KS + kk);  // global K step: channels [8 ks, 8 ks + 8)
+                            umma_tf32(d_tmem, dPf + (uint64_t)(kk * 64), descQ0 + (uint64_t)(q_fh + (ks >> 2) * q_group_units + (ks & 3u) * 2u),
+                                      idesc, accumulate);
+                            accumulate = 1u;
                         }
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
@@ -843,6 +848,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
         const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 0u, 0u);
+        const uint64_t desc0 = umma_smem_desc(0, 16u, 1024u, UMMA_SW_128B);  // K-major 128-byte rows; address added per stage
         uint32_t s = 0, ph = 0;
         bool ok = true;
         bool first_line = true;
@@ -856,13 +862,16 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t stg = st_base + s * p.stage_bytes;
+                const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
+                const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
+                const uint32_t first = first_line ? 0u : 1u;
                 for (int m = 0; m < p.mtiles; ++m) {
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t dA = umma_smem_desc(stg + (uint32_t)m * 16384u + kk * 32u, 16u, 1024u, UMMA_SW_128B);
-                        const uint64_t dB = umma_smem_desc(stg + p.a_bytes + kk * 32u, 16u, 1024u, UMMA_SW_128B);
-                        umma_tf32(tmem_base + (uint32_t)m * p.NQ, dA, dB, idesc, (first_line && kk == 0) ? 0u : 1u);
-                    }
+                    const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
+                    const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
+                    umma_tf32(d, dA, dB0, idesc, first);
+                    umma_tf32(d, dA + 2, dB0 + 2, idesc, 1u);
+                    umma_tf32(d, dA + 4, dB0 + 4, idesc, 1u);
+                    umma_tf32(d, dA + 6, dB0 + 6, idesc, 1u);
                 }
                 tc_commit(smem_u32(&ws.empty[s]));
                 if (g + gridDim.x >= p.total_lines) tc_commit(smem_u32(&ws.tfull));

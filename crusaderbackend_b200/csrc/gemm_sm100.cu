@@ -17,7 +17,6 @@
 //
 // 3xTF32: a = hi + lo with hi = the 19 high bits the tensor core reads from the fp32 word, lo = a - hi
 // (exact), rounded to TF32. D = P_hi*Q_lo + P_lo*Q_hi + P_hi*Q_hi; the dropped lo*lo term is < 2^-20 |p q|.
-#include <cstdlib>
 #include <utility>
 
 #include "cb_internal.h"
@@ -39,7 +38,6 @@ struct GemmParams {
     int num_kb, splits, kb_per_split;
     int kc;                // k-blocks per accumulation chunk: the accumulator is drained to C every kc blocks
     int tmem_cols;         // allocated TMEM columns (power of two >= 2*bn)
-    int nsplit;            // 2: every UMMA is issued as two half-N instructions into disjoint accumulator columns
     int p_batched, q_batched;
     float* C;
     long long ldc, strideC;
@@ -194,13 +192,21 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        const uint32_t nh = (uint32_t)p.bn / (uint32_t)p.nsplit;  // UMMA N per instruction
-        const uint32_t idesc = umma_idesc_tf32(128, nh, P_MN ? 1u : 0u, Q_MN ? 1u : 0u);
+        // One thread feeds the tensor core, so the instructions it spends per tcgen05.mma bound the whole kernel:
+        // the descriptors of a stage are built once and advanced by constant adds, the chunk position is a counter
+        // (no division), and everything that is not an UMMA stays outside the unrolled k-step loop.
+        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.bn, P_MN ? 1u : 0u, Q_MN ? 1u : 0u);
+        constexpr uint64_t kStepP = P_MN ? (1024u >> 4) : (32u >> 4);  // descriptor address units (16 B) per k-step
+        constexpr uint64_t kStepQ = Q_MN ? (1024u >> 4) : (32u >> 4);
+        const uint64_t descP0 = P_MN ? desc_mn(0) : desc_k(0);  // layout bits; the start address is added below
+        const uint64_t descQ0 = Q_MN ? desc_mn(0) : desc_k(0);
+        const uint64_t lo_units = (uint64_t)(hi_bytes >> 4);
         uint32_t s = 0, ph = 0;
         uint32_t sub = 0;  // running accumulator sub-tile counter
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
             const WorkItem it = decode_work(p, w);
+            int kc_pos = 0;
             for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
                 ok = warp_wait(smem_u32(&ps.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
                 if (!ok) break;
@@ -209,52 +215,41 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                     if (!ok) break;
                 }
                 tc_fence_after();
-                const int kc_pos = (kb - it.kb0) % p.kc;
                 const bool chunk_first = kc_pos == 0;
                 const bool chunk_last = kc_pos == p.kc - 1 || kb == it.kb1 - 1;
+                kc_pos = chunk_last ? 0 : kc_pos + 1;
                 const uint32_t sP = tiles_base + s * stage_bytes;
-                const uint32_t sQ = sP + p_bytes;
-                for (int m = 0; m < p.mi && ok; ++m) {
-                    const uint32_t u = sub + (uint32_t)m;
-                    const uint32_t a = u & 1u;
-                    if (chunk_first) {
-                        // first product into this accumulator: the epilogue must have drained its last use
-                        ok = warp_wait(smem_u32(&ps.tempty[a]), ((u >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
+                if (chunk_first) {
+                    // first product into these accumulators: the epilogue must have drained their last use
+                    for (int m = 0; m < p.mi && ok; ++m) {
+                        const uint32_t u = sub + (uint32_t)m;
+                        ok = warp_wait(smem_u32(&ps.tempty[u & 1u]), ((u >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
                                        CBK_TIMEOUT_TMEM_EMPTY);
-                        if (!ok) break;
-                        tc_fence_after();
                     }
-                    if (lane == 0) {
-                        const uint32_t d_tmem = tmem_base + a * acc_stride;
-                        const uint32_t pm = sP + (uint32_t)m * (uint32_t)kPTileBytes;
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (lane == 0) {
+                    const uint64_t dQ = descQ0 + (uint64_t)(((sP + p_bytes) >> 4) & 0x3FFFu);
+                    const uint32_t first = chunk_first ? 0u : 1u;
+                    for (int m = 0; m < p.mi; ++m) {
+                        const uint32_t d_tmem = tmem_base + ((sub + (uint32_t)m) & 1u) * acc_stride;
+                        const uint64_t dP = descP0 + (uint64_t)(((sP + (uint32_t)m * (uint32_t)kPTileBytes) >> 4) & 0x3FFFu);
+                        if (X3) {
 #pragma unroll
-                        for (int kk = 0; kk < kBK / 8; ++kk) {
-                            const uint32_t p_off = P_MN ? kk * 1024u : kk * 32u;
-                            const uint32_t q_off = Q_MN ? kk * 1024u : kk * 32u;
-                            const uint64_t dP = P_MN ? desc_mn(pm + p_off) : desc_k(pm + p_off);
-                            const uint64_t dQ = Q_MN ? desc_mn(sQ + q_off) : desc_k(sQ + q_off);
-                            const uint32_t first = (chunk_first && kk == 0) ? 0u : 1u;
-                            // Consecutive UMMAs into the same accumulator columns serialise on that accumulator; two
-                            // half-N instructions into disjoint column ranges alternate and overlap.
-                            for (uint32_t h = 0; h < (uint32_t)p.nsplit; ++h) {
-                                const uint32_t dh = d_tmem + h * nh;
-                                const uint64_t qh = (uint64_t)((h * nh * 128u) >> 4);  // rows h*nh of the Q tile
-                                if (X3) {
-                                    const uint64_t dPl = P_MN ? desc_mn(pm + hi_bytes + p_off) : desc_k(pm + hi_bytes + p_off);
-                                    const uint64_t dQl = Q_MN ? desc_mn(sQ + hi_bytes + q_off) : desc_k(sQ + hi_bytes + q_off);
-                                    umma_tf32(dh, dP, dQl + qh, idesc, first);
-                                    umma_tf32(dh, dPl, dQ + qh, idesc, 1u);
-                                    umma_tf32(dh, dP, dQ + qh, idesc, 1u);
-                                } else {
-                                    umma_tf32(dh, dP, dQ + qh, idesc, first);
-                                }
+                            for (int kk = 0; kk < kBK / 8; ++kk) {
+                                const uint64_t a = dP + kk * kStepP, b = dQ + kk * kStepQ;
+                                umma_tf32(d_tmem, a, b + lo_units, idesc, kk == 0 ? first : 1u);
+                                umma_tf32(d_tmem, a + lo_units, b, idesc, 1u);
+                                umma_tf32(d_tmem, a, b, idesc, 1u);
                             }
+                        } else {
+                            umma_tf32(d_tmem, dP, dQ, idesc, first);
+                            umma_tf32(d_tmem, dP + kStepP, dQ + kStepQ, idesc, 1u);
+                            umma_tf32(d_tmem, dP + 2 * kStepP, dQ + 2 * kStepQ, idesc, 1u);
+                            umma_tf32(d_tmem, dP + 3 * kStepP, dQ + 3 * kStepQ, idesc, 1u);
                         }
                     }
-                    __syncwarp();
-                }
-                if (!ok) break;
-                if (lane == 0) {
                     tc_commit(smem_u32(&ps.empty[s]));  // stage reusable once these MMAs retire
                     if (chunk_last)
                         for (int m = 0; m < p.mi; ++m) tc_commit(smem_u32(&ps.tfull[(sub + m) & 1u]));
@@ -619,7 +614,6 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     int cols = 32;
     while (cols < 2 * gp.bn) cols <<= 1;
     gp.tmem_cols = cols;
-    { const char* e = getenv("CB_NSPLIT"); gp.nsplit = (e && atoi(e) == 2 && gp.bn % 64 == 0) ? 2 : 1; }
     gp.p_batched = (g.batch > 1 && g.strideP != 0) ? 1 : 0;
     gp.q_batched = (g.batch > 1 && g.strideQ != 0) ? 1 : 0;
     gp.C = g.C; gp.ldc = g.ldc; gp.strideC = g.strideC;

@@ -194,6 +194,199 @@ __global__ void bn_paramgrad_kernel(const float* __restrict__ dY, const float* _
     }
 }
 
+
+// ------------------------------------------------------------------ BatchNorm, batch-parallel form
+// Block = 16 float4 position vectors (64 positions, 256 contiguous bytes per sample) x 16 batch groups. Every thread
+// keeps its SPT samples (n = group, group + 16, ...) in registers, so X (and dY) are read from HBM exactly once;
+// the per-position sums are combined across the 16 groups through shared memory in a fixed order. This fills the GPU
+// where the one-thread-per-position form leaves it with P/4 threads (4096 for a 16x32x32 map).
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 f4_zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+
+// sum over the 16 batch groups of the block; every thread returns the total of its position vector
+__device__ __forceinline__ float4 bn_group_sum(float4 v, float4 (*red)[16]) {
+    red[threadIdx.y][threadIdx.x] = v;
+    __syncthreads();
+    float4 t = f4_zero();
+#pragma unroll
+    for (int g = 0; g < 16; ++g) t = f4_add(t, red[g][threadIdx.x]);
+    __syncthreads();
+    return t;
+}
+
+template <int SPT>
+__global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict__ X, const float* __restrict__ beta,
+                                                         const float* __restrict__ gamma, float* __restrict__ mean,
+                                                         float* __restrict__ var, float* __restrict__ Y,
+                                                         float* __restrict__ xhat, int N, long long P) {
+    __shared__ float4 red[16][16];
+    const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
+    const bool live = p < P;
+    const int g = threadIdx.y;
+    float4 x[SPT];
+    float4 s = f4_zero();
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        const int n = g + 16 * i;
+        x[i] = (live && n < N) ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
+        s = f4_add(s, x[i]);
+    }
+    const float invN = 1.0f / (float)N;
+    float4 m = bn_group_sum(s, red);
+    m = make_float4(m.x * invN, m.y * invN, m.z * invN, m.w * invN);
+    float4 q = f4_zero();
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        if (g + 16 * i < N) {
+            const float a = x[i].x - m.x, b = x[i].y - m.y, c = x[i].z - m.z, d = x[i].w - m.w;
+            q = f4_add(q, make_float4(a * a, b * b, c * c, d * d));
+        }
+    }
+    float4 v = bn_group_sum(q, red);
+    v = make_float4(v.x * invN, v.y * invN, v.z * invN, v.w * invN);
+    if (!live) return;
+    const float4 inv = make_float4(1.0f / sqrtf(v.x + 1e-8f), 1.0f / sqrtf(v.y + 1e-8f), 1.0f / sqrtf(v.z + 1e-8f),
+                                   1.0f / sqrtf(v.w + 1e-8f));
+    const float4 ga = *reinterpret_cast<const float4*>(gamma + p), be = *reinterpret_cast<const float4*>(beta + p);
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        const int n = g + 16 * i;
+        if (n < N) {
+            const float4 h = make_float4((x[i].x - m.x) * inv.x, (x[i].y - m.y) * inv.y, (x[i].z - m.z) * inv.z,
+                                         (x[i].w - m.w) * inv.w);
+            *reinterpret_cast<float4*>(Y + (long long)n * P + p) =
+                make_float4(h.x * ga.x + be.x, h.y * ga.y + be.y, h.z * ga.z + be.z, h.w * ga.w + be.w);
+            if (xhat) *reinterpret_cast<float4*>(xhat + (long long)n * P + p) = h;
+        }
+    }
+    if (g == 0) {
+        if (mean) *reinterpret_cast<float4*>(mean + p) = m;
+        if (var) *reinterpret_cast<float4*>(var + p) = v;
+    }
+}
+
+// Data gradient (statistics recomputed from X as seblas::batchNormGrad does) and, when dgamma / dbeta are given, the
+// parameter gradients dbeta = sum dy, dgamma = sum dy * xhat of seblas::batchNormParamGrads in the same pass.
+template <int SPT>
+__global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
+                                                         const float* __restrict__ X, float* __restrict__ dX,
+                                                         float* __restrict__ dgamma, float* __restrict__ dbeta, int N,
+                                                         long long P) {
+    __shared__ float4 red[16][16];
+    const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
+    const bool live = p < P;
+    const int g = threadIdx.y;
+    float4 x[SPT], dy[SPT];
+    float4 s = f4_zero();
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        const int n = g + 16 * i;
+        const bool on = live && n < N;
+        x[i] = on ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
+        dy[i] = on ? *reinterpret_cast<const float4*>(dY + (long long)n * P + p) : f4_zero();
+        s = f4_add(s, x[i]);
+    }
+    const float invN = 1.0f / (float)N;
+    float4 m = bn_group_sum(s, red);
+    m = make_float4(m.x * invN, m.y * invN, m.z * invN, m.w * invN);
+    const float4 ga = live ? *reinterpret_cast<const float4*>(gamma + p) : f4_zero();
+    float4 sq = f4_zero(), sdx = f4_zero(), sd = f4_zero(), sxc = f4_zero();
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        if (g + 16 * i < N) {
+            const float4 xc = make_float4(x[i].x - m.x, x[i].y - m.y, x[i].z - m.z, x[i].w - m.w);
+            x[i] = xc;  // keep the centred value
+            sq = f4_add(sq, make_float4(xc.x * xc.x, xc.y * xc.y, xc.z * xc.z, xc.w * xc.w));
+            sdx = f4_add(sdx, make_float4(dy[i].x * xc.x, dy[i].y * xc.y, dy[i].z * xc.z, dy[i].w * xc.w));
+            sd = f4_add(sd, dy[i]);
+            sxc = f4_add(sxc, xc);
+        }
+    }
+    sq = bn_group_sum(sq, red);
+    sdx = bn_group_sum(sdx, red);   // sum dy * xc   (dxhat = dy * gamma is factored out below)
+    sd = bn_group_sum(sd, red);     // sum dy
+    sxc = bn_group_sum(sxc, red);
+    if (!live) return;
+    float o_inv[4], o_dvar[4], o_dmean[4];
+    const float sqv[4] = {sq.x, sq.y, sq.z, sq.w}, sdxv[4] = {sdx.x, sdx.y, sdx.z, sdx.w}, sdv[4] = {sd.x, sd.y, sd.z, sd.w},
+                sxcv[4] = {sxc.x, sxc.y, sxc.z, sxc.w}, gav[4] = {ga.x, ga.y, ga.z, ga.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float inv = 1.0f / sqrtf(sqv[e] * invN + 1e-8f);
+        o_inv[e] = inv;
+        o_dvar[e] = gav[e] * sdxv[e] * -0.5f * inv * inv * inv;
+        o_dmean[e] = -gav[e] * sdv[e] * inv + o_dvar[e] * (-2.0f * sxcv[e]) * invN;
+    }
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+        const int n = g + 16 * i;
+        if (n < N) {
+            float4 o;
+            o.x = dy[i].x * gav[0] * o_inv[0] + o_dvar[0] * x[i].x * 2.0f * invN + o_dmean[0] * invN;
+            o.y = dy[i].y * gav[1] * o_inv[1] + o_dvar[1] * x[i].y * 2.0f * invN + o_dmean[1] * invN;
+            o.z = dy[i].z * gav[2] * o_inv[2] + o_dvar[2] * x[i].z * 2.0f * invN + o_dmean[2] * invN;
+            o.w = dy[i].w * gav[3] * o_inv[3] + o_dvar[3] * x[i].w * 2.0f * invN + o_dmean[3] * invN;
+            *reinterpret_cast<float4*>(dX + (long long)n * P + p) = o;
+        }
+    }
+    if (g == 0 && dgamma && dbeta) {
+        *reinterpret_cast<float4*>(dbeta + p) = sd;
+        *reinterpret_cast<float4*>(dgamma + p) =
+            make_float4(sdx.x * o_inv[0], sdx.y * o_inv[1], sdx.z * o_inv[2], sdx.w * o_inv[3]);  // sum dy * xhat
+    }
+}
+
+// Parameter gradients alone (seblas::batchNormParamGrads): one pass over dY and xhat, batch-parallel.
+__global__ void __launch_bounds__(256) bn_paramgrad_par_kernel(const float* __restrict__ dY, const float* __restrict__ xhat,
+                                                               float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                               int N, long long P) {
+    __shared__ float4 red[16][16];
+    const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
+    const bool live = p < P;
+    float4 sg = f4_zero(), sb = f4_zero();
+    if (live) {
+        for (int n = threadIdx.y; n < N; n += 16) {
+            const float4 h = *reinterpret_cast<const float4*>(xhat + (long long)n * P + p);
+            const float4 d = *reinterpret_cast<const float4*>(dY + (long long)n * P + p);
+            sb = f4_add(sb, d);
+            sg = f4_add(sg, make_float4(d.x * h.x, d.y * h.y, d.z * h.z, d.w * h.w));
+        }
+    }
+    sg = bn_group_sum(sg, red);
+    sb = bn_group_sum(sb, red);
+    if (live && threadIdx.y == 0) {
+        *reinterpret_cast<float4*>(dgamma + p) = sg;
+        *reinterpret_cast<float4*>(dbeta + p) = sb;
+    }
+}
+
+// samples per thread for the batch-parallel kernels: smallest power of two >= ceil(N / 16), 0 when N > 256
+inline int bn_spt(int N) {
+    const int need = (N + 15) / 16;
+    for (int s = 1; s <= 16; s <<= 1)
+        if (s >= need) return s;
+    return 0;
+}
+
+template <int SPT>
+void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
+                       float* xhat, int N, long long P) {
+    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
+}
+template <int SPT>
+void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                       float* dbeta, int N, long long P) {
+    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, N, P);
+}
+#define BN_SPT_SWITCH(spt, CALL)            \
+    switch (spt) {                          \
+        case 1: CALL(1); break;             \
+        case 2: CALL(2); break;             \
+        case 4: CALL(4); break;             \
+        case 8: CALL(8); break;             \
+        default: CALL(16); break;           \
+    }
+
 // ------------------------------------------------------------------ elementwise
 enum { OP_RELU, OP_RELU_GRAD, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_ADDS, OP_SUBS, OP_MULS, OP_DIVS, OP_FILL,
        OP_ADD_ZERO_B };
@@ -430,6 +623,13 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
     if (N == 0 || P == 0) return CB_OK;
     if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd: null operand");
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(Y) && (!xhat || aligned16(xhat));
+    const int spt = bn_spt(N);
+    if (vec && spt > 0 && aligned16(beta) && aligned16(gamma) && (!mean || aligned16(mean)) && (!var || aligned16(var))) {
+#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, N, P)
+        BN_SPT_SWITCH(spt, CB_CALL)
+#undef CB_CALL
+        return done(ctx, "cb_bn_fwd");
+    }
     if (vec) bn_fwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
     else bn_fwd_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
     return done(ctx, "cb_bn_fwd");
@@ -441,6 +641,13 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
     if (N == 0 || P == 0) return CB_OK;
     if (!dY || !gamma || !X || !dX) return fail(ctx, CB_EINVAL, "cb_bn_bwd: null operand");
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
+    const int spt = bn_spt(N);
+    if (vec && spt > 0 && aligned16(gamma)) {
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, N, P)
+        BN_SPT_SWITCH(spt, CB_CALL)
+#undef CB_CALL
+        return done(ctx, "cb_bn_bwd");
+    }
     if (vec) bn_bwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(dY, gamma, X, dX, N, P);
     else bn_bwd_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(dY, gamma, X, dX, N, P);
     return done(ctx, "cb_bn_bwd");
@@ -452,9 +659,29 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
     if (P == 0) return CB_OK;
     if (!dY || !xhat || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_paramgrad: null operand");
     const bool vec = (P % 4 == 0) && aligned16(xhat) && aligned16(dY);
+    if (vec && aligned16(dgamma) && aligned16(dbeta)) {
+        bn_paramgrad_par_kernel<<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, xhat, dgamma, dbeta, N, P);
+        return done(ctx, "cb_bn_paramgrad");
+    }
     if (vec) bn_paramgrad_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(dY, xhat, dgamma, dbeta, N, P);
     else bn_paramgrad_kernel<1><<<grid_for(ctx, P, 128), 128, 0, ctx->stream>>>(dY, xhat, dgamma, dbeta, N, P);
     return done(ctx, "cb_bn_paramgrad");
+}
+
+int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                    float* dbeta, int N, long long P) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
+    if (N == 0 || P == 0) return CB_OK;
+    if (!dY || !gamma || !X || !dX || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: null operand");
+    const int spt = bn_spt(N);
+    const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
+                    aligned16(dgamma) && aligned16(dbeta);
+    if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, N, P)
+    BN_SPT_SWITCH(spt, CB_CALL)
+#undef CB_CALL
+    return done(ctx, "cb_bn_bwd_fused");
 }
 
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n) {

@@ -105,7 +105,9 @@ int add_bn(cbt_model* m, int in) {
     const long long p = (long long)x.c * x.h * x.w;
     o.w_off = add_param(m, p, 0, 1, 1, x.c, x.h, x.w);   // gamma, shape (1,C,H,W): BatchNorm.cuh:27-33
     o.b_off = add_param(m, p, 0, 2, 1, x.c, x.h, x.w);   // beta
-    o.xhat = new_tensor(m, x.n, x.c, x.h, x.w);
+    // x-hat is only stored when the fused backward (which recomputes it from X) cannot serve this shape
+    const bool fused = x.n <= 256 && (p % 4) == 0;
+    o.xhat = fused ? -1 : new_tensor(m, x.n, x.c, x.h, x.w);
     o.out = new_tensor(m, x.n, x.c, x.h, x.w);
     m->ops.push_back(o);
     return o.out;
@@ -355,8 +357,8 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                                     o.stride, o.pad, o.pad, 0));
                 break;
             case OP_BN:
-                CBT_TRY(cb_bn_fwd(ctx, x.a, m->P + o.b_off, m->P + o.w_off, nullptr, nullptr, y.a, m->t[o.xhat].a, x.n,
-                                  (long long)x.c * x.h * x.w));
+                CBT_TRY(cb_bn_fwd(ctx, x.a, m->P + o.b_off, m->P + o.w_off, nullptr, nullptr, y.a,
+                                  o.xhat >= 0 ? m->t[o.xhat].a : nullptr, x.n, (long long)x.c * x.h * x.w));
                 break;
             case OP_RELU: CBT_TRY(cb_relu(ctx, x.a, y.a, x.size())); break;
             case OP_ADD: {
@@ -434,9 +436,14 @@ int cbt_backward(cbt_model* m) {
                 continue;
             }
             case OP_BN:
-                CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, m->G + o.w_off, m->G + o.b_off, x.n,
-                                        (long long)x.c * x.h * x.w));
-                CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, (long long)x.c * x.h * x.w));
+                if (o.xhat < 0) {
+                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, m->G + o.w_off, m->G + o.b_off, x.n,
+                                            (long long)x.c * x.h * x.w));
+                } else {
+                    CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, m->G + o.w_off, m->G + o.b_off, x.n,
+                                            (long long)x.c * x.h * x.w));
+                    CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, (long long)x.c * x.h * x.w));
+                }
                 break;
             case OP_CONV:
                 CBT_TRY(cb_conv_wgrad(ctx, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,

@@ -120,6 +120,11 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
               float* xhat, int N, long long P);
 int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, int N, long long P);
 int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgamma, float* dbeta, int N, long long P);
+/* batchNormGrad and batchNormParamGrads (seblas/operations/cuBatchNorm.cu:64-147) in one pass over X and dY: dX,
+ * dgamma = sum dy * xhat and dbeta = sum dy (assigned), with xhat recomputed from X so it need not be stored.
+ * Needs N <= 256, P % 4 == 0 and 16-byte aligned tensors (CB_EUNSUPPORTED otherwise: use the two calls). */
+int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                    float* dbeta, int N, long long P);
 
 /* seblas::relu / reluGradFast (seblas/operations/cuActivation.cu:268,296). */
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n);

@@ -74,7 +74,8 @@ def test_golden_linear(torch_cuda, ctxs, golden):
         assert orc.max_err_norm(dW.cpu().numpy(), golden[name + "/dW"]) <= 2e-5
 
 
-@pytest.mark.parametrize("shape", [(8, 3, 5, 5), (128, 16, 32, 32), (96, 7, 3, 3), (130, 64, 8, 8), (2, 1, 1, 1)])
+@pytest.mark.parametrize("shape", [(8, 3, 5, 5), (128, 16, 32, 32), (96, 7, 3, 3), (130, 64, 8, 8), (2, 1, 1, 1), (16, 32, 16, 16),
+                                   (300, 4, 4, 4), (64, 342, 8, 8)])
 def test_batchnorm(torch_cuda, ctxs, shape):
     """Statistics per (c,h,w) over the batch; batch sizes above the reference's limit of 96 are accepted."""
     torch = torch_cuda
@@ -100,6 +101,14 @@ def test_batchnorm(torch_cuda, ctxs, shape):
     rdg, rdb = orc.bn_paramgrad(dY, xh.cpu().numpy())
     assert orc.max_err_norm(dg.cpu().numpy().ravel(), rdg) <= F32
     assert orc.max_err_norm(db.cpu().numpy().ravel(), rdb) <= F32
+    # the fused backward (dX, dgamma, dbeta in one pass, x-hat recomputed) agrees with the two separate calls
+    if shape[0] <= 256 and np.prod(shape[1:]) % 4 == 0:
+        dX2 = torch.full(shape, float("nan"), device="cuda")
+        dg2, db2 = (torch.full(shape[1:], float("nan"), device="cuda") for _ in range(2))
+        ctx.batchNormGradFused(dev(torch, dY), dev(torch, g), dev(torch, X), dX2, dg2, db2)
+        assert np.abs(dX2.cpu().numpy() - ref_dX).max() <= 2e-5 * max(np.abs(ref_dX).max(), term)
+        assert orc.max_err_norm(dg2.cpu().numpy().ravel(), rdg) <= 2e-5
+        assert orc.max_err_norm(db2.cpu().numpy().ravel(), rdb) <= F32
 
 
 def test_golden_batchnorm(torch_cuda, ctxs, golden):
