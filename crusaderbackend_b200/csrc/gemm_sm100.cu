@@ -3,8 +3,8 @@
 // One persistent, warp-specialised kernel computes D[i][j] = sum_k P[i][k] * Q[j][k]:
 //   warp 0      TMA producer: cp.async.bulk.tensor tiles into 128B-swizzled shared memory, mbarrier pipeline
 //   warp 1      UMMA issuer: one lane issues tcgen05.mma kind::tf32 (M=128, N=bn, K=8), accumulators in TMEM
-//   warps 2..5  epilogue: tcgen05.ld -> registers -> bias/ReLU -> global stores (one TMEM lane quarter each)
-//   warps 6..9  (3xTF32 only) split warps: write lo = a - tf32(a) beside each stage
+//   warps 2..17 epilogue: tcgen05.ld -> registers -> bias/ReLU -> global stores (four warps per TMEM lane quarter)
+//   warps 18..21 (3xTF32 only) split warps: write lo = a - tf32(a) beside each stage
 // P is the operand on the UMMA M side (128 TMEM lanes), Q the one on the N side (TMEM columns). Each operand
 // is either K-major (k contiguous in memory) or MN-major (i / j contiguous); both are fed by TMA without
 // a transpose: K-major tiles are [rows][32 k] boxes (128B swizzle), MN-major tiles are [32 k][32 rows] boxes
@@ -27,6 +27,7 @@ namespace cb {
 namespace {
 
 constexpr int kMaxStages = 8;
+constexpr int kEpiWarps = 16;     // epilogue warps (4 per TMEM lane quarter)
 constexpr int kBK = 32;            // fp32 elements per k-block = one 128-byte swizzle row
 constexpr int kPTileBytes = 128 * kBK * 4;
 
@@ -99,7 +100,7 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
 }
 
 template <bool P_MN, bool Q_MN, bool X3>
-__global__ void __launch_bounds__(X3 ? 320 : 192, 1)
+__global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEpiWarps, 1)
     umma_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                      const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ps.tfull[a]), 1);
-            mbar_init(smem_u32(&ps.tempty[a]), 128);
+            mbar_init(smem_u32(&ps.tempty[a]), 32 * kEpiWarps);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tmP);
@@ -259,9 +260,13 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + kEpiWarps) {
         // ------------------------------------------------------------ epilogue (TMEM -> global)
+        // One warp per scheduler cannot hide the latencies of the epilogue's loads and stores (in 3xTF32 mode the
+        // read-modify-write drains sit on the critical path), so each TMEM lane quarter is served by four warps that
+        // split the column chunks between them.
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+        const int slot = (warp - 2) >> 2;
         uint32_t sub = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
@@ -283,7 +288,7 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
                     float bi = 0.f;
                     if (p.bias_i != nullptr && i_ok && add_bias) bi = p.bias_i[i];
                     const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
-                    for (int c = 0; c < p.bn; c += 16) {
+                    for (int c = slot * 16; c < p.bn; c += 16 * (kEpiWarps / 4)) {
                         if (it.j0 + c >= p.J) break;  // warp-uniform
                         uint32_t r[16];
                         tmem_ld16(t_row + (uint32_t)c, r);
@@ -333,7 +338,7 @@ __global__ void __launch_bounds__(X3 ? 320 : 192, 1)
     } else {
         // ------------------------------------------------------------ split warps (3xTF32 only)
         if (X3) {
-            const int t = threadIdx.x - 192;  // 0..127
+            const int t = threadIdx.x - (64 + 32 * kEpiWarps);  // 0..127
             uint32_t s = 0, ph = 0;
             bool ok = true;
             const uint32_t n_vec = hi_bytes >> 4;
@@ -530,12 +535,12 @@ cudaError_t launch_variant(bool x3, dim3 grid, size_t smem, cudaStream_t st, con
         e = cudaFuncSetAttribute(umma_gemm_kernel<P_MN, Q_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem);
         if (e != cudaSuccess) return e;
-        umma_gemm_kernel<P_MN, Q_MN, true><<<grid, 320, smem, st>>>(tp, tq, gp);
+        umma_gemm_kernel<P_MN, Q_MN, true><<<grid, 64 + 32 * kEpiWarps + 128, smem, st>>>(tp, tq, gp);
     } else {
         e = cudaFuncSetAttribute(umma_gemm_kernel<P_MN, Q_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem);
         if (e != cudaSuccess) return e;
-        umma_gemm_kernel<P_MN, Q_MN, false><<<grid, 192, smem, st>>>(tp, tq, gp);
+        umma_gemm_kernel<P_MN, Q_MN, false><<<grid, 64 + 32 * kEpiWarps, smem, st>>>(tp, tq, gp);
     }
     return cudaGetLastError();
 }
