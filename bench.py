@@ -237,7 +237,7 @@ def bench_ours(args):
                          "nominal_tf32_tflops": 1100.0},
             "tflops_by_shape": detail,
         }
-        line["cpu_baseline"] = None if args.no_cpu else cpu_baseline_leg()
+        line["cpu_baseline"] = None if (args.no_cpu or world > 1) else cpu_baseline_leg()  # rank 0 at N = 1 only
         if not args.no_cpu and world == 1:
             try:
                 line["reference_cuda"] = reference_cuda_leg()
@@ -252,6 +252,9 @@ def bench_ours(args):
     if (not args.shapes or args.resnet) and not args.no_resnet:
         try:
             extra_resnet = resnet56_section(torch, local, world, max(args.steps, 5), args.warmup)
+            if world > 1:
+                extra_resnet["weak_scaling_128_per_gpu"] = resnet56_section(torch, local, world, max(args.steps, 5),
+                                                                            args.warmup, weak=True)
         except Exception as exc:  # keep the headline line even if the training section fails
             extra_resnet = {"error": str(exc)[:300]}
     if rank == 0:
@@ -309,7 +312,7 @@ def conv_section(ctx, torch, dev, flush, only=None):
     return out
 
 
-def resnet56_section(torch, local, world, steps, warmup):
+def resnet56_section(torch, local, world, steps, warmup, weak=False):
     """ResNet-56 training step (forward + backward + gradient allreduce + Momentum), global batch 128 split over the
     ranks (strong scaling, the configuration of the specification), replayed as one CUDA graph. Each timed step
     includes the host->device copy of that step's images and labels from pinned memory and ends with a device->host
@@ -318,7 +321,7 @@ def resnet56_section(torch, local, world, steps, warmup):
     from crusaderbackend_b200.train import ResNetTrainer
     from crusaderbackend_b200 import dp
     from oracle import oracle as orc
-    gb = 128
+    gb = 128 * world if weak else 128   # weak: 128 images per GPU; strong (the spec's configuration): 128 in total
     rank = int(os.environ.get("RANK", "0"))
     start, count = dp.shard_batch(gb, world, rank)
     ctx = Context(local, math="tf32", sync=False)
@@ -367,10 +370,10 @@ def resnet56_section(torch, local, world, steps, warmup):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms = float(t.item())
     res = {"images_per_s": round(gb / ms * 1e3, 1), "ms_per_step": round(ms, 3), "global_batch": gb,
-           "per_gpu_batch": count, "scaling": "strong", "math": "tf32", "kernels_per_step": int(launches),
+           "per_gpu_batch": count, "scaling": "weak" if weak else "strong", "math": "tf32", "kernels_per_step": int(launches),
            "cuda_graph": True, "loss_mean_last": round(float(h_loss.item()) / count, 5),
            "h2d_bytes_per_step": int(h_img.numel() * 4 + h_lab.numel() * 4), "d2h_bytes_per_step": 4,
-           "flops_per_step": 96.5e9,
+           "flops_per_step": 96.5e9 * gb / 128,
            "note": "forward+backward+allreduce+Momentum; BatchNorm statistics are per GPU shard"}
     tr.close()
     ctx.close()
@@ -401,6 +404,7 @@ SAMPLE_TEXT = "sweep subset: {1024,2048}^3 x {NN,NT,TN} + 4096^3 NN + 128x10x409
 def cpu_baseline_leg():
     """OpenMP fp32 port of the same GEMMs on the host cores, bounded to roughly ten seconds."""
     from oracle import oracle as orc
+    orc.use_all_cores()
     ops = cpu_operands(orc)
     cpu_pass(orc, ops[:3])  # warm the thread pool
     total, reps = 0.0, 0
@@ -466,6 +470,7 @@ def bench_reference(args):
     if rank != 0:
         return
     from oracle import oracle as orc
+    orc.use_all_cores()
     ops = cpu_operands(orc)
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_pass(orc, ops)

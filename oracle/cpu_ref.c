@@ -24,6 +24,15 @@
 
 typedef long long i64;
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline asks for the cores it is meant to use. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

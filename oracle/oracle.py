@@ -45,6 +45,15 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Sets the OpenMP team to every core this process may run on (launchers often export OMP_NUM_THREADS=1)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads.argtypes = [_i]
+    lib().orc_set_num_threads(n)
+    return num_threads()
+
+
 def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
