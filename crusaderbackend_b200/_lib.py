@@ -46,7 +46,10 @@ SIGNATURES = {
     "cb_bn_fwd": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_bwd": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_paramgrad": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
-    "cb_bn_bwd_fused": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_bwd_fused": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_fwd_relu": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
+    "cb_add_relu": (_i, [_ctx, _f, _f, _f, _ll]),
+    "cb_relu_grad2": (_i, [_ctx, _f, _f, _f, _f, _ll]),
     "cb_relu": (_i, [_ctx, _f, _f, _ll]),
     "cb_relu_grad": (_i, [_ctx, _f, _f, _f, _ll]),
     "cb_tensor_op": (_i, [_ctx, _i, _f, _f, _fl, _ll]),

@@ -191,11 +191,24 @@ class Context:
         self._check(self.lib.cb_bn_paramgrad(self.h, _ptr(dY), _ptr(xHat), _ptr(dGamma), _ptr(dBeta), N,
                                              dY.numel() // N))
 
-    def batchNormGradFused(self, dY, gamma, X, dX, dGamma, dBeta):
+    def batchNormGradFused(self, dY, gamma, X, dX, dGamma, dBeta, relu_out=None):
         N = X.shape[0]
-        self._check(self.lib.cb_bn_bwd_fused(self.h, _ptr(dY), _ptr(gamma), _ptr(X), _ptr(dX), _ptr(dGamma), _ptr(dBeta), N,
-                                             X.numel() // N))
+        self._check(self.lib.cb_bn_bwd_fused(self.h, _ptr(dY), _ptr(gamma), _ptr(X), _ptr(dX), _ptr(dGamma), _ptr(dBeta),
+                                             _ptr(relu_out), N, X.numel() // N))
         return dX
+
+    def batchNormRelu(self, X, beta, gamma, Y):
+        N = X.shape[0]
+        self._check(self.lib.cb_bn_fwd_relu(self.h, _ptr(X), _ptr(beta), _ptr(gamma), _ptr(Y), N, X.numel() // N))
+        return Y
+
+    def addRelu(self, A, B, Out):
+        self._check(self.lib.cb_add_relu(self.h, _ptr(A), _ptr(B), _ptr(Out), A.numel()))
+        return Out
+
+    def reluGrad2(self, Y, dY, dA, dB=None):
+        self._check(self.lib.cb_relu_grad2(self.h, _ptr(Y), _ptr(dY), _ptr(dA), _ptr(dB), Y.numel()))
+        return dA
 
     def relu(self, X, Y):
         self._check(self.lib.cb_relu(self.h, _ptr(X), _ptr(Y), X.numel()))

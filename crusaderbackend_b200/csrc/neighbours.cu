@@ -218,7 +218,7 @@ template <int SPT>
 __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict__ X, const float* __restrict__ beta,
                                                          const float* __restrict__ gamma, float* __restrict__ mean,
                                                          float* __restrict__ var, float* __restrict__ Y,
-                                                         float* __restrict__ xhat, int N, long long P) {
+                                                         float* __restrict__ xhat, int N, long long P, int relu) {
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -254,8 +254,9 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
         if (n < N) {
             const float4 h = make_float4((x[i].x - m.x) * inv.x, (x[i].y - m.y) * inv.y, (x[i].z - m.z) * inv.z,
                                          (x[i].w - m.w) * inv.w);
-            *reinterpret_cast<float4*>(Y + (long long)n * P + p) =
-                make_float4(h.x * ga.x + be.x, h.y * ga.y + be.y, h.z * ga.z + be.z, h.w * ga.w + be.w);
+            float4 y = make_float4(h.x * ga.x + be.x, h.y * ga.y + be.y, h.z * ga.z + be.z, h.w * ga.w + be.w);
+            if (relu) y = make_float4(fmaxf(y.x, 0.f), fmaxf(y.y, 0.f), fmaxf(y.z, 0.f), fmaxf(y.w, 0.f));
+            *reinterpret_cast<float4*>(Y + (long long)n * P + p) = y;
             if (xhat) *reinterpret_cast<float4*>(xhat + (long long)n * P + p) = h;
         }
     }
@@ -270,8 +271,8 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
 template <int SPT>
 __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
                                                          const float* __restrict__ X, float* __restrict__ dX,
-                                                         float* __restrict__ dgamma, float* __restrict__ dbeta, int N,
-                                                         long long P) {
+                                                         float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                         const float* __restrict__ relu_out, int N, long long P) {
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -284,6 +285,11 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
         const bool on = live && n < N;
         x[i] = on ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
         dy[i] = on ? *reinterpret_cast<const float4*>(dY + (long long)n * P + p) : f4_zero();
+        if (relu_out && on) {  // the ReLU that followed this layer in the forward pass: dy passes where its output is > 0
+            const float4 r = *reinterpret_cast<const float4*>(relu_out + (long long)n * P + p);
+            dy[i] = make_float4(r.x > 0.f ? dy[i].x : 0.f, r.y > 0.f ? dy[i].y : 0.f, r.z > 0.f ? dy[i].z : 0.f,
+                                r.w > 0.f ? dy[i].w : 0.f);
+        }
         s = f4_add(s, x[i]);
     }
     const float invN = 1.0f / (float)N;
@@ -370,13 +376,14 @@ inline int bn_spt(int N) {
 
 template <int SPT>
 void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
-                       float* xhat, int N, long long P) {
-    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
+                       float* xhat, int N, long long P, int relu) {
+    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P, relu);
 }
 template <int SPT>
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                       float* dbeta, int N, long long P) {
-    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, N, P);
+                       float* dbeta, const float* relu_out, int N, long long P) {
+    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, relu_out, N,
+                                                                                            P);
 }
 #define BN_SPT_SWITCH(spt, CALL)            \
     switch (spt) {                          \
@@ -389,7 +396,7 @@ void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const f
 
 // ------------------------------------------------------------------ elementwise
 enum { OP_RELU, OP_RELU_GRAD, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_ADDS, OP_SUBS, OP_MULS, OP_DIVS, OP_FILL,
-       OP_ADD_ZERO_B };
+       OP_ADD_ZERO_B, OP_ADD_RELU };
 
 template <int OP>
 __device__ __forceinline__ float ew(float a, float b, float c, float s) {
@@ -397,6 +404,7 @@ __device__ __forceinline__ float ew(float a, float b, float c, float s) {
         case OP_RELU: return fmaxf(a, 0.f);
         case OP_RELU_GRAD: return a > 0.f ? b : 0.f;
         case OP_ADD: case OP_ADD_ZERO_B: return a + b;
+        case OP_ADD_RELU: return fmaxf(a + b, 0.f);
         case OP_SUB: return a - b;
         case OP_MUL: return a * b;
         case OP_DIV: return a / b;
@@ -602,6 +610,16 @@ __global__ void momentum_multi_kernel(const MomentumTensor* __restrict__ ts, flo
     }
 }
 
+// dA[i] = dB[i] = (Y[i] > 0 ? dY[i] : 0): the gradient of out = relu(a + b) for both addends (dB may be null)
+__global__ void relu_grad2_kernel(const float* __restrict__ Y, const float* __restrict__ dY, float* __restrict__ dA,
+                                  float* __restrict__ dB, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float g = Y[i] > 0.f ? dY[i] : 0.f;
+        dA[i] = g;
+        if (dB) dB[i] = g;
+    }
+}
+
 int done(cb_ctx* ctx, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
@@ -625,7 +643,7 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(Y) && (!xhat || aligned16(xhat));
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(beta) && aligned16(gamma) && (!mean || aligned16(mean)) && (!var || aligned16(var))) {
-#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, N, P)
+#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, N, P, 0)
         BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
         return done(ctx, "cb_bn_fwd");
@@ -643,7 +661,7 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(gamma)) {
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, N, P)
         BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
         return done(ctx, "cb_bn_bwd");
@@ -669,19 +687,47 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
 }
 
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                    float* dbeta, int N, long long P) {
+                    float* dbeta, const float* relu_out, int N, long long P) {
     if (!ctx) return CB_EINVAL;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!dY || !gamma || !X || !dX || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: null operand");
     const int spt = bn_spt(N);
     const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
-                    aligned16(dgamma) && aligned16(dbeta);
+                    aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out));
     if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, N, P)
     BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
     return done(ctx, "cb_bn_bwd_fused");
+}
+
+int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {
+    if (!ctx) return CB_EINVAL;
+    if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: negative extent");
+    if (N == 0 || P == 0) return CB_OK;
+    if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: null operand");
+    const int spt = bn_spt(N);
+    if (!((P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(Y) && aligned16(beta) && aligned16(gamma)))
+        return fail(ctx, CB_EUNSUPPORTED, "cb_bn_fwd_relu: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
+#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, N, P, 1)
+    BN_SPT_SWITCH(spt, CB_CALL)
+#undef CB_CALL
+    return done(ctx, "cb_bn_fwd_relu");
+}
+
+int cb_add_relu(cb_ctx* ctx, const float* A, const float* B, float* Out, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && (!A || !B || !Out))) return fail(ctx, CB_EINVAL, "cb_add_relu: bad argument");
+    return launch_eltwise<OP_ADD_RELU>(ctx, A, const_cast<float*>(B), Out, 0.f, n, "cb_add_relu");
+}
+
+int cb_relu_grad2(cb_ctx* ctx, const float* Y, const float* dY, float* dA, float* dB, long long n) {
+    if (!ctx) return CB_EINVAL;
+    if (n < 0 || (n > 0 && (!Y || !dY || !dA))) return fail(ctx, CB_EINVAL, "cb_relu_grad2: bad argument");
+    if (n == 0) return CB_OK;
+    relu_grad2_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(Y, dY, dA, dB, n);
+    return done(ctx, "cb_relu_grad2");
 }
 
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n) {

@@ -37,6 +37,7 @@ struct Op {
     long long w_off = -1, b_off = -1;   // offsets into the flat parameter buffer (conv filter / BN gamma / FC weight; BN beta / FC bias)
     int xhat = -1;                      // BN: tensor id of x-hat
     bool in0_grad_accumulate = false;   // backward adds into in0's gradient instead of overwriting it
+    bool relu = false;                  // BN / ADD: a ReLU is folded into this op (out is the activated tensor)
 };
 
 struct ParamEntry {
@@ -113,6 +114,17 @@ int add_bn(cbt_model* m, int in) {
     return o.out;
 }
 
+// BatchNorm followed by ReLU as one op when the fused kernels cover the shape (N <= 256, C*H*W % 4 == 0)
+int add_relu(cbt_model* m, int in);
+int add_bn_relu(cbt_model* m, int in) {
+    const TensorBuf x = m->t[in];
+    const long long p = (long long)x.c * x.h * x.w;
+    if (!(x.n <= 256 && (p % 4) == 0)) return add_relu(m, add_bn(m, in));
+    const int out = add_bn(m, in);
+    m->ops.back().relu = true;
+    return out;
+}
+
 int add_relu(cbt_model* m, int in) {
     const TensorBuf x = m->t[in];
     Op o{};
@@ -129,6 +141,13 @@ int add_add(cbt_model* m, int a, int b) {
     o.out = new_tensor(m, x.n, x.c, x.h, x.w);
     m->ops.push_back(o);
     return o.out;
+}
+
+// out = relu(a + b): the shortcut add and the ReLU after it (archive/Resnet56:14-15) as one op
+int add_add_relu(cbt_model* m, int a, int b) {
+    const int out = add_add(m, a, b);
+    m->ops.back().relu = true;
+    return out;
 }
 
 // channel concatenation [in0 ; in1] (seblas concat, seblas/operations/cuConcat.cu:9-60, as ChannelConcatenater uses it)
@@ -247,17 +266,17 @@ int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_st
     m->ctx = ctx; m->batch = batch; m->classes = classes;
     int x = new_tensor(m, batch, 3, image_hw, image_hw);
     m->input = x;
-    x = add_relu(m, add_bn(m, add_conv(m, x, 16, 3, 1, 1)));
+    x = add_bn_relu(m, add_conv(m, x, 16, 3, 1, 1));
     int ch = 16;
     for (int stage = 0; stage < 3; ++stage) {
         const int oc = 16 << stage;
         for (int b = 0; b < blocks_per_stage; ++b) {
             const int stride = (stage > 0 && b == 0) ? 2 : 1;
-            int y = add_relu(m, add_bn(m, add_conv(m, x, oc, 3, stride, 1)));
+            int y = add_bn_relu(m, add_conv(m, x, oc, 3, stride, 1));
             y = add_bn(m, add_conv(m, y, oc, 3, 1, 1));
             int sc = x;
             if (stride != 1 || ch != oc) sc = add_conv(m, x, oc, 1, stride, 0);  // bare 1x1 projection
-            x = add_relu(m, add_add(m, y, sc));
+            x = add_add_relu(m, y, sc);
             ch = oc;
         }
     }
@@ -278,16 +297,16 @@ int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int
     x = add_conv(m, x, 2 * growth, 3, 1, 1);
     for (int block = 0; block < 3; ++block) {
         for (int l = 0; l < layers; ++l) {
-            int y = add_conv(m, add_relu(m, add_bn(m, x)), 4 * growth, 1, 1, 0);
-            y = add_conv(m, add_relu(m, add_bn(m, y)), growth, 3, 1, 1);
+            int y = add_conv(m, add_bn_relu(m, x), 4 * growth, 1, 1, 0);
+            y = add_conv(m, add_bn_relu(m, y), growth, 3, 1, 1);
             x = add_concat(m, x, y);
         }
         if (block < 2) {
             const int ch = m->t[x].c;
-            x = add_avgpool2(m, add_conv(m, add_relu(m, add_bn(m, x)), ch / 2, 1, 1, 0));
+            x = add_avgpool2(m, add_conv(m, add_bn_relu(m, x), ch / 2, 1, 1, 0));
         }
     }
-    x = add_relu(m, add_bn(m, x));
+    x = add_bn_relu(m, x);
     *out = m;
     return finalize_model(m, x, classes);
 }
@@ -357,12 +376,20 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                                     o.stride, o.pad, o.pad, 0));
                 break;
             case OP_BN:
+                if (o.relu) {
+                    CBT_TRY(cb_bn_fwd_relu(ctx, x.a, m->P + o.b_off, m->P + o.w_off, y.a, x.n, (long long)x.c * x.h * x.w));
+                    break;
+                }
                 CBT_TRY(cb_bn_fwd(ctx, x.a, m->P + o.b_off, m->P + o.w_off, nullptr, nullptr, y.a,
                                   o.xhat >= 0 ? m->t[o.xhat].a : nullptr, x.n, (long long)x.c * x.h * x.w));
                 break;
             case OP_RELU: CBT_TRY(cb_relu(ctx, x.a, y.a, x.size())); break;
             case OP_ADD: {
                 // y = in0 + in1 (ShortcutEndpoint::forward, seann/operands/controlling/ShortcutEndpoint.cu:57-74)
+                if (o.relu) {
+                    CBT_TRY(cb_add_relu(ctx, x.a, m->t[o.in1].a, y.a, y.size()));
+                    break;
+                }
                 e = cudaMemcpyAsync(y.a, x.a, (size_t)x.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
                 if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
                 CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, y.a, m->t[o.in1].a, 0.f, y.size()));
@@ -428,6 +455,11 @@ int cbt_backward(cbt_model* m) {
             case OP_ADD: {
                 // both inputs receive dY (ShortcutEndpoint::xGrads routes the same gradient to the skip path)
                 TensorBuf& x1 = m->t[o.in1];
+                if (o.relu && !o.in0_grad_accumulate) {
+                    CBT_TRY(cb_relu_grad2(ctx, y.a, y.d, x.d, x1.d, y.size()));
+                    continue;
+                }
+                if (o.relu) CBT_TRY(cb_relu_grad2(ctx, y.a, y.d, y.d, nullptr, y.size()));  // mask in place, then route
                 cudaError_t e = cudaMemcpyAsync(x1.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
                 if (e == cudaSuccess && !o.in0_grad_accumulate)
                     e = cudaMemcpyAsync(x.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
@@ -437,8 +469,8 @@ int cbt_backward(cbt_model* m) {
             }
             case OP_BN:
                 if (o.xhat < 0) {
-                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, m->G + o.w_off, m->G + o.b_off, x.n,
-                                            (long long)x.c * x.h * x.w));
+                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, m->G + o.w_off, m->G + o.b_off,
+                                            o.relu ? y.a : nullptr, x.n, (long long)x.c * x.h * x.w));
                 } else {
                     CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, m->G + o.w_off, m->G + o.b_off, x.n,
                                             (long long)x.c * x.h * x.w));

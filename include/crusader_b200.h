@@ -122,13 +122,22 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
 int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgamma, float* dbeta, int N, long long P);
 /* batchNormGrad and batchNormParamGrads (seblas/operations/cuBatchNorm.cu:64-147) in one pass over X and dY: dX,
  * dgamma = sum dy * xhat and dbeta = sum dy (assigned), with xhat recomputed from X so it need not be stored.
- * Needs N <= 256, P % 4 == 0 and 16-byte aligned tensors (CB_EUNSUPPORTED otherwise: use the two calls). */
+ * relu_out (nullable): output of a ReLU that followed this layer in the forward pass; dY is then masked by
+ * relu_out > 0 first (reluGradFast folded in). Needs N <= 256, P % 4 == 0 and 16-byte aligned tensors
+ * (CB_EUNSUPPORTED otherwise: use the separate calls). */
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                    float* dbeta, int N, long long P);
+                    float* dbeta, const float* relu_out, int N, long long P);
+/* Y = relu(batchNorm(X)) in one pass (the BatchNorm -> ReLU pair of the operand graph, seann/operands/seblas/BatchNorm.cu:14
+ * followed by activate/ReLU.cu:8); same limits as cb_bn_bwd_fused. */
+int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P);
 
 /* seblas::relu / reluGradFast (seblas/operations/cuActivation.cu:268,296). */
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n);
 int cb_relu_grad(cb_ctx* ctx, const float* X, const float* dY, float* dX, long long n);
+/* Out = relu(A + B): the shortcut add (seann/operands/controlling/ShortcutEndpoint.cu:57-74) and the ReLU after it in one
+ * pass; and its gradient for both addends, dA = dB = (Y > 0 ? dY : 0) (dB nullable). */
+int cb_add_relu(cb_ctx* ctx, const float* A, const float* B, float* Out, long long n);
+int cb_relu_grad2(cb_ctx* ctx, const float* Y, const float* dY, float* dA, float* dB, long long n);
 
 /* In-place tensor arithmetic of seblas::Tensor (operator+ - * / with a tensor or a scalar, constFill;
  * seblas/tensor/Tensor.cu:462-660): A = A op B or A = A op scalar. */

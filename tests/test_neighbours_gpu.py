@@ -109,6 +109,17 @@ def test_batchnorm(torch_cuda, ctxs, shape):
         assert np.abs(dX2.cpu().numpy() - ref_dX).max() <= 2e-5 * max(np.abs(ref_dX).max(), term)
         assert orc.max_err_norm(dg2.cpu().numpy().ravel(), rdg) <= 2e-5
         assert orc.max_err_norm(db2.cpu().numpy().ravel(), rdb) <= F32
+        # BatchNorm -> ReLU folded: forward relu(bn(X)); backward with dY masked by the ReLU output
+        R = torch.full(shape, float("nan"), device="cuda")
+        ctx.batchNormRelu(dev(torch, X), dev(torch, b), dev(torch, g), R)
+        assert orc.max_err_norm(R.cpu().numpy(), np.maximum(rY, 0)) <= F32
+        dYm = np.where(R.cpu().numpy() > 0, dY, 0).astype(np.float32)
+        ctx.batchNormGradFused(dev(torch, dY), dev(torch, g), dev(torch, X), dX2, dg2, db2, relu_out=R)
+        ref_m = orc.bn_bwd(dYm, g, X)
+        assert np.abs(dX2.cpu().numpy() - ref_m).max() <= 2e-5 * max(np.abs(ref_m).max(), term)
+        rdg_m, rdb_m = orc.bn_paramgrad(dYm, xh.cpu().numpy())
+        assert orc.max_err_norm(dg2.cpu().numpy().ravel(), rdg_m) <= 2e-5
+        assert orc.max_err_norm(db2.cpu().numpy().ravel(), rdb_m) <= F32
 
 
 def test_golden_batchnorm(torch_cuda, ctxs, golden):
@@ -150,6 +161,13 @@ def test_relu_and_tensor_ops_bit_exact(torch_cuda, ctxs, n):
     dA, res = dev(torch, X), dev(torch, dY)
     ctx.grad_handover(dA, res)
     assert np.array_equal(dA.cpu().numpy(), X + dY) and not res.any()
+    out = torch.full((n,), 9.0, device="cuda")
+    ctx.addRelu(dev(torch, X), dev(torch, dY), out)
+    assert np.array_equal(out.cpu().numpy(), np.maximum(X + dY, 0))
+    ga, gb = torch.full((n,), 9.0, device="cuda"), torch.full((n,), 9.0, device="cuda")
+    ctx.reluGrad2(out, dev(torch, dY), ga, gb)
+    want = np.where(np.maximum(X + dY, 0) > 0, dY, 0).astype(np.float32)
+    assert np.array_equal(ga.cpu().numpy(), want) and np.array_equal(gb.cpu().numpy(), want)
 
 
 def test_pooling_softmax_loss(torch_cuda, ctxs, golden):
