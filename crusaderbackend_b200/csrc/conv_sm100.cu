@@ -96,7 +96,9 @@ __device__ __forceinline__ void s2_untap(int f, int& phase, int& t) {
     t = (f == 0) ? 0 : 1;
 }
 
-constexpr int kEpiWarps = 16;  // epilogue warps: 4 per TMEM lane quarter, each taking every 4th chunk of 8 channels
+// Epilogue warps are a template parameter of the kernel: 16 (4 per TMEM lane quarter) for wide outputs, 8 for outputs
+// of at most 32 channels, where two such CTAs share an SM so that their UMMA chains (each serial on its accumulator)
+// overlap.
 
 template <int CH>
 __device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[CH]) {
@@ -149,7 +151,8 @@ __device__ __forceinline__ void conv_epilogue_chunk(const ConvParams& p, uint32_
     }
 }
 
-__global__ void __launch_bounds__(64 + 32 * kEpiWarps, 1)
+template <int kEpiWarps>
+__global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
     umma_conv_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                      const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -477,6 +480,7 @@ struct ConvEnv {
 // Geometry the tensor-core forward / data-gradient kernel covers; fills the derived sizes.
 struct ConvPlan {
     int Cin, Cout, OCp, NQ, CG, L, KS, shared_rows, nblocks, stages;
+    int ew;   // epilogue warps of the kernel instantiation: 8 (two CTAs per SM) or 16
     size_t w_bytes;
     uint32_t block_bytes, stage_bytes;
 };
@@ -499,7 +503,10 @@ static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int Cin, int C
     q.w_bytes = (size_t)FH * q.CG * q.NQ * kRowBytes;
     q.shared_rows = (q.L == 1 && IH % 4 == 0) ? 1 : 0;
     q.nblocks = q.shared_rows ? FH + 3 : FH * 4;
-    const long long cap = (long long)smem_optin - 2048 - (long long)q.w_bytes;
+    // narrow outputs: the 8-epilogue-warp instantiation, sized so that two CTAs fit one SM (shared memory and TMEM halves)
+    q.ew = (q.OCp <= 32 && q.w_bytes <= 40 * 1024) ? 8 : 16;
+    const long long budget = q.ew == 8 ? (long long)(smem_optin < 113 * 1024 ? smem_optin : 113 * 1024) : (long long)smem_optin;
+    const long long cap = budget - 2048 - (long long)q.w_bytes;
     // as many K steps per stage as leaves a pipeline of at least 4 stages (fewer, larger TMA boxes)
     const int cin8 = (q.Cin + 7) / 8;
     q.KS = 0;
@@ -598,12 +605,16 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
+        cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(umma_conv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
         if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel attribute");
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    const int grid = p.tiles < env.sm_count ? p.tiles : env.sm_count;
-    umma_conv_kernel<<<grid, 64 + 32 * kEpiWarps, smem, env.stream>>>(tmIn, tmW, p);
+    const int slots = env.sm_count * (q.ew == 8 ? 2 : 1);  // resident CTAs
+    const int grid = p.tiles < slots ? p.tiles : slots;
+    if (q.ew == 8) umma_conv_kernel<8><<<grid, 64 + 32 * 8, smem, env.stream>>>(tmIn, tmW, p);
+    else umma_conv_kernel<16><<<grid, 64 + 32 * 16, smem, env.stream>>>(tmIn, tmW, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel launch");
     return CB_OK;
