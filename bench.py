@@ -109,7 +109,7 @@ def bench_ours(args):
     import torch
     import torch.distributed as dist
     from crusaderbackend_b200.api import Context
-    from oracle import oracle as orc  # seeded generators only; the CPU baseline leg below times the oracle
+    from crusaderbackend_b200 import seeds as orc
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -320,7 +320,7 @@ def resnet56_section(torch, local, world, steps, warmup, weak=False):
     from crusaderbackend_b200.api import Context
     from crusaderbackend_b200.train import ResNetTrainer
     from crusaderbackend_b200 import dp
-    from oracle import oracle as orc
+    from crusaderbackend_b200 import seeds as orc
     gb = 128 * world if weak else 128   # weak: 128 images per GPU; strong (the spec's configuration): 128 in total
     rank = int(os.environ.get("RANK", "0"))
     start, count = dp.shard_batch(gb, world, rank)

@@ -88,7 +88,7 @@ class ResNetTrainer:
     def init_params(self, seed_key="init") -> np.ndarray:
         """He-normal filters and dense weights, gamma = 1, beta = 0 — the reference's randFillNetParams
         (seann/operands/seblas/Conv2D.cu:45-50, Linear.cu:42-46, BatchNorm.cu:8-11) with seeded draws."""
-        from oracle import oracle as orc  # seeded generators shared with the tests
+        from . import seeds as orc
         host = np.zeros(self.n_params, dtype=np.float32)
         for i, e in enumerate(self.entries):
             sl = slice(e["offset"], e["offset"] + e["size"])

@@ -1,7 +1,8 @@
 """numpy face of the CPU oracle (oracle/cpu_ref.c) and the seeded input generators.
 
-TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's CPU-baseline
-legs; the shipped package never imports it.
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by bench.py's CPU legs (the
+`cpu_baseline` object and `--impl reference`). Nothing under crusaderbackend_b200/ imports it; the seeded input
+generators it re-exports live in crusaderbackend_b200/seeds.py.
 """
 from __future__ import annotations
 
@@ -63,24 +64,13 @@ def _opt(a):
 
 
 # ------------------------------------------------------------------ seeded inputs
-def rng_for(*key) -> np.random.Generator:
-    """One PCG64 stream per (name, shape...) key so every test and the bench draw identical inputs."""
-    import zlib
-    seed = zlib.crc32(repr(key).encode())
-    return np.random.Generator(np.random.PCG64(seed))
+# The generators live in the package (the executor and the benchmark draw from them too); the tests reach them
+# through this module so that oracle and library always see the same streams.
+import sys as _sys
 
-
-def uniform_pm1(shape, *key) -> np.ndarray:
-    return rng_for("u", *key).uniform(-1.0, 1.0, size=shape).astype(np.float32)
-
-
-def normal(shape, *key, std: float = 1.0) -> np.ndarray:
-    return (rng_for("n", *key).standard_normal(size=shape) * std).astype(np.float32)
-
-
-def he_normal_filter(oc: int, ic: int, fh: int, fw: int, *key) -> np.ndarray:
-    """He-normal filter N(0, 2/(IC*FH*FW)) as seann's Conv2D draws it (seann/operands/seblas/Conv2D.cu:45-50)."""
-    return normal((oc, ic, fh, fw), "he", *key, std=float(np.sqrt(2.0 / (ic * fh * fw))))
+if str(_DIR.parent) not in _sys.path:
+    _sys.path.insert(0, str(_DIR.parent))
+from crusaderbackend_b200.seeds import he_normal_filter, normal, rng_for, uniform_pm1  # noqa: E402,F401
 
 
 # ------------------------------------------------------------------ error metrics
