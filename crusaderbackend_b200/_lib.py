@@ -6,10 +6,12 @@ point raises. Build it with `python -m crusaderbackend_b200.build`.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "lib" / "libcrusader_b200.so"
+# CRUSADER_B200_LIB: load another build of the same library (e.g. the instrumented one of `build --trace`)
+LIB_PATH = Path(os.environ.get("CRUSADER_B200_LIB") or _PKG / "lib" / "libcrusader_b200.so")
 
 CB_OK, CB_EINVAL, CB_ECUDA, CB_ETIMEOUT, CB_EUNSUPPORTED, CB_ENOMEM = 0, -1, -2, -3, -4, -5
 CB_MATH_TF32, CB_MATH_3XTF32, CB_MATH_FP32 = 0, 1, 2
@@ -30,6 +32,7 @@ SIGNATURES = {
     "cb_get_math": (_i, [_ctx]),
     "cb_set_sync": (_i, [_ctx, _i]),
     "cb_set_deterministic": (_i, [_ctx, _i]),
+    "cb_freeze_workspace": (_i, [_ctx, _i]),
     "cb_synchronize": (_i, [_ctx]),
     "cb_last_error": (C.c_char_p, [_ctx]),
     "cb_launch_count": (_ll, [_ctx]),
@@ -54,6 +57,8 @@ SIGNATURES = {
     "cb_relu_grad": (_i, [_ctx, _f, _f, _f, _ll]),
     "cb_tensor_op": (_i, [_ctx, _i, _f, _f, _fl, _ll]),
     "cb_grad_handover": (_i, [_ctx, _f, _f, _ll]),
+    "cb_concat_channels": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(_i), _f, _i, _i]),
+    "cb_concat_grads": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(_i), _f, _i, _i]),
     "cb_avgpool": (_i, [_ctx, _f, _f, _ll, _i, _i, _i, _i]),
     "cb_avgpool_back": (_i, [_ctx, _f, _f, _ll, _i, _i, _i, _i]),
     "cb_global_avgpool": (_i, [_ctx, _f, _f, _ll, _i]),

@@ -46,19 +46,25 @@ def needs_build() -> bool:
     return any(p.stat().st_mtime > t for p in _sources() + _headers())
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, trace: bool = False) -> Path:
+    """trace=True builds a second library, libcrusader_b200_trace.so, with the kernels' time-stamp instrumentation
+    (-DCB_TRACE) compiled in; the product library never carries it."""
+    lib_path = LIB_DIR / "libcrusader_b200_trace.so" if trace else LIB_PATH
+    if not force and not trace and not needs_build():
         return LIB_PATH
     nvcc = _nvcc()
     LIB_DIR.mkdir(exist_ok=True)
-    OBJ_DIR.mkdir(exist_ok=True)
+    obj_dir = OBJ_DIR / "trace" if trace else OBJ_DIR
+    obj_dir.mkdir(parents=True, exist_ok=True)
     hdr_time = max(p.stat().st_mtime for p in _headers())
     flags = list(NVCC_FLAGS)
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
+    if trace:
+        flags += ["-DCB_TRACE"]
 
     def compile_one(src: Path) -> Path:
-        obj = OBJ_DIR / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
             return obj
         cmd = [nvcc, *flags, "-c", str(src), "-o", str(obj)]
@@ -73,16 +79,17 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(compile_one, _sources()))
-    cmd = [nvcc, "-shared", "-cudart", "shared", "-o", str(LIB_PATH), *map(str, objs),
+    cmd = [nvcc, "-shared", "-cudart", "shared", "-o", str(lib_path), *map(str, objs),
            "-Xlinker", "-rpath", "-Xlinker", "/usr/local/cuda/lib64"]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+                 trace="--trace" in sys.argv)
     print(path)

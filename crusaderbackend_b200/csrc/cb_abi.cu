@@ -51,55 +51,48 @@ int finish(cb_ctx* ctx, const char* what) {
     return read_status(ctx, what);
 }
 
-int ensure_workspace(cb_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->workspace_bytes) return CB_OK;
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+// Growth of one of the three scratch blocks. The old block is released only after the whole device is idle (work queued
+// on a stream the context used earlier may still read it), and never while the workspace is frozen or the stream is
+// being captured: a captured graph keeps the addresses of the blocks it was recorded with, so a later free would leave
+// it reading released memory.
+static int grow_block(cb_ctx* ctx, void** block, size_t* have, size_t bytes, size_t slack) {
+    if (bytes <= *have) return CB_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return fail(ctx, CB_ENOMEM, "workspace growth requested while the stream is being captured: run the same calls once "
+                                    "before the capture so that the scratch is already large enough");
+    if (ctx->workspace_frozen)
+        return fail(ctx, CB_ENOMEM, "workspace is frozen (cb_freeze_workspace) and this call needs a larger scratch block");
+    cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return check_cuda(ctx, e, "workspace growth sync");
-    if (ctx->workspace) cudaFree(ctx->workspace);
-    ctx->workspace = nullptr;
-    ctx->workspace_bytes = 0;
-    size_t want = bytes + (bytes >> 2);
-    want = (want + 255) & ~size_t(255);
-    e = cudaMalloc(&ctx->workspace, want);
+    if (*block) cudaFree(*block);
+    *block = nullptr;
+    *have = 0;
+    size_t want = (bytes + slack + 255) & ~size_t(255);
+    e = cudaMalloc(block, want);
     if (e != cudaSuccess) {
         check_cuda(ctx, e, "workspace cudaMalloc");
         return CB_ENOMEM;
     }
-    ctx->workspace_bytes = want;
+    *have = want;
     return CB_OK;
 }
 
-int ensure_workspace2(cb_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->workspace2_bytes) return CB_OK;
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return check_cuda(ctx, e, "workspace growth sync");
-    if (ctx->workspace2) cudaFree(ctx->workspace2);
-    ctx->workspace2 = nullptr;
-    ctx->workspace2_bytes = 0;
-    size_t want = (bytes + 255) & ~size_t(255);
-    e = cudaMalloc(&ctx->workspace2, want);
-    if (e != cudaSuccess) {
-        check_cuda(ctx, e, "workspace cudaMalloc");
-        return CB_ENOMEM;
-    }
-    ctx->workspace2_bytes = want;
-    return CB_OK;
-}
+int ensure_workspace(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->workspace, &ctx->workspace_bytes, bytes, bytes >> 2); }
+int ensure_workspace2(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->workspace2, &ctx->workspace2_bytes, bytes, 0); }
+int ensure_workspace3(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->workspace3, &ctx->workspace3_bytes, bytes, 0); }
 
-int ensure_workspace3(cb_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->workspace3_bytes) return CB_OK;
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) return check_cuda(ctx, e, "workspace growth sync");
-    if (ctx->workspace3) cudaFree(ctx->workspace3);
-    ctx->workspace3 = nullptr;
-    ctx->workspace3_bytes = 0;
-    size_t want = (bytes + 255) & ~size_t(255);
-    e = cudaMalloc(&ctx->workspace3, want);
-    if (e != cudaSuccess) {
-        check_cuda(ctx, e, "workspace cudaMalloc");
-        return CB_ENOMEM;
+// Entry check of every context call: the context must exist and its device must be the current one (launches go to the
+// current device; scratch and tensor maps belong to the context's).
+int enter(cb_ctx* ctx) {
+    if (!ctx) return CB_EINVAL;
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) return fail(ctx, CB_ECUDA, "cudaGetDevice failed");
+    if (cur != ctx->device) {
+        char buf[128];
+        snprintf(buf, sizeof(buf), "this context was created on device %d but device %d is current", ctx->device, cur);
+        return fail(ctx, CB_EINVAL, buf);
     }
-    ctx->workspace3_bytes = want;
     return CB_OK;
 }
 
@@ -225,6 +218,12 @@ int cb_set_sync(cb_ctx* ctx, int on) {
     return CB_OK;
 }
 
+int cb_freeze_workspace(cb_ctx* ctx, int on) {
+    if (!ctx) return CB_EINVAL;
+    ctx->workspace_frozen = on ? 1 : 0;
+    return CB_OK;
+}
+
 int cb_set_deterministic(cb_ctx* ctx, int on) {
     if (!ctx) return CB_EINVAL;
     ctx->deterministic = on ? 1 : 0;
@@ -232,9 +231,18 @@ int cb_set_deterministic(cb_ctx* ctx, int on) {
 }
 
 int cb_synchronize(cb_ctx* ctx) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     return read_status(ctx, "cb_synchronize");
 }
+
+#ifdef CB_TRACE
+// Development builds only: the next tensor-core convolution kernels write 16 time stamps per CTA into `buf`.
+int cb_debug_set_trace(cb_ctx* ctx, long long* buf) {
+    if (!ctx) return CB_EINVAL;
+    ctx->trace = buf;
+    return CB_OK;
+}
+#endif
 
 const char* cb_last_error(const cb_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
 long long cb_launch_count(const cb_ctx* ctx) { return ctx ? ctx->launches : 0; }
@@ -243,7 +251,7 @@ const char* cb_last_kernel(const cb_ctx* ctx) { return ctx ? ctx->last_kernel : 
 int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
             int ldb, float* C, int ldc, int batch, long long strideA, long long strideB, long long strideC,
             int accumulate) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(ctx, CB_EINVAL, "cb_gemm: negative extent");
     if (M == 0 || N == 0 || batch == 0) return CB_OK;
     if (!A || !B || !C) return fail(ctx, CB_EINVAL, "cb_gemm: null operand");

@@ -22,11 +22,13 @@ struct cb_ctx {
     size_t workspace2_bytes = 0;
     void* workspace3 = nullptr;    // scratch: lo parts and partial results of the 3xTF32 convolutions
     size_t workspace3_bytes = 0;
+    int workspace_frozen = 0;      // 1: a call that would need a larger scratch block fails instead of reallocating
     long long launches = 0;
     int sm_count = 148;
     int max_smem_optin = 0;
     std::string last_error;
     const char* last_kernel = "none";
+    long long* trace = nullptr;    // device buffer for per-CTA time stamps (builds with -DCB_TRACE only)
 };
 
 namespace cb {
@@ -35,8 +37,10 @@ int fail(cb_ctx* ctx, int code, const std::string& msg);
 int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what);
 // Returns after an optional sync; maps a non-zero device status word to CB_ETIMEOUT.
 int finish(cb_ctx* ctx, const char* what);
-// Grows the context workspace to at least `bytes` (stream-ordered with respect to earlier users
-// because growth synchronises the stream before freeing the old block).
+// CB_OK when ctx is non-null and its device is the current one.
+int enter(cb_ctx* ctx);
+// Grows one of the context's scratch blocks to at least `bytes`; growth waits for the whole device before the old
+// block is freed, and is refused (CB_ENOMEM) while the workspace is frozen or the stream is being captured.
 int ensure_workspace(cb_ctx* ctx, size_t bytes);
 int ensure_workspace2(cb_ctx* ctx, size_t bytes);
 int ensure_workspace3(cb_ctx* ctx, size_t bytes);

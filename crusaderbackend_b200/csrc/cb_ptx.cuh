@@ -4,7 +4,8 @@
 // Conventions used throughout:
 //  * every wait on an mbarrier is bounded (mbar_wait): after CB_WAIT_LIMIT_NS of polling the
 //    waiter raises the CTA-wide abort flag, records a status code in global memory and returns
-//    false; callers leave their loops, the CTA drains, frees its TMEM and exits.
+//    false; callers leave their loops; the producer then waits (bounded, mbar_drain) for the copies it
+//    armed, the MMA issuer commits and waits for the MMAs it issued, and only then is TMEM freed.
 //  * shared-memory addresses handed to PTX are 32-bit shared::cta window addresses.
 #pragma once
 #include <cuda.h>
@@ -15,7 +16,29 @@
 #define CB_WAIT_LIMIT_NS 2000000000ull
 #endif
 
+// Development aid, compiled out unless the library is built with -DCB_TRACE: per-CTA time stamps (SM clock) of the
+// pipeline roles' milestones, 16 slots per CTA, written to a buffer the caller hands in through cb_debug_set_trace.
+#ifdef CB_TRACE
+#define CB_TRACE_EVENT(buf, slot)                                                      \
+    do {                                                                               \
+        if (buf) (buf)[(long long)blockIdx.x * 16 + (slot)] = (long long)clock64();    \
+    } while (0)
+#define CB_TRACE_WALL(buf, slot)                                                       \
+    do {                                                                               \
+        if (buf) (buf)[(long long)blockIdx.x * 16 + (slot)] = (long long)cb::globaltimer_ns(); \
+    } while (0)
+#else
+#define CB_TRACE_EVENT(buf, slot) do {} while (0)
+#define CB_TRACE_WALL(buf, slot) do {} while (0)
+#endif
+
 namespace cb {
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -60,28 +83,37 @@ enum : int {
     CBK_TIMEOUT_DRAIN = 107       // drain of in-flight copies after an abort
 };
 
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 // Bounded wait: gives up after CB_WAIT_LIMIT_NS of wall time (or when another role raised the abort
 // flag). Returns true when the phase completed, false on abort/timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                              int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > CB_WAIT_LIMIT_NS) break;
+            if (globaltimer_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    return mbar_wait_for(bar, parity, abort_flag, status, code, CB_WAIT_LIMIT_NS);
+}
+
+// After an abort: gives work that is still in flight a bounded chance to land before the CTA releases what it targets.
+// Waits (at most ~1 ms) for the given phase of `bar`; records CBK_TIMEOUT_DRAIN when it does not complete.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, int* status) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((it & 63u) == 63u && globaltimer_ns() - t0 > 1000000ull) break;
+    }
+    atomicCAS(status, 0, 107 /* CBK_TIMEOUT_DRAIN */);
 }
 
 // generic-proxy writes (st.shared) -> visible to the async proxy (TMA / tcgen05 operand reads)

@@ -267,7 +267,7 @@ extern "C" {
 
 int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
                 int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     ConvGeo g;
     int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_fwd");
     if (rc != CB_OK) return rc;
@@ -289,7 +289,7 @@ int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const flo
 
 int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
                   int FH, int FW, int sH, int sW, int pH, int pW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     ConvGeo g;
     int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_dgrad");
     if (rc != CB_OK) return rc;
@@ -311,7 +311,7 @@ int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N
 
 int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
                   int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     ConvGeo g;
     int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_wgrad");
     if (rc != CB_OK) return rc;

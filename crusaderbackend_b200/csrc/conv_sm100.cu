@@ -65,6 +65,7 @@ struct ConvParams {
     // filter packing done by the CTA itself (0: the packed filter is fetched by TMA from a scratch buffer)
     int pack_in_kernel, pack_mode, OCs, ICs, FHs, FWs, out_first, out_count;
     const float* Wsrc;
+    long long* trace;
 };
 
 struct __align__(8) ConvSmem {
@@ -73,6 +74,7 @@ struct __align__(8) ConvSmem {
     uint64_t tfull[2];
     uint64_t tempty[2];
     uint64_t wbar;
+    uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -165,6 +167,8 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
     const uint32_t st_base = w_base + p.w_bytes;
 
     if (threadIdx.x == 0) {
+        CB_TRACE_WALL(p.trace, 0);
+        CB_TRACE_EVENT(p.trace, 1);
         cs.abort_flag = 0;
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(smem_u32(&cs.full[s]), 1);
@@ -175,6 +179,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
             mbar_init(smem_u32(&cs.tempty[a]), 32 * kEpiWarps);
         }
         mbar_init(smem_u32(&cs.wbar), p.pack_in_kernel ? 32 * kEpiWarps : 1);
+        mbar_init(smem_u32(&cs.drain), 1);
         mbar_fence_init();
         tma_prefetch_desc(&tmIn);
         if (!p.pack_in_kernel) tma_prefetch_desc(&tmW);
@@ -189,6 +194,8 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
     tc_fence_after();
     const uint32_t tmem_base = cs.tmem_base;
     const uint32_t acc_stride = (uint32_t)p.tmem_cols >> 1;
+    uint32_t armed = 0, armed_parity = 0;  // producer lane: stages armed at least once / parity of their last arming
+    if (threadIdx.x == 0) CB_TRACE_EVENT(p.trace, 2);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -211,6 +218,8 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
                     const uint32_t full = smem_u32(&cs.full[s]);
                     const uint32_t dst0 = st_base + s * p.stage_bytes;
                     mbar_expect_tx(full, p.stage_bytes);
+                    armed |= 1u << s;
+                    armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
                     const int c0 = cb * p.KS * kCB;
                     if (p.shared_rows) {
                         // W == 32: the tile is 4 consecutive rows of one image; ONE box (32 px, 8*KS channels, FH+3
@@ -249,6 +258,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
         const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
         uint32_t s = 0, ph = 0, lt = 0;
         bool ok = warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
+        if (lane == 0) CB_TRACE_EVENT(p.trace, 4);
         for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
             const uint32_t a = lt & 1u;
             ok = warp_wait(smem_u32(&cs.tempty[a]), ((lt >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
@@ -260,6 +270,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
                 ok = warp_wait(smem_u32(&cs.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
+                if (lane == 0 && lt == 0 && cb == 0) CB_TRACE_EVENT(p.trace, 5);
                 if (lane == 0) {
                     const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
                     uint32_t accumulate = cb == 0 ? 0u : 1u;
@@ -275,6 +286,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
                     if (cb == p.NCB - 1) tc_commit(smem_u32(&cs.tfull[a]));
+                    if (lt == 0 && cb == p.NCB - 1) CB_TRACE_EVENT(p.trace, 6);
                 }
                 __syncwarp();
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
@@ -328,6 +340,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
             }
             fence_proxy_async_smem();
             mbar_arrive(smem_u32(&cs.wbar));
+            if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 3);
         }
         uint32_t lt = 0;
         bool ok = true;
@@ -340,6 +353,8 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if (threadIdx.x == 64 && lt == 0) CB_TRACE_EVENT(p.trace, 7);
+            if (threadIdx.x == 64 && lt == 1) CB_TRACE_EVENT(p.trace, 9);
             const int g = 4 * tile + quarter;
             const bool valid = g < (int)p.total_lines;
             const int n = g / p.LPI;
@@ -351,14 +366,35 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
                 conv_epilogue_chunk<8>(p, t_row, c, out, plane, valid, has_left, has_right);
             tc_fence_before();
             mbar_arrive(smem_u32(&cs.tempty[a]));
+            if (threadIdx.x == 64 && lt == 0) CB_TRACE_EVENT(p.trace, 8);
+            if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 10);
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (cs.abort_flag) {
+        // A bounded wait gave up somewhere in this CTA. Copies armed before that may still be in flight towards this
+        // CTA's shared memory and issued MMAs may still be running on its accumulators: give both a bounded chance to
+        // finish before the shared memory and TMEM are released.
+        if (warp == 0 && lane == 0) {
+            if (!p.pack_in_kernel) mbar_drain(smem_u32(&cs.wbar), 0, p.status);
+            for (int st = 0; st < p.stages; ++st)
+                if ((armed >> st) & 1u) mbar_drain(smem_u32(&cs.full[st]), (armed_parity >> st) & 1u, p.status);
+        }
+        if (warp == 1 && lane == 0) {
+            tc_commit(smem_u32(&cs.drain));
+            mbar_drain(smem_u32(&cs.drain), 0, p.status);
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+    if (threadIdx.x == 0) {
+        CB_TRACE_EVENT(p.trace, 11);
+        CB_TRACE_WALL(p.trace, 12);
     }
 }
 
@@ -568,6 +604,7 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
     p.pack_mode = ps.mode; p.OCs = ps.OC; p.ICs = ps.IC; p.FHs = ps.FHs; p.FWs = ps.FWs;
     p.out_first = ps.out_first; p.out_count = ps.out_count;
     p.Wsrc = W;
+    p.trace = err_ctx ? err_ctx->trace : nullptr;
 
     CUtensorMap tmIn, tmW;
     int rc;

@@ -37,7 +37,7 @@ using namespace cb;
 extern "C" {
 
 int cb_linear_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, float* Y, int batch, int IN, int OUT) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (batch < 0 || IN < 0 || OUT < 0) return fail(ctx, CB_EINVAL, "cb_linear_fwd: negative extent");
     if (batch == 0 || OUT == 0) return CB_OK;
     if (!X || !W || !Y) return fail(ctx, CB_EINVAL, "cb_linear_fwd: null operand");
@@ -54,7 +54,7 @@ int cb_linear_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, f
 }
 
 int cb_linear_xgrad(cb_ctx* ctx, const float* dY, const float* W, float* dX, int batch, int IN, int OUT) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (batch < 0 || IN < 0 || OUT < 0) return fail(ctx, CB_EINVAL, "cb_linear_xgrad: negative extent");
     if (batch == 0 || IN == 0) return CB_OK;
     if (!dY || !W || !dX) return fail(ctx, CB_EINVAL, "cb_linear_xgrad: null operand");
@@ -71,7 +71,7 @@ int cb_linear_xgrad(cb_ctx* ctx, const float* dY, const float* W, float* dX, int
 
 int cb_linear_paramgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, float* db, int batch, int IN,
                         int OUT) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (batch < 0 || IN < 0 || OUT < 0) return fail(ctx, CB_EINVAL, "cb_linear_paramgrad: negative extent");
     if (OUT == 0 || batch == 0) return CB_OK;
     if (!dY || !X || !dW) return fail(ctx, CB_EINVAL, "cb_linear_paramgrad: null operand");

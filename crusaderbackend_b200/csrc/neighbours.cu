@@ -620,6 +620,15 @@ __global__ void relu_grad2_kernel(const float* __restrict__ Y, const float* __re
     }
 }
 
+// dst[n][c][hw] += src[n][c0 + c][hw]: one channel slice of a concatenated gradient added into its source's buffer
+__global__ void slice_add_kernel(float* __restrict__ dst, const float* __restrict__ src, long long total, long long per_n,
+                                 long long src_per_n, long long src_off) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / per_n, r = i - n * per_n;
+        dst[i] += src[n * src_per_n + src_off + r];
+    }
+}
+
 int done(cb_ctx* ctx, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
@@ -636,7 +645,7 @@ extern "C" {
 
 int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
               float* xhat, int N, long long P) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd: null operand");
@@ -654,7 +663,7 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
 }
 
 int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, int N, long long P) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!dY || !gamma || !X || !dX) return fail(ctx, CB_EINVAL, "cb_bn_bwd: null operand");
@@ -672,7 +681,7 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
 }
 
 int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgamma, float* dbeta, int N, long long P) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_paramgrad: negative extent");
     if (P == 0) return CB_OK;
     if (!dY || !xhat || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_paramgrad: null operand");
@@ -688,7 +697,7 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
 
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                     float* dbeta, const float* relu_out, int N, long long P) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!dY || !gamma || !X || !dX || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: null operand");
@@ -703,7 +712,7 @@ int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const floa
 }
 
 int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: null operand");
@@ -717,13 +726,13 @@ int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* 
 }
 
 int cb_add_relu(cb_ctx* ctx, const float* A, const float* B, float* Out, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && (!A || !B || !Out))) return fail(ctx, CB_EINVAL, "cb_add_relu: bad argument");
     return launch_eltwise<OP_ADD_RELU>(ctx, A, const_cast<float*>(B), Out, 0.f, n, "cb_add_relu");
 }
 
 int cb_relu_grad2(cb_ctx* ctx, const float* Y, const float* dY, float* dA, float* dB, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && (!Y || !dY || !dA))) return fail(ctx, CB_EINVAL, "cb_relu_grad2: bad argument");
     if (n == 0) return CB_OK;
     relu_grad2_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(Y, dY, dA, dB, n);
@@ -731,19 +740,19 @@ int cb_relu_grad2(cb_ctx* ctx, const float* Y, const float* dY, float* dA, float
 }
 
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && (!X || !Y))) return fail(ctx, CB_EINVAL, "cb_relu: bad argument");
     return launch_eltwise<OP_RELU>(ctx, X, nullptr, Y, 0.f, n, "cb_relu");
 }
 
 int cb_relu_grad(cb_ctx* ctx, const float* X, const float* dY, float* dX, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && (!X || !dY || !dX))) return fail(ctx, CB_EINVAL, "cb_relu_grad: bad argument");
     return launch_eltwise<OP_RELU_GRAD>(ctx, X, const_cast<float*>(dY), dX, 0.f, n, "cb_relu_grad");
 }
 
 int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && !A)) return fail(ctx, CB_EINVAL, "cb_tensor_op: bad argument");
     if (op >= CB_OP_ADD && op <= CB_OP_DIV && n > 0 && !B) return fail(ctx, CB_EINVAL, "cb_tensor_op: null B");
     float* b = const_cast<float*>(B);
@@ -762,13 +771,13 @@ int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, lo
 }
 
 int cb_grad_handover(cb_ctx* ctx, float* dA, float* dA_reserve, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0 || (n > 0 && (!dA || !dA_reserve))) return fail(ctx, CB_EINVAL, "cb_grad_handover: bad argument");
     return launch_eltwise<OP_ADD_ZERO_B>(ctx, dA, dA_reserve, dA, 0.f, n, "cb_grad_handover");
 }
 
 int cb_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H, int W, int rH, int rW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (NC < 0 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool: bad extent");
     const long long total = NC * (H / rH) * (W / rW);
     if (total == 0) return CB_OK;
@@ -778,7 +787,7 @@ int cb_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H, int W
 }
 
 int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H, int W, int rH, int rW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (NC < 0 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool_back: bad extent");
     const long long total = NC * H * W;
     if (total == 0) return CB_OK;
@@ -788,7 +797,7 @@ int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H
 }
 
 int cb_global_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int HW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (NC < 0 || HW < 1) return fail(ctx, CB_EINVAL, "cb_global_avgpool: bad extent");
     if (NC == 0) return CB_OK;
     if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_global_avgpool: null operand");
@@ -797,7 +806,7 @@ int cb_global_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H
 }
 
 int cb_global_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int HW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (NC < 0 || HW < 1) return fail(ctx, CB_EINVAL, "cb_global_avgpool_back: bad extent");
     if (NC == 0) return CB_OK;
     if (!dX || !dY) return fail(ctx, CB_EINVAL, "cb_global_avgpool_back: null operand");
@@ -806,7 +815,7 @@ int cb_global_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC
 }
 
 int cb_softmax(cb_ctx* ctx, const float* X, float* Y, int rows, int step) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (rows < 0 || step < 1) return fail(ctx, CB_EINVAL, "cb_softmax: bad extent");
     if (rows == 0) return CB_OK;
     if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_softmax: null operand");
@@ -815,7 +824,7 @@ int cb_softmax(cb_ctx* ctx, const float* X, float* Y, int rows, int step) {
 }
 
 int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY, float* loss_sum, long long n) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (n < 0) return fail(ctx, CB_EINVAL, "cb_cross_entropy: negative extent");
     if (!Y || !labels) return fail(ctx, CB_EINVAL, "cb_cross_entropy: null operand");
     if (loss_sum) {
@@ -828,7 +837,7 @@ int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY
 }
 
 int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || C < 0 || HW < 0) return fail(ctx, CB_EINVAL, "cb_conv_bias: negative extent");
     const long long total = (long long)N * C * HW;
     if (total == 0) return CB_OK;
@@ -838,7 +847,7 @@ int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW)
 }
 
 int cb_conv_bias_grad(cb_ctx* ctx, const float* dY, float* db, int N, int C, int HW, int accumulate) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || C < 0 || HW < 0) return fail(ctx, CB_EINVAL, "cb_conv_bias_grad: negative extent");
     if (C == 0) return CB_OK;
     if (!dY || !db) return fail(ctx, CB_EINVAL, "cb_conv_bias_grad: null operand");
@@ -846,9 +855,52 @@ int cb_conv_bias_grad(cb_ctx* ctx, const float* dY, float* db, int N, int C, int
     return done(ctx, "cb_conv_bias_grad");
 }
 
+int cb_concat_channels(cb_ctx* ctx, int count, const float* const* X, const int* channels, float* Y, int N, int HW) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (count < 0 || N < 0 || HW < 0 || (count > 0 && (!X || !channels || !Y))) return fail(ctx, CB_EINVAL, "cb_concat_channels: bad argument");
+    long long ctot = 0;
+    for (int i = 0; i < count; ++i) {
+        if (channels[i] < 0 || (channels[i] > 0 && !X[i])) return fail(ctx, CB_EINVAL, "cb_concat_channels: bad source");
+        ctot += channels[i];
+    }
+    if (N == 0 || HW == 0 || ctot == 0) return CB_OK;
+    long long c0 = 0;
+    for (int i = 0; i < count; ++i) {
+        if (channels[i] == 0) continue;
+        const size_t row = (size_t)channels[i] * HW * sizeof(float);
+        cudaError_t e = cudaMemcpy2DAsync(Y + c0 * HW, (size_t)ctot * HW * sizeof(float), X[i], row, row, (size_t)N,
+                                          cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cb_concat_channels");
+        c0 += channels[i];
+    }
+    return finish(ctx, "cb_concat_channels");
+}
+
+int cb_concat_grads(cb_ctx* ctx, int count, float* const* dX, const int* channels, const float* dY, int N, int HW) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (count < 0 || N < 0 || HW < 0 || (count > 0 && (!dX || !channels || !dY))) return fail(ctx, CB_EINVAL, "cb_concat_grads: bad argument");
+    long long ctot = 0;
+    for (int i = 0; i < count; ++i) {
+        if (channels[i] < 0 || (channels[i] > 0 && !dX[i])) return fail(ctx, CB_EINVAL, "cb_concat_grads: bad destination");
+        ctot += channels[i];
+    }
+    if (N == 0 || HW == 0 || ctot == 0) return CB_OK;
+    long long c0 = 0;
+    for (int i = 0; i < count; ++i) {
+        if (channels[i] == 0) continue;
+        const long long per_n = (long long)channels[i] * HW, total = per_n * N;
+        slice_add_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(dX[i], dY, total, per_n, ctot * HW, c0 * HW);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cb_concat_grads");
+        ctx->launches += 1;
+        c0 += channels[i];
+    }
+    return finish(ctx, "cb_concat_grads");
+}
+
 int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
                       const long long* sizes, const unsigned char* is_weight, float lr, float beta, float l2) {
-    if (!ctx) return CB_EINVAL;
+    if (int rc_enter = enter(ctx)) return rc_enter;
     if (ntensors < 0) return fail(ctx, CB_EINVAL, "cb_momentum_multi: negative tensor count");
     if (ntensors == 0) return CB_OK;
     if (!w || !g || !m || !sizes) return fail(ctx, CB_EINVAL, "cb_momentum_multi: null table");

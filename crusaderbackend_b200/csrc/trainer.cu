@@ -67,6 +67,7 @@ struct cbt_model {
     std::vector<void*> owned;      // device allocations released by cbt_destroy
     std::string err;
     void* mom_table = nullptr;     // device descriptor table of the Momentum step, built by cbt_bind
+    int bn_grad_swap = 0;          // 1: BatchNorm's two parameter gradients land in each other's slot, as in the reference
     long long mom_biggest = 1;
 };
 
@@ -467,16 +468,20 @@ int cbt_backward(cbt_model* m) {
                 if (o.in0_grad_accumulate) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, y.d, 0.f, x.size()));
                 continue;
             }
-            case OP_BN:
+            case OP_BN: {
+                // where d(gamma) and d(beta) are stored: their own slots, or each other's (reference order)
+                float* dgamma = m->G + (m->bn_grad_swap ? o.b_off : o.w_off);
+                float* dbeta = m->G + (m->bn_grad_swap ? o.w_off : o.b_off);
                 if (o.xhat < 0) {
-                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, m->G + o.w_off, m->G + o.b_off,
+                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta,
                                             o.relu ? y.a : nullptr, x.n, (long long)x.c * x.h * x.w));
                 } else {
-                    CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, m->G + o.w_off, m->G + o.b_off, x.n,
+                    CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, dgamma, dbeta, x.n,
                                             (long long)x.c * x.h * x.w));
                     CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, (long long)x.c * x.h * x.w));
                 }
                 break;
+            }
             case OP_CONV:
                 CBT_TRY(cb_conv_wgrad(ctx, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
                                       o.stride, o.pad, o.pad, 1));
@@ -487,6 +492,17 @@ int cbt_backward(cbt_model* m) {
         }
         if (o.in0_grad_accumulate && o.in0 != m->input) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
     }
+    return CB_OK;
+}
+
+// The reference's BatchNorm operand hands beta's gradient tensor to the kernel argument that receives d(gamma) and
+// gamma's to the one that receives d(beta) (seann/operands/seblas/BatchNorm.cu:24 against the parameter order of
+// seblas/operations/cuBatchNorm.cuh:16), so its Momentum step moves beta by d(gamma) and gamma by d(beta). on = 1
+// reproduces that order, for runs that must follow the reference's operand graph step by step; the default (0) is the
+// mathematically right assignment.
+int cbt_set_reference_bn_grad_order(cbt_model* m, int on) {
+    if (!m) return CB_EINVAL;
+    m->bn_grad_swap = on ? 1 : 0;
     return CB_OK;
 }
 

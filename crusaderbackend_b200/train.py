@@ -31,6 +31,7 @@ TRAIN_SIGNATURES = {
     "cbt_loss_ptr": (C.c_void_p, [C.c_void_p]),
     "cbt_copy_tensor": (_i, [C.c_void_p, _i, _i, _f, _ll]),
     "cbt_copy_loss": (_i, [C.c_void_p, _f]),
+    "cbt_set_reference_bn_grad_order": (_i, [C.c_void_p, _i]),
 }
 KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
 
@@ -108,6 +109,11 @@ class ResNetTrainer:
         self.params.copy_(torch.from_numpy(np.ascontiguousarray(host, dtype=np.float32)))
         self.grads.zero_()
         self.momentum.zero_()
+
+    def set_reference_bn_grad_order(self, on: bool):
+        """Store BatchNorm's d(gamma) / d(beta) in each other's slot, as the reference's operand does
+        (seann/operands/seblas/BatchNorm.cu:24)."""
+        self._check(self.lib.cbt_set_reference_bn_grad_order(self.h, int(on)))
 
     # ---- step
     def forward(self, images: torch.Tensor, labels_onehot: torch.Tensor):

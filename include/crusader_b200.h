@@ -9,7 +9,8 @@
  *
  * Return value: CB_OK or a negative CB_E* code; cb_last_error() describes the last failure.
  * The caller owns every tensor. A context owns a small device status word and a scratch workspace.
- * A context is used by one host thread at a time; create one per GPU.
+ * A context is used by one host thread at a time; create one per GPU. cb_create makes its device current and leaves
+ * it current; every later call on the context requires that device to be the current one (CB_EINVAL otherwise).
  */
 #ifndef CRUSADER_B200_H
 #define CRUSADER_B200_H
@@ -46,6 +47,11 @@ int cb_set_math(cb_ctx* ctx, int mode);
 int cb_get_math(const cb_ctx* ctx);
 /* 1: synchronise after every call and surface device-side status (reference-compatible). 0: async. */
 int cb_set_sync(cb_ctx* ctx, int sync_every_call);
+/* 1: from now on a call that would need a larger scratch block than the context holds fails with CB_ENOMEM instead of
+ * reallocating. A CUDA graph captured over cb_* calls keeps the addresses of the scratch blocks it was recorded with:
+ * freeze the workspace after the warm-up calls and before (or right after) the capture, and keep it frozen for as long
+ * as the graph is replayed. Growth is also refused while the context's stream is being captured. */
+int cb_freeze_workspace(cb_ctx* ctx, int on);
 /* 1: never split a reduction across CTAs with atomics (bit-reproducible results). Default 0. */
 int cb_set_deterministic(cb_ctx* ctx, int on);
 /* Waits for the stream, then reads and clears the device status word. CB_OK or CB_ETIMEOUT/CB_ECUDA. */
@@ -149,6 +155,12 @@ int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, lo
 /* dA += dA_reserve; dA_reserve = 0 in one pass: the step every operand's xGrads begins with
  * (e.g. seann/operands/seblas/Conv2D.cu:19-21). */
 int cb_grad_handover(cb_ctx* ctx, float* dA, float* dA_reserve, long long n);
+
+/* Channel concatenation Y = [X[0] ; X[1] ; ...] of `count` N x channels[i] x HW tensors (seblas::concat,
+ * seblas/operations/cuConcat.cu:33-49) and its gradient, which ADDS each channel slice of dY into dX[i]
+ * (seblas::concatGrads, cuConcat.cu:51-82, adds into the sources' dAReserve). X / dX / channels are host arrays. */
+int cb_concat_channels(cb_ctx* ctx, int count, const float* const* X, const int* channels, float* Y, int N, int HW);
+int cb_concat_grads(cb_ctx* ctx, int count, float* const* dX, const int* channels, const float* dY, int N, int HW);
 
 /* Non-overlapping average pooling over NC planes of H x W and its gradient (seblas::avgPool / avgPoolBack,
  * seblas/operations/cuPool.cu:153-169); global average pooling and its gradient (cuPool.cu:171-184). */

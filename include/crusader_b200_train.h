@@ -44,6 +44,11 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels_onehot);
 int cbt_backward(cbt_model* m);
 int cbt_update(cbt_model* m, float lr, float beta, float l2);
 
+/* on = 1: store BatchNorm's two parameter gradients in each other's slot, which is what the reference's operand does
+ * (seann/operands/seblas/BatchNorm.cu:24 passes beta's and gamma's gradient tensors to seblas::batchNormParamGrads in
+ * swapped order); for step-by-step comparisons with the reference's own operand graph. Default 0: the right slots. */
+int cbt_set_reference_bn_grad_order(cbt_model* m, int on);
+
 /* Mean cross-entropy per sample of the last forward pass (synchronises the stream), as Sequential::train logs it. */
 int cbt_loss(cbt_model* m, float* loss_mean);
 /* Device pointers for tests: value (grad = 0) / gradient (grad = 1) of tensor id; -1 = logits, -2 = softmax. */
