@@ -38,9 +38,15 @@ SIGNATURES = {
     "cb_launch_count": (_ll, [_ctx]),
     "cb_last_kernel": (C.c_char_p, [_ctx]),
     "cb_gemm": (_i, [_ctx, _i, _i, _i, _i, _i, _f, _i, _f, _i, _f, _i, _i, _ll, _ll, _ll, _i]),
+    "cb_measure_umma_peak": (_i, [_ctx, _i, _i, _i, _i, C.POINTER(_fl)]),
     "cb_conv_fwd": (_i, [_ctx, _f, _f, _f, _f] + [_i] * 12),
     "cb_conv_dgrad": (_i, [_ctx, _f, _f, _f] + [_i] * 11),
     "cb_conv_wgrad": (_i, [_ctx, _f, _f, _f] + [_i] * 12),
+    "cb_conv_fwd_ex": (_i, [_ctx, _f, _f, _f] + [_i] * 11 + [C.c_void_p]),
+    "cb_conv_dgrad_ex": (_i, [_ctx, _f, _f, _f] + [_i] * 12 + [_ll, _ll]),
+    "cb_conv_wgrad_ex": (_i, [_ctx, _f, _f, _f] + [_i] * 12 + [_ll, _ll]),
+    "cb_conv_cache_filters": (_i, [_ctx, _i]),
+    "cb_filters_changed": (_i, [_ctx]),
     "cb_conv_bias": (_i, [_ctx, _f, _f, _i, _i, _i]),
     "cb_conv_bias_grad": (_i, [_ctx, _f, _f, _i, _i, _i, _i]),
     "cb_linear_fwd": (_i, [_ctx, _f, _f, _f, _f, _i, _i, _i]),
@@ -67,6 +73,8 @@ SIGNATURES = {
     "cb_cross_entropy": (_i, [_ctx, _f, _f, _f, _f, _ll]),
     "cb_momentum": (_i, [_ctx, _f, _f, _f, _ll, _fl, _fl, _fl, _i]),
     "cb_conv_fwd_noalloc": (_i, [_i, C.c_void_p, _f, _f, _f, _f] + [_i] * 12 + [C.c_char_p, _i]),
+    "cb_conv_fwd_noalloc_status": (_i, [_i, C.c_void_p, C.c_char_p, _i]),
+    "cb_selftest_wait_timeout": (_i, [_ctx, _i]),
     "cb_momentum_multi": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                C.POINTER(_ll), C.POINTER(C.c_ubyte), _fl, _fl, _fl]),
 }

@@ -80,6 +80,12 @@ class Context:
     def last_kernel(self) -> str:
         return self.lib.cb_last_kernel(self.h).decode()
 
+    def measure_umma_peak(self, n: int = 256, p_mn: bool = False, q_mn: bool = False, iters: int = 20000) -> float:
+        """TFLOP/s of a resident-operand tcgen05.mma loop (M=128, N=n, K=8, TF32) on every SM."""
+        out = C.c_float()
+        self._check(self.lib.cb_measure_umma_peak(self.h, n, int(p_mn), int(q_mn), iters, C.byref(out)))
+        return float(out.value)
+
     # ---- GEMM (raw)
     def gemm(self, A: torch.Tensor, B: torch.Tensor, C_: torch.Tensor, transA: bool = False, transB: bool = False,
              accumulate: bool = False) -> torch.Tensor:

@@ -18,7 +18,7 @@ int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what) {
     return fail(ctx, CB_ECUDA, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }
 
-static const char* status_name(int s) {
+const char* status_name(int s) {
     switch (s) {
         case CBK_TIMEOUT_EMPTY: return "producer timed out waiting for a free stage";
         case CBK_TIMEOUT_FULL: return "MMA issuer timed out waiting for operands";
@@ -192,6 +192,7 @@ int cb_destroy(cb_ctx* ctx) {
     if (ctx->workspace2) cudaFree(ctx->workspace2);
     if (ctx->workspace3) cudaFree(ctx->workspace3);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    filter_cache_destroy(ctx);
     delete ctx;
     return CB_OK;
 }
@@ -243,6 +244,32 @@ int cb_debug_set_trace(cb_ctx* ctx, long long* buf) {
     return CB_OK;
 }
 #endif
+
+namespace {
+// Waits on a barrier that nothing ever arrives at, with a limit of limit_ns: the bounded wait gives up, records its
+// status and the kernel returns normally.
+__global__ void wait_timeout_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_for(smem_u32(&bar), 0, &abort_flag, status, CBK_TIMEOUT_FULL, limit_ns);
+}
+}  // namespace
+
+int cb_selftest_wait_timeout(cb_ctx* ctx, int limit_ms) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (limit_ms < 1 || limit_ms > 1000) return fail(ctx, CB_EINVAL, "cb_selftest_wait_timeout: limit must be 1..1000 ms");
+    wait_timeout_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, (unsigned long long)limit_ms * 1000000ull);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "cb_selftest_wait_timeout");
+    ctx->launches += 1;
+    return finish(ctx, "cb_selftest_wait_timeout");
+}
 
 const char* cb_last_error(const cb_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
 long long cb_launch_count(const cb_ctx* ctx) { return ctx ? ctx->launches : 0; }

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string>
+#include <vector>
 
 #include "../../include/crusader_b200.h"
 
@@ -29,12 +30,17 @@ struct cb_ctx {
     std::string last_error;
     const char* last_kernel = "none";
     long long* trace = nullptr;    // device buffer for per-CTA time stamps (builds with -DCB_TRACE only)
+    int filter_cache_on = 0;       // packed convolution filters are kept between calls (cb_conv_cache_filters)
+    long long filter_version = 0;  // bumped by every call that may have changed a filter's values
+    void* filter_cache = nullptr;  // the cache itself (conv_sm100.cu)
 };
 
 namespace cb {
 
 int fail(cb_ctx* ctx, int code, const std::string& msg);
 int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what);
+// Text for a CBK_* code a kernel left in a status word.
+const char* status_name(int s);
 // Returns after an optional sync; maps a non-zero device status word to CB_ETIMEOUT.
 int finish(cb_ctx* ctx, const char* what);
 // CB_OK when ctx is non-null and its device is the current one.
@@ -70,6 +76,27 @@ struct GemmCall {
     int accumulate = 0;
     Epilogue ep;
 };
+// Per-element tail of a convolution, applied in this order while the accumulator is written out:
+// y = conv; y = y * scale + shift (if scale); y += bias[oc] (if bias); y += out (if accumulate); y = max(y, 0) (if relu).
+struct ConvEpilogue {
+    const float* bias = nullptr;
+    const float* scale = nullptr;   // with shift: Cout values, or Cout*H*W values when per_position
+    const float* shift = nullptr;
+    int per_position = 0;
+    int relu = 0;
+    int accumulate = 0;
+};
+// Tensor-core convolution paths. Each returns CB_EUNSUPPORTED, before any work is queued, when the geometry is outside
+// what it covers. in/out batch strides: elements between consecutive images, 0 = densely packed.
+int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
+                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, bool dgrad_of, long long in_batch,
+                  long long out_batch);
+int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch);
+// Packed-filter cache of a context (conv_sm100.cu).
+int filter_cache_repack_all(cb_ctx* ctx);
+void filter_cache_destroy(cb_ctx* ctx);
+
 bool umma_gemm_eligible(const GemmCall& g);
 int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3);
 int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g);

@@ -9,15 +9,26 @@ namespace {
 
 struct ConvGeo {
     int N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, OH, OW;
+    long long x_batch, y_batch;  // elements between consecutive images of the input-side / output-side tensor
 };
 
 constexpr int kOcTile = 8;
 
+__device__ __forceinline__ float apply_epilogue(const ConvEpilogue& ep, float v, int oc, long long pos_idx, float old) {
+    if (ep.scale) {
+        const long long si = ep.per_position ? pos_idx : (long long)oc;
+        v = fmaf(v, ep.scale[si], ep.shift[si]);
+    }
+    if (ep.bias) v += ep.bias[oc];
+    if (ep.accumulate) v += old;
+    if (ep.relu) v = fmaxf(v, 0.f);
+    return v;
+}
+
 // Forward: one thread per output pixel, kOcTile output channels in registers; consecutive threads walk ow, so
 // X loads are coalesced and every weight load is a warp-wide broadcast.
 __global__ void __launch_bounds__(256) conv_fwd_simt(const float* __restrict__ W, const float* __restrict__ X,
-                                                     float* __restrict__ Y, const float* __restrict__ bias,
-                                                     const ConvGeo g, int relu) {
+                                                     float* __restrict__ Y, const ConvGeo g, const ConvEpilogue ep) {
     const long long pix = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long npix = (long long)g.N * g.OH * g.OW;
     if (pix >= npix) return;
@@ -28,8 +39,8 @@ __global__ void __launch_bounds__(256) conv_fwd_simt(const float* __restrict__ W
     const int n = (int)(t / g.OH);
     float acc[kOcTile];
 #pragma unroll
-    for (int o = 0; o < kOcTile; ++o) acc[o] = (bias && oc0 + o < g.OC) ? bias[oc0 + o] : 0.f;
-    const float* Xn = X + (long long)n * g.IC * g.IH * g.IW;
+    for (int o = 0; o < kOcTile; ++o) acc[o] = 0.f;
+    const float* Xn = X + (long long)n * g.x_batch;
     const long long wstride = (long long)g.IC * g.FH * g.FW;
     for (int ic = 0; ic < g.IC; ++ic) {
         for (int fh = 0; fh < g.FH; ++fh) {
@@ -46,18 +57,18 @@ __global__ void __launch_bounds__(256) conv_fwd_simt(const float* __restrict__ W
             }
         }
     }
+    float* Yn = Y + (long long)n * g.y_batch;
 #pragma unroll
     for (int o = 0; o < kOcTile; ++o)
         if (oc0 + o < g.OC) {
-            float v = acc[o];
-            if (relu) v = fmaxf(v, 0.f);
-            Y[(((long long)n * g.OC + oc0 + o) * g.OH + oh) * g.OW + ow] = v;
+            const long long idx = ((long long)(oc0 + o) * g.OH + oh) * g.OW + ow;
+            Yn[idx] = apply_epilogue(ep, acc[o], oc0 + o, idx, ep.accumulate ? Yn[idx] : 0.f);
         }
 }
 
-// Data gradient: one thread per dX pixel, kOcTile input channels in registers.
+// Data gradient: one thread per dX pixel, kOcTile input channels in registers. x_batch is dX's stride, y_batch dY's.
 __global__ void __launch_bounds__(256) conv_dgrad_simt(const float* __restrict__ W, const float* __restrict__ dY,
-                                                       float* __restrict__ dX, const ConvGeo g) {
+                                                       float* __restrict__ dX, const ConvGeo g, int accumulate) {
     const long long pix = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long npix = (long long)g.N * g.IH * g.IW;
     if (pix >= npix) return;
@@ -69,7 +80,7 @@ __global__ void __launch_bounds__(256) conv_dgrad_simt(const float* __restrict__
     float acc[kOcTile];
 #pragma unroll
     for (int o = 0; o < kOcTile; ++o) acc[o] = 0.f;
-    const float* dYn = dY + (long long)n * g.OC * g.OH * g.OW;
+    const float* dYn = dY + (long long)n * g.y_batch;
     const int taps = g.FH * g.FW;
     for (int fh = 0; fh < g.FH; ++fh) {
         const int th = ih + g.pH - fh;
@@ -90,9 +101,13 @@ __global__ void __launch_bounds__(256) conv_dgrad_simt(const float* __restrict__
             }
         }
     }
+    float* dXn = dX + (long long)n * g.x_batch;
 #pragma unroll
     for (int o = 0; o < kOcTile; ++o)
-        if (ic0 + o < g.IC) dX[(((long long)n * g.IC + ic0 + o) * g.IH + ih) * g.IW + iw] = acc[o];
+        if (ic0 + o < g.IC) {
+            float* dst = dXn + ((long long)(ic0 + o) * g.IH + ih) * g.IW + iw;
+            *dst = accumulate ? *dst + acc[o] : acc[o];
+        }
 }
 
 // Weight gradient: one block per (oc, ic) pair and batch slice; threads stride over the output pixels and keep up
@@ -113,8 +128,8 @@ __global__ void __launch_bounds__(256) conv_wgrad_simt(const float* __restrict__
 #pragma unroll
         for (int t = 0; t < kTapGroup; ++t) acc[t] = 0.f;
         for (int n = n0; n < n1; ++n) {
-            const float* dyp = dY + ((long long)n * g.OC + oc) * opix;
-            const float* xp = X + ((long long)n * g.IC + ic) * g.IH * g.IW;
+            const float* dyp = dY + (long long)n * g.y_batch + (long long)oc * opix;
+            const float* xp = X + (long long)n * g.x_batch + (long long)ic * g.IH * g.IW;
             for (int q = threadIdx.x; q < opix; q += blockDim.x) {
                 const int oh = q / g.OW, ow = q - oh * g.OW;
                 const float d = dyp[q];
@@ -150,12 +165,17 @@ __global__ void __launch_bounds__(256) conv_wgrad_simt(const float* __restrict__
 }
 
 int make_geo(cb_ctx* ctx, ConvGeo& g, int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH,
-             int pW, const char* who) {
+             int pW, long long x_batch, long long y_batch, const char* who) {
     if (N < 0 || IC < 0 || OC < 0 || IH < 0 || IW < 0) return fail(ctx, CB_EINVAL, std::string(who) + ": negative extent");
     if (FH < 1 || FW < 1 || sH < 1 || sW < 1 || pH < 0 || pW < 0)
         return fail(ctx, CB_EINVAL, std::string(who) + ": filter, stride must be >= 1 and padding >= 0");
     if (IH + 2 * pH < FH || IW + 2 * pW < FW) return fail(ctx, CB_EINVAL, std::string(who) + ": filter larger than the padded input");
-    g = ConvGeo{N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, (IH - FH + 2 * pH) / sH + 1, (IW - FW + 2 * pW) / sW + 1};
+    g = ConvGeo{N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, (IH - FH + 2 * pH) / sH + 1, (IW - FW + 2 * pW) / sW + 1, 0, 0};
+    const long long x_dense = (long long)IC * IH * IW, y_dense = (long long)OC * g.OH * g.OW;
+    if ((x_batch && x_batch < x_dense) || (y_batch && y_batch < y_dense))
+        return fail(ctx, CB_EINVAL, std::string(who) + ": batch stride smaller than one image");
+    g.x_batch = x_batch ? x_batch : x_dense;
+    g.y_batch = y_batch ? y_batch : y_dense;
     return CB_OK;
 }
 
@@ -168,24 +188,28 @@ int after_launch(cb_ctx* ctx, const char* what) {
 }
 
 // ---- 3xTF32 composition: x = hi + lo with hi = the 19 bits the tensor core reads, lo = rna_tf32(x - hi).
-__global__ void tf32_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, long long n) {
+// lo[n][i] = lo part of x[n*x_batch + i], written densely (per elements per image)
+__global__ void tf32_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, long long n, long long per,
+                               long long x_batch) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float v = x[i];
+        const long long img = i / per;
+        const float v = x[img * x_batch + (i - img * per)];
         const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
         uint32_t r;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v - hi));
         lo[i] = __uint_as_float(r);
     }
 }
-// y = y + a + b (+ bias[channel]) (ReLU): the sum of the three tensor-core passes
-__global__ void sum3_kernel(float* __restrict__ y, const float* __restrict__ a, const float* __restrict__ b,
-                            const float* __restrict__ bias, long long n, int C, long long plane, int relu) {
+// out = epilogue((a + b) + c): the sum of the three tensor-core passes (the two small cross terms first), dense
+// temporaries in, (possibly strided) output tensor out
+__global__ void sum3_kernel(float* __restrict__ out, const float* __restrict__ lead, const float* __restrict__ a,
+                            const float* __restrict__ b, const ConvEpilogue ep, long long n, long long per, long long plane,
+                            long long out_batch) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        float v = a[i] + b[i];  // the two small cross terms first, then the leading term
-        v += y[i];
-        if (bias) v += bias[(i / plane) % C];
-        if (relu) v = fmaxf(v, 0.f);
-        y[i] = v;
+        const long long img = i / per, r = i - img * per;
+        float* dst = out + img * out_batch + r;
+        const float v = (a[i] + b[i]) + lead[i];
+        *dst = apply_epilogue(ep, v, (int)(r / plane), r, ep.accumulate ? *dst : 0.f);
     }
 }
 
@@ -197,39 +221,42 @@ int grid_el(const cb_ctx* ctx, long long n) {
 
 }  // namespace
 
-// Tensor-core paths (conv_sm100.cu). Each returns CB_EUNSUPPORTED when the geometry is outside what it covers.
-int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
-                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of);
-int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate);
-
-
 // 3xTF32 forward / data gradient on the tensor cores: out = pass(W_hi, In_lo) + pass(W_lo, In_hi) + pass(W_hi, In_hi),
 // where every pass is the TF32 kernel (it reads the hi parts by truncation). The dropped lo*lo term is < 2^-20 relative.
-// Scratch (workspace3): In_lo, W_lo and the two cross-term outputs. Returns CB_EUNSUPPORTED when the TF32 kernel does
-// not cover the geometry, before any work was queued.
-static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out, const float* bias, int N, int IC, int IH,
-                       int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of,
-                       long long in_elems, long long out_elems, int out_channels, long long out_plane) {
+// Scratch (workspace3): In_lo, W_lo and the three partial outputs, all densely packed; the last kernel adds them and
+// applies the epilogue while writing the caller's output. Returns CB_EUNSUPPORTED when the TF32 kernel does not cover the
+// geometry, before any work was queued.
+static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out, const ConvEpilogue& ep, int N, int IC,
+                       int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, bool dgrad_of,
+                       long long in_per, long long out_per, long long out_plane, long long in_batch, long long out_batch) {
     const long long w_elems = (long long)OC * IC * FH * FW;
+    const long long in_elems = in_per * N, out_elems = out_per * N;
     auto up = [](long long n) { return (n + 63) & ~63LL; };
-    const size_t need = (size_t)(up(in_elems) + up(w_elems) + 2 * up(out_elems)) * sizeof(float);
+    const size_t need = (size_t)(up(in_elems) + up(w_elems) + 3 * up(out_elems)) * sizeof(float);
     int rc = ensure_workspace3(ctx, need);
     if (rc != CB_OK) return rc;
     float* in_lo = static_cast<float*>(ctx->workspace3);
     float* w_lo = in_lo + up(in_elems);
-    float* t1 = w_lo + up(w_elems);
+    float* t0 = w_lo + up(w_elems);
+    float* t1 = t0 + up(out_elems);
     float* t2 = t1 + up(out_elems);
+    const ConvEpilogue plain{};
     // leading term first: it also tells whether the geometry is covered
-    rc = umma_conv_fwd(ctx, W, In, Out, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
+    rc = umma_conv_fwd(ctx, W, In, t0, plain, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dgrad_of, in_batch, 0);
     if (rc != CB_OK) return rc;
-    tf32_lo_kernel<<<grid_el(ctx, in_elems), 256, 0, ctx->stream>>>(In, in_lo, in_elems);
-    tf32_lo_kernel<<<grid_el(ctx, w_elems), 256, 0, ctx->stream>>>(W, w_lo, w_elems);
-    rc = umma_conv_fwd(ctx, W, in_lo, t1, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
-    if (rc == CB_OK) rc = umma_conv_fwd(ctx, w_lo, In, t2, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, dgrad_of);
+    tf32_lo_kernel<<<grid_el(ctx, in_elems), 256, 0, ctx->stream>>>(In, in_lo, in_elems, in_per, in_batch ? in_batch : in_per);
+    tf32_lo_kernel<<<grid_el(ctx, w_elems), 256, 0, ctx->stream>>>(W, w_lo, w_elems, w_elems, w_elems);
+    rc = umma_conv_fwd(ctx, W, in_lo, t1, plain, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dgrad_of, 0, 0);
+    if (rc == CB_OK) {
+        // w_lo is a temporary whose address recurs with different contents: it must not enter the packed-filter cache
+        const int cache_on = ctx->filter_cache_on;
+        ctx->filter_cache_on = 0;
+        rc = umma_conv_fwd(ctx, w_lo, In, t2, plain, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dgrad_of, in_batch, 0);
+        ctx->filter_cache_on = cache_on;
+    }
     if (rc != CB_OK) return rc;
-    sum3_kernel<<<grid_el(ctx, out_elems), 256, 0, ctx->stream>>>(Out, t1, t2, bias, out_elems, out_channels, out_plane,
-                                                                 relu ? 1 : 0);
+    sum3_kernel<<<grid_el(ctx, out_elems), 256, 0, ctx->stream>>>(Out, t0, t1, t2, ep, out_elems, out_per, out_plane,
+                                                                 out_batch ? out_batch : out_per);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "3xTF32 convolution");
     ctx->launches += 3;
@@ -237,7 +264,7 @@ static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out,
     return CB_OK;
 }
 
-// 3xTF32 weight gradient: three accumulating TF32 passes (dY_hi X_lo, dY_lo X_hi, dY_hi X_hi).
+// 3xTF32 weight gradient: three accumulating TF32 passes (dY_hi X_lo, dY_lo X_hi, dY_hi X_hi); dense tensors.
 static int wgrad_3xtf32(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC, int FH,
                         int FW, int sH, int sW, int pH, int pW, int accumulate, long long x_elems, long long dy_elems) {
     auto up = [](long long n) { return (n + 63) & ~63LL; };
@@ -245,12 +272,12 @@ static int wgrad_3xtf32(cb_ctx* ctx, const float* dY, const float* X, float* dW,
     if (rc != CB_OK) return rc;
     float* x_lo = static_cast<float*>(ctx->workspace3);
     float* dy_lo = x_lo + up(x_elems);
-    rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate);
+    rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, 0, 0);
     if (rc != CB_OK) return rc;
-    tf32_lo_kernel<<<grid_el(ctx, x_elems), 256, 0, ctx->stream>>>(X, x_lo, x_elems);
-    tf32_lo_kernel<<<grid_el(ctx, dy_elems), 256, 0, ctx->stream>>>(dY, dy_lo, dy_elems);
-    rc = umma_conv_wgrad(ctx, dY, x_lo, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1);
-    if (rc == CB_OK) rc = umma_conv_wgrad(ctx, dy_lo, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1);
+    tf32_lo_kernel<<<grid_el(ctx, x_elems), 256, 0, ctx->stream>>>(X, x_lo, x_elems, x_elems, x_elems);
+    tf32_lo_kernel<<<grid_el(ctx, dy_elems), 256, 0, ctx->stream>>>(dY, dy_lo, dy_elems, dy_elems, dy_elems);
+    rc = umma_conv_wgrad(ctx, dY, x_lo, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1, 0, 0);
+    if (rc == CB_OK) rc = umma_conv_wgrad(ctx, dy_lo, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 1, 0, 0);
     if (rc != CB_OK) return rc;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "3xTF32 weight gradient");
@@ -263,78 +290,130 @@ static int wgrad_3xtf32(cb_ctx* ctx, const float* dY, const float* X, float* dW,
 
 using namespace cb;
 
+static int conv_fwd_impl(cb_ctx* ctx, const float* W, const float* X, float* Y, int N, int IC, int IH, int IW, int OC, int FH,
+                         int FW, int sH, int sW, int pH, int pW, const cb_epilogue* cep, const char* who) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    ConvEpilogue ep{};
+    long long xb = 0, yb = 0;
+    if (cep) {
+        ep.bias = cep->bias; ep.scale = cep->scale; ep.shift = cep->shift;
+        ep.per_position = cep->per_position ? 1 : 0; ep.relu = cep->relu ? 1 : 0; ep.accumulate = cep->accumulate ? 1 : 0;
+        xb = cep->x_batch_stride; yb = cep->y_batch_stride;
+        if ((ep.scale == nullptr) != (ep.shift == nullptr)) return fail(ctx, CB_EINVAL, std::string(who) + ": scale and shift go together");
+    }
+    ConvGeo g;
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, xb, yb, who);
+    if (rc != CB_OK) return rc;
+    const long long npix = (long long)N * g.OH * g.OW;
+    if (npix == 0 || OC == 0) return CB_OK;
+    if (!W || !X || !Y) return fail(ctx, CB_EINVAL, std::string(who) + ": null operand");
+    if (ctx->math == CB_MATH_TF32) {  // tensor cores; 3xTF32 = three such passes; FP32 (and uncovered geometries) = CUDA cores
+        rc = umma_conv_fwd(ctx, W, X, Y, ep, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, false, xb, yb);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
+    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = conv_3xtf32(ctx, W, X, Y, ep, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, false, (long long)IC * IH * IW,
+                         (long long)OC * g.OH * g.OW, (long long)g.OH * g.OW, xb, yb);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
+    }
+    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((OC + kOcTile - 1) / kOcTile));
+    conv_fwd_simt<<<grid, 256, 0, ctx->stream>>>(W, X, Y, g, ep);
+    return after_launch(ctx, who);
+}
+
+static int conv_dgrad_impl(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
+                           int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long dx_batch,
+                           const char* who) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    ConvGeo g;
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, dx_batch, dy_batch, who);
+    if (rc != CB_OK) return rc;
+    const long long npix = (long long)N * IH * IW;
+    if (npix == 0 || IC == 0) return CB_OK;
+    if (!W || !dY || !dX) return fail(ctx, CB_EINVAL, std::string(who) + ": null operand");
+    ConvEpilogue ep{};
+    ep.accumulate = accumulate ? 1 : 0;
+    if (ctx->math == CB_MATH_TF32) {
+        rc = umma_conv_fwd(ctx, W, dY, dX, ep, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, true, dy_batch, dx_batch);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
+    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = conv_3xtf32(ctx, W, dY, dX, ep, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, true, (long long)OC * g.OH * g.OW,
+                         (long long)IC * IH * IW, (long long)IH * IW, dy_batch, dx_batch);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
+    }
+    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((IC + kOcTile - 1) / kOcTile));
+    conv_dgrad_simt<<<grid, 256, 0, ctx->stream>>>(W, dY, dX, g, accumulate ? 1 : 0);
+    return after_launch(ctx, who);
+}
+
 extern "C" {
 
 int cb_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
                 int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu) {
-    if (int rc_enter = enter(ctx)) return rc_enter;
-    ConvGeo g;
-    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_fwd");
-    if (rc != CB_OK) return rc;
-    const long long npix = (long long)N * g.OH * g.OW;
-    if (npix == 0 || OC == 0) return CB_OK;
-    if (!W || !X || !Y) return fail(ctx, CB_EINVAL, "cb_conv_fwd: null operand");
-    if (ctx->math == CB_MATH_TF32) {  // tensor cores; 3xTF32 = three such passes; FP32 (and uncovered geometries) = CUDA cores
-        rc = umma_conv_fwd(ctx, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, relu, false);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_fwd") : rc;
-    } else if (ctx->math == CB_MATH_3XTF32) {
-        rc = conv_3xtf32(ctx, W, X, Y, bias, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, relu, false,
-                         (long long)N * IC * IH * IW, npix * OC, OC, (long long)g.OH * g.OW);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_fwd") : rc;
-    }
-    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((OC + kOcTile - 1) / kOcTile));
-    conv_fwd_simt<<<grid, 256, 0, ctx->stream>>>(W, X, Y, bias, g, relu ? 1 : 0);
-    return after_launch(ctx, "cb_conv_fwd");
+    cb_epilogue ep{};
+    ep.bias = bias;
+    ep.relu = relu;
+    return conv_fwd_impl(ctx, W, X, Y, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, &ep, "cb_conv_fwd");
+}
+
+int cb_conv_fwd_ex(cb_ctx* ctx, const float* W, const float* X, float* Y, int N, int IC, int IH, int IW, int OC, int FH,
+                   int FW, int sH, int sW, int pH, int pW, const cb_epilogue* ep) {
+    return conv_fwd_impl(ctx, W, X, Y, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, ep, "cb_conv_fwd_ex");
 }
 
 int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
                   int FH, int FW, int sH, int sW, int pH, int pW) {
-    if (int rc_enter = enter(ctx)) return rc_enter;
-    ConvGeo g;
-    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_dgrad");
-    if (rc != CB_OK) return rc;
-    const long long npix = (long long)N * IH * IW;
-    if (npix == 0 || IC == 0) return CB_OK;
-    if (!W || !dY || !dX) return fail(ctx, CB_EINVAL, "cb_conv_dgrad: null operand");
-    if (ctx->math == CB_MATH_TF32) {
-        rc = umma_conv_fwd(ctx, W, dY, dX, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, true);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_dgrad") : rc;
-    } else if (ctx->math == CB_MATH_3XTF32) {
-        rc = conv_3xtf32(ctx, W, dY, dX, nullptr, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, true,
-                         (long long)N * OC * g.OH * g.OW, npix * IC, IC, (long long)IH * IW);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_dgrad") : rc;
-    }
-    dim3 grid((unsigned)((npix + 255) / 256), (unsigned)((IC + kOcTile - 1) / kOcTile));
-    conv_dgrad_simt<<<grid, 256, 0, ctx->stream>>>(W, dY, dX, g);
-    return after_launch(ctx, "cb_conv_dgrad");
+    return conv_dgrad_impl(ctx, W, dY, dX, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, 0, 0, 0, "cb_conv_dgrad");
 }
 
-int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                  int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
+int cb_conv_dgrad_ex(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
+                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch_stride,
+                     long long dx_batch_stride) {
+    return conv_dgrad_impl(ctx, W, dY, dX, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, dy_batch_stride,
+                           dx_batch_stride, "cb_conv_dgrad_ex");
+}
+
+int cb_conv_cache_filters(cb_ctx* ctx, int on) {
+    if (!ctx) return CB_EINVAL;
+    ctx->filter_cache_on = on ? 1 : 0;
+    ctx->filter_version += 1;
+    return CB_OK;
+}
+
+int cb_filters_changed(cb_ctx* ctx) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    const int rc = filter_cache_repack_all(ctx);
+    return rc == CB_OK ? finish(ctx, "cb_filters_changed") : rc;
+}
+
+}  // extern "C"
+
+static int conv_wgrad_impl(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                           int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch,
+                           const char* who) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     ConvGeo g;
-    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, "cb_conv_wgrad");
+    int rc = make_geo(ctx, g, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, x_batch, dy_batch, who);
     if (rc != CB_OK) return rc;
     if (OC == 0 || IC == 0) return CB_OK;
-    if (!dW) return fail(ctx, CB_EINVAL, "cb_conv_wgrad: null operand");
+    if (!dW) return fail(ctx, CB_EINVAL, std::string(who) + ": null operand");
     const size_t wbytes = (size_t)OC * IC * FH * FW * sizeof(float);
     if ((long long)N * g.OH * g.OW == 0) {
         if (!accumulate) {
             cudaError_t e = cudaMemsetAsync(dW, 0, wbytes, ctx->stream);
-            if (e != cudaSuccess) return check_cuda(ctx, e, "cb_conv_wgrad: clear");
+            if (e != cudaSuccess) return check_cuda(ctx, e, "convolution weight gradient: clear");
         }
-        return finish(ctx, "cb_conv_wgrad");
+        return finish(ctx, who);
     }
-    if (!dY || !X) return fail(ctx, CB_EINVAL, "cb_conv_wgrad: null operand");
+    if (!dY || !X) return fail(ctx, CB_EINVAL, std::string(who) + ": null operand");
     if (ctx->math == CB_MATH_TF32) {
-        rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_wgrad") : rc;
-    } else if (ctx->math == CB_MATH_3XTF32) {
+        rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, dy_batch, x_batch);
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
+    } else if (ctx->math == CB_MATH_3XTF32 && !dy_batch && !x_batch) {
         rc = wgrad_3xtf32(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate,
                           (long long)N * IC * IH * IW, (long long)N * OC * g.OH * g.OW);
-        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, "cb_conv_wgrad") : rc;
+        if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
     }
-    if (OC > 65535 || IC > 65535) return fail(ctx, CB_EUNSUPPORTED, "cb_conv_wgrad: more than 65535 channels");
+    if (OC > 65535 || IC > 65535) return fail(ctx, CB_EUNSUPPORTED, std::string(who) + ": more than 65535 channels");
     int splits = 1;
     if (!ctx->deterministic) {
         const long long pairs = (long long)OC * IC;
@@ -349,11 +428,25 @@ int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N
         mode = 2;
         if (!accumulate) {
             cudaError_t e = cudaMemsetAsync(dW, 0, wbytes, ctx->stream);
-            if (e != cudaSuccess) return check_cuda(ctx, e, "cb_conv_wgrad: clear");
+            if (e != cudaSuccess) return check_cuda(ctx, e, "convolution weight gradient: clear");
         }
     }
     conv_wgrad_simt<<<dim3(OC, IC, splits), 256, 0, ctx->stream>>>(dY, X, dW, g, nps, mode);
-    return after_launch(ctx, "cb_conv_wgrad");
+    return after_launch(ctx, who);
+}
+
+extern "C" {
+
+int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                  int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
+    return conv_wgrad_impl(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, 0, 0, "cb_conv_wgrad");
+}
+
+int cb_conv_wgrad_ex(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch_stride,
+                     long long x_batch_stride) {
+    return conv_wgrad_impl(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, dy_batch_stride,
+                           x_batch_stride, "cb_conv_wgrad_ex");
 }
 
 }  // extern "C"

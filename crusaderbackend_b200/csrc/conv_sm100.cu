@@ -2,48 +2,49 @@
 //
 // Forward and data-gradient run the same kernel: D[pixel][oc] = sum over (tap, c) of In[n, c, oh+fh-pH, ow+fw-pW]
 // * Wp[tap][oc][c]. The 128 TMEM lanes of an accumulator are 128 output pixels (UMMA M), the columns are the output
-// channels (UMMA N = OC rounded up to 16), K walks 8 input channels of one filter tap per tcgen05.mma.
+// channels (UMMA N), K walks 8 input channels of one filter tap per tcgen05.mma.
 //
 //  * Pixels are grouped in "lines" of 32 consecutive floats of one channel plane (32/W image rows of a W-wide map,
 //    W in {8,16,32}); a CTA tile is 4 lines. For each filter row fh and line, one TMA box (32 pixels of the
-//    flattened H*W plane, 8 channels) of the NCHW input lands as an [8 channels][128 bytes] block — exactly the MN-major operand layout the tensor
-//    core reads (128-byte swizzle with 32-byte atoms). Rows above / below the image are out of bounds for the
-//    tensor map and arrive as zeros, which is the vertical padding.
+//    flattened H*W plane, 8*KS channels) of the NCHW input lands as [channels][128 bytes] — exactly the MN-major
+//    operand layout the tensor core reads (128-byte swizzle with 32-byte atoms). Rows above / below the image are out
+//    of bounds for the tensor map and arrive as zeros, which is the vertical padding.
 //  * A TMA box may not start at an odd column (its innermost coordinate must be 16-byte aligned), so the
 //    horizontal taps cannot be fetched as shifted boxes. They are not shifted on the input side at all: the three
-//    horizontal taps of a filter row are folded into the UMMA N dimension (N = 3 x OC, accumulator column
-//    fw*OCp + oc holds the partial sum of tap fw evaluated at the UNSHIFTED pixel), and the epilogue adds
-//    D0[x-1] + D1[x] + D2[x+1] with two warp shuffles per value; lanes at a row edge take zero instead, which is
-//    the horizontal padding. A pipeline stage is therefore only the centre copy of the input rows.
-//  * The filter is packed once per CTA into [fh][32-channel group][fw][oc][32 channels] (K-major rows of 128 bytes,
-//    zero padded, 128-byte swizzle) and stays resident in shared memory for the whole persistent CTA. The sixteen
-//    epilogue warps, idle until the first tile completes, build it straight from the caller's filter (coalesced
-//    reads, scattered 4-byte shared-memory writes), so forward and data gradient need no scratch buffer. (The
-//    allocation-free entry point keeps the older route: a pack kernel writes a scratch copy that TMA then loads.)
-//    For the data gradient the pack transposes the channel roles and rotates the filter by 180 degrees
-//    (seblas/operations/cuConv.cu:321-326 does the same rotation on the fly).
-//  * Epilogue (16 warps, 4 per TMEM lane quarter): tcgen05.ld, tap combine, + bias, ReLU, and stores in which the 32
-//    lanes of a warp write 128 contiguous bytes.
+//    horizontal taps of a filter row are folded into the UMMA N dimension (accumulator column fw*OCs + oc holds the
+//    partial sum of tap fw evaluated at the UNSHIFTED pixel), and the epilogue adds D0[x-1] + D1[x] + D2[x+1] with
+//    two warp shuffles per value; lanes at a row edge take zero instead, which is the horizontal padding.
+//  * The filter reaches the kernel already packed as [fh][32-channel group][fw][oc][32 channels] (K-major rows of
+//    128 bytes, zero padded) in global memory and is fetched once per CTA by TMA into 128-byte-swizzled shared
+//    memory, where it stays for the whole persistent CTA. The packing is a separate small kernel
+//    (pack_filter_kernel); with the context's filter cache on it runs once per weight update instead of once per call
+//    (cb_conv_cache_filters / cb_filters_changed). For the data gradient the pack transposes the channel roles and
+//    rotates the filter by 180 degrees (seblas/operations/cuConv.cu:321-326 does the same rotation on the fly).
+//  * When a layer has fewer pixel tiles than the GPU has CTA slots, the output channels are split over 2 or 4 CTAs
+//    per tile (each fetches only its slice of the packed filter and runs a narrower UMMA), so that small feature maps
+//    still occupy the whole GPU.
+//  * Epilogue (4 or 2 warps per TMEM lane quarter): tcgen05.ld, tap combine, then optional per-channel or
+//    per-position scale / shift, bias, accumulation onto the output, ReLU, and stores in which the 32 lanes of a warp
+//    write 128 contiguous bytes.
 //
 // Covered geometry: stride 1, filter 1x1 (pad 0) or 3x3 (pad 1) per axis, W in {8,16,32}, (32/W) | H,
-// FW * OC(rounded to 16) <= 256, packed filter <= ~150 KB. Everything else is served by the CUDA-core kernels in conv_simt.cu.
+// FW * OC(rounded to 16) <= 256 per CTA, packed filter slice <= ~150 KB; stride 2 through the phase split below.
+// Everything else is served by the CUDA-core kernels in conv_simt.cu.
 #include <cstdio>
+#include <cstdlib>
+#include <mutex>
 
-#include "cb_internal.h"
-#include "cb_ptx.cuh"
+#include "conv_common.cuh"
 
 namespace cb {
 namespace {
 
-constexpr int kCB = 8;          // input channels per UMMA K step
-constexpr int kMaxStages = 8;
-constexpr int kRowBytes = 128;  // one line of 32 floats
-
 struct ConvParams {
     int N, Cin, H, W, Cout;   // "input" and "output" of this pass (forward: X -> Y, dgrad: dY -> dX)
     int FH, FW, pH, pW;       // taps and padding: tap (fh, fw) reads the input at offset (fh - pH, fw - pW), each in [-1, 1]
-    int OCp;                  // Cout rounded up to 16
-    int NQ;                   // UMMA N = FW * OCp
+    int OCs;                  // output channels one CTA computes (a multiple of 16)
+    int nsplit;               // CTAs sharing a pixel tile, CTA b taking channels [(b % nsplit) * OCs, +OCs)
+    int NQ;                   // UMMA N = FW * OCs
     int CG;                   // 32-channel groups of the packed filter
     int KS;                   // UMMA K steps (8 channels each) per pipeline stage
     int NCB;                  // ceil(Cin / (8 * KS)) pipeline stages per tile
@@ -55,22 +56,20 @@ struct ConvParams {
     int tiles;                // ceil(total_lines / 4)
     int stages;
     int tmem_cols;
-    uint32_t w_bytes;         // resident packed filter
+    uint32_t w_bytes;         // resident slice of the packed filter
     uint32_t block_bytes;     // one line of a stage: 8 * KS channels x 128 B
     uint32_t stage_bytes;     // nblocks * block_bytes
+    int tma_out;              // 1: results leave through TMA stores (2: TMA reduce-adds) staged in shared memory
     float* Out;
-    const float* bias;
-    int relu;
+    long long out_batch;      // elements between consecutive images of the output
+    ConvEpilogue ep;
     int* status;
-    // filter packing done by the CTA itself (0: the packed filter is fetched by TMA from a scratch buffer)
-    int pack_in_kernel, pack_mode, OCs, ICs, FHs, FWs, out_first, out_count;
-    const float* Wsrc;
     long long* trace;
 };
 
 struct __align__(8) ConvSmem {
-    uint64_t full[kMaxStages];
-    uint64_t empty[kMaxStages];
+    uint64_t full[kConvMaxStages];
+    uint64_t empty[kConvMaxStages];
     uint64_t tfull[2];
     uint64_t tempty[2];
     uint64_t wbar;
@@ -79,92 +78,125 @@ struct __align__(8) ConvSmem {
     int abort_flag;
 };
 
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane, volatile int* abort_flag,
-                                          int* status, int code) {
-    int ok = 1;
-    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
-// Source filter tap of the stride-2 convolution that lands on (input phase, tap of the 2x2 phase convolution):
-// with ih = 2 oh + fh - 1, tap fh = 0 reads phase 1 at row oh - 1, fh = 1 phase 0 at row oh, fh = 2 phase 1 at row oh.
-__device__ __forceinline__ int s2_tap(int phase, int t) { return phase == 1 ? (t == 0 ? 0 : 2) : (t == 1 ? 1 : -1); }
-
 enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3 };
+constexpr int kMaxTileUmmas = 256;  // UMMAs of one tile (filter rows x 8-channel steps) the issuer's table holds
 
-// Inverse of s2_tap: source tap f of the 3x3 stride-2 filter -> (input phase, tap of the 2x2 phase convolution).
-__device__ __forceinline__ void s2_untap(int f, int& phase, int& t) {
-    phase = (f == 1) ? 0 : 1;
-    t = (f == 0) ? 0 : 1;
-}
+// Horizontal tap sets the kernel is instantiated for: the taps' column offsets fw - pW.
+enum { TAPS_1 = 0 /* {0} */, TAPS_3 = 1 /* {-1, 0, +1} */, TAPS_2L = 2 /* {-1, 0} */, TAPS_2R = 3 /* {0, +1} */ };
 
-// Epilogue warps are a template parameter of the kernel: 16 (4 per TMEM lane quarter) for wide outputs, 8 for outputs
-// of at most 32 channels, where two such CTAs share an SM so that their UMMA chains (each serial on its accumulator)
-// overlap.
-
-template <int CH>
-__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[CH]) {
-    if constexpr (CH == 32) tmem_ld32(taddr, r);
-    else if constexpr (CH == 16) tmem_ld16(taddr, r);
-    else tmem_ld8(taddr, r);
-}
-
-// One chunk of CH output channels of a tile's epilogue: the FW horizontal taps were accumulated at the unshifted
-// pixel in column blocks fw*OCp + oc; tap fw reads column ow + (fw - pW), so its partial sum sits (fw - pW) lanes
-// away. Lanes that would read across a row edge take zero instead (the horizontal padding).
-template <int CH>
-__device__ __forceinline__ void conv_epilogue_chunk(const ConvParams& p, uint32_t t_row, int c, float* out,
-                                                    long long plane, bool valid, bool has_left, bool has_right) {
-    uint32_t r0[CH], r1[CH], r2[CH];
-    tmem_ld_n<CH>(t_row + (uint32_t)c, r0);
-    if (p.FW > 1) tmem_ld_n<CH>(t_row + (uint32_t)(p.OCp + c), r1);
-    if (p.FW > 2) tmem_ld_n<CH>(t_row + (uint32_t)(2 * p.OCp + c), r2);
+// One chunk of 8 output channels of a tile's epilogue: the horizontal taps were accumulated at the unshifted pixel in
+// column blocks fw*OCs + c; the tap with column offset d holds its partial sum d lanes away, and lanes that would read
+// across a row edge take zero instead (the horizontal padding). The epilogue is bound by instruction issue (every SM
+// runs 16 epilogue warps), so the tap set is a template parameter and the plain forms take a branch-free path.
+// The 8 x 32 results leave either through one TMA store of the [8 channels][32 pixels] block, staged in this warp's
+// shared-memory slot `stage` (eight direct stores per thread land in eight different 4 KB-apart lines and were the
+// slowest part of the kernel), or, for the epilogue forms TMA cannot express (accumulate followed by ReLU), directly.
+template <int TAPS>
+__device__ __forceinline__ void conv_epilogue_chunk(const ConvParams& p, const CUtensorMap* tmOut, uint32_t t_row, int c,
+                                                    int oc0, float* img, long long plane, int pix, int n, bool valid,
+                                                    bool has_left, bool has_right, uint32_t stage, int lane, bool traced) {
+    uint32_t r0[8], r1[8], r2[8];
+    tmem_ld8(t_row + (uint32_t)c, r0);
+    if (TAPS != TAPS_1) tmem_ld8(t_row + (uint32_t)(p.OCs + c), r1);
+    if (TAPS == TAPS_3) tmem_ld8(t_row + (uint32_t)(2 * p.OCs + c), r2);
     tmem_ld_wait();
-    float v[CH];
+    if (traced) CB_TRACE_EVENT(p.trace, 13);
+    float v[8];
 #pragma unroll
-    for (int e = 0; e < CH; ++e) v[e] = 0.f;
-    for (int fw = 0; fw < p.FW; ++fw) {
-        const int d = fw - p.pW;  // warp-uniform
-#pragma unroll
-        for (int e = 0; e < CH; ++e) {
-            const float x = __uint_as_float(fw == 0 ? r0[e] : (fw == 1 ? r1[e] : r2[e]));
-            if (d == 0) {
-                v[e] += x;
-            } else if (d < 0) {
-                const float up = __shfl_up_sync(0xffffffffu, x, 1);
-                v[e] += has_left ? up : 0.f;
-            } else {
-                const float dn = __shfl_down_sync(0xffffffffu, x, 1);
-                v[e] += has_right ? dn : 0.f;
-            }
+    for (int e = 0; e < 8; ++e) {
+        if (TAPS == TAPS_1) {
+            v[e] = __uint_as_float(r0[e]);
+        } else if (TAPS == TAPS_3) {
+            const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(r0[e]), 1);
+            const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[e]), 1);
+            v[e] = ((has_left ? up : 0.f) + __uint_as_float(r1[e])) + (has_right ? dn : 0.f);
+        } else if (TAPS == TAPS_2L) {
+            const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(r0[e]), 1);
+            v[e] = (has_left ? up : 0.f) + __uint_as_float(r1[e]);
+        } else {
+            const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(r1[e]), 1);
+            v[e] = __uint_as_float(r0[e]) + (has_right ? dn : 0.f);
         }
     }
-    if (valid) {
+    if (traced) CB_TRACE_EVENT(p.trace, 14);
+    const bool plain = p.ep.scale == nullptr && p.ep.bias == nullptr;
+    if (p.tma_out) {
+        // the store issued two chunks ago from this slot must have finished reading it
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        const uint32_t mine = stage + (uint32_t)(lane * 4);
+        if (plain) {
+            const bool relu = p.ep.relu != 0;
 #pragma unroll
-        for (int e = 0; e < CH; ++e) {
-            const int oc = c + e;
+            for (int e = 0; e < 8; ++e)
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(mine + (uint32_t)(e * 128)), "f"(relu ? fmaxf(v[e], 0.f) : v[e])
+                             : "memory");
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int oc = oc0 + c + e;
+                float y = v[e];
+                if (oc < p.Cout) {
+                    if (p.ep.scale) {
+                        const long long si = p.ep.per_position ? (long long)oc * plane + pix : (long long)oc;
+                        y = fmaf(y, __ldg(p.ep.scale + si), __ldg(p.ep.shift + si));
+                    }
+                    if (p.ep.bias) y += __ldg(p.ep.bias + oc);
+                    if (p.ep.relu) y = fmaxf(y, 0.f);
+                }
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(mine + (uint32_t)(e * 128)), "f"(y) : "memory");
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && valid) {
+            if (p.tma_out == 2) tma_reduce_add_3d(tmOut, stage, pix, oc0 + c, n);
+            else tma_store_3d(tmOut, stage, pix, oc0 + c, n);
+            tma_store_commit();
+        }
+    } else if (valid) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int oc = oc0 + c + e;
             if (oc < p.Cout) {
                 float y = v[e];
-                if (p.bias) y += __ldg(p.bias + oc);
-                if (p.relu) y = fmaxf(y, 0.f);
-                out[(long long)oc * plane] = y;
+                const long long idx = (long long)oc * plane + pix;
+                if (p.ep.scale) {
+                    const long long si = p.ep.per_position ? idx : (long long)oc;
+                    y = fmaf(y, __ldg(p.ep.scale + si), __ldg(p.ep.shift + si));
+                }
+                if (p.ep.bias) y += __ldg(p.ep.bias + oc);
+                if (p.ep.accumulate) y += img[idx];
+                if (p.ep.relu) y = fmaxf(y, 0.f);
+                img[idx] = y;
             }
         }
     }
+    if (traced) CB_TRACE_EVENT(p.trace, 15);
 }
 
-template <int kEpiWarps>
-__global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
+// Epilogue warps are a template parameter of the kernel (8 = 2 per TMEM lane quarter is what the planner picks; 16 is
+// kept for experiments). Outputs of at most 32 channels per CTA with a small filter run two CTAs per SM so that their
+// UMMA chains overlap.
+template <int kEpiWarps, int TAPS>
+__global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
     umma_conv_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
-                     const ConvParams p) {
+                     const __grid_constant__ CUtensorMap tmOut, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ ConvSmem cs;
+    __shared__ uint2 mma_tab[kMaxTileUmmas];  // per UMMA of a tile: descriptor offsets of its P and Q operands
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     volatile int* abort_flag = &cs.abort_flag;
 
     const uint32_t w_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t st_base = w_base + p.w_bytes;
+    const uint32_t out_base = st_base + (uint32_t)p.stages * p.stage_bytes;  // epilogue staging: 2 KB per epilogue warp
+    // this CTA's slice of the output channels and its walk over the pixel tiles
+    const int split = (int)blockIdx.x % p.nsplit;
+    const int tile0 = (int)blockIdx.x / p.nsplit;
+    const int tile_step = (int)gridDim.x / p.nsplit;
+    const int oc0 = split * p.OCs;
 
     if (threadIdx.x == 0) {
         CB_TRACE_WALL(p.trace, 0);
@@ -178,11 +210,12 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
             mbar_init(smem_u32(&cs.tfull[a]), 1);
             mbar_init(smem_u32(&cs.tempty[a]), 32 * kEpiWarps);
         }
-        mbar_init(smem_u32(&cs.wbar), p.pack_in_kernel ? 32 * kEpiWarps : 1);
+        mbar_init(smem_u32(&cs.wbar), 1);
         mbar_init(smem_u32(&cs.drain), 1);
         mbar_fence_init();
         tma_prefetch_desc(&tmIn);
-        if (!p.pack_in_kernel) tma_prefetch_desc(&tmW);
+        tma_prefetch_desc(&tmW);
+        if (p.tma_out) tma_prefetch_desc(&tmOut);
     }
     __syncthreads();
     if (warp == 1) {
@@ -199,20 +232,20 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0 && !p.pack_in_kernel) {
-            // resident filter: one box [FW*OCp rows][32 channels] per (filter row, channel group)
+        if (lane == 0) {
+            // resident filter slice: one box [FW taps][OCs rows][32 channels] per (filter row, channel group)
             const uint32_t wbar = smem_u32(&cs.wbar);
             mbar_expect_tx(wbar, p.w_bytes);
             const int boxes = p.FH * p.CG;
             for (int b = 0; b < boxes; ++b)
-                tma_load_3d(w_base + (uint32_t)b * p.NQ * kRowBytes, &tmW, wbar, 0, b * p.NQ, 0);
+                tma_load_3d(w_base + (uint32_t)b * p.NQ * kRowBytes, &tmW, wbar, 0, oc0, b * p.FW);
         }
         __syncwarp();
         uint32_t s = 0, ph = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+        for (int tile = tile0; tile < p.tiles && ok; tile += tile_step) {
             for (int cb = 0; cb < p.NCB; ++cb) {
-                ok = warp_wait(smem_u32(&cs.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
+                ok = conv_warp_wait(smem_u32(&cs.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t full = smem_u32(&cs.full[s]);
@@ -247,107 +280,75 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        // One thread feeds the tensor core: descriptor constants are hoisted and each UMMA costs a few integer adds.
+        // One thread feeds the tensor core, and the instructions it spends per tcgen05.mma bound the kernel (a 128 x 48
+        // x 8 UMMA is ~25 cycles of tensor pipe): the operand descriptor offsets of every UMMA of a tile are tabulated
+        // once by the whole warp, so that issuing one costs a shared-memory load and two 64-bit adds.
         const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 1u, 0u);
         // P: 4 lines x [8 channels][128 B], MN-major: block_bytes between lines (LBO), 512 B per 4 channel rows (SBO)
         const uint64_t descP0 = umma_smem_desc(0, p.block_bytes, 512u, UMMA_SW_128B_BASE32B);
         // Q: packed filter rows [(fw, oc)][32 channels], K-major 128-byte rows
         const uint64_t descQ0 = umma_smem_desc(w_base, 16u, 1024u, UMMA_SW_128B);
-        const uint32_t blk_units = p.block_bytes >> 4;               // descriptor address units (16 B) per line block
-        const uint32_t fh_blocks = p.shared_rows ? 1u : 4u;          // blocks between consecutive filter rows
-        const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
+        const int per_stage = p.FH * p.KS;
+        {
+            const uint32_t blk_units = p.block_bytes >> 4;               // descriptor address units (16 B) per line block
+            const uint32_t fh_blocks = p.shared_rows ? 1u : 4u;          // blocks between consecutive filter rows
+            const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
+            for (int i = lane; i < p.NCB * per_stage; i += 32) {
+                const int cb = i / per_stage, rem = i - cb * per_stage;
+                const int fh = rem / p.KS, kk = rem - fh * p.KS;
+                const uint32_t ks = (uint32_t)(cb * p.KS + kk);  // global K step: channels [8 ks, 8 ks + 8)
+                mma_tab[i] = make_uint2((uint32_t)fh * fh_blocks * blk_units + (uint32_t)kk * 64u,
+                                        ((uint32_t)(fh * p.CG) + (ks >> 2)) * q_group_units + (ks & 3u) * 2u);
+            }
+            __syncwarp();
+        }
         uint32_t s = 0, ph = 0, lt = 0;
-        bool ok = warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
+        bool ok = conv_warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
         if (lane == 0) CB_TRACE_EVENT(p.trace, 4);
-        for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
+        for (int tile = tile0; tile < p.tiles && ok; tile += tile_step, ++lt) {
             const uint32_t a = lt & 1u;
-            ok = warp_wait(smem_u32(&cs.tempty[a]), ((lt >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
-                           CBK_TIMEOUT_TMEM_EMPTY);
+            ok = conv_warp_wait(smem_u32(&cs.tempty[a]), ((lt >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
+                                CBK_TIMEOUT_TMEM_EMPTY);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + a * acc_stride;
+            int ti = 0;
             for (int cb = 0; cb < p.NCB; ++cb) {
-                ok = warp_wait(smem_u32(&cs.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
+                ok = conv_warp_wait(smem_u32(&cs.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0 && lt == 0 && cb == 0) CB_TRACE_EVENT(p.trace, 5);
                 if (lane == 0) {
                     const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
-                    uint32_t accumulate = cb == 0 ? 0u : 1u;
-                    for (int fh = 0; fh < p.FH; ++fh) {
-                        const uint64_t dPf = pbase + (uint64_t)((uint32_t)fh * fh_blocks * blk_units);
-                        const uint32_t q_fh = (uint32_t)(fh * p.CG) * q_group_units;
-                        for (int kk = 0; kk < p.KS; ++kk) {
-                            const uint32_t ks = (uint32_t)(cb * p.KS + kk);  // global K step: channels [8 ks, 8 ks + 8)
-                            umma_tf32(d_tmem, dPf + (uint64_t)(kk * 64), descQ0 + (uint64_t)(q_fh + (ks >> 2) * q_group_units + (ks & 3u) * 2u),
-                                      idesc, accumulate);
-                            accumulate = 1u;
-                        }
+#pragma unroll 2
+                    for (int j = 0; j < per_stage; ++j, ++ti) {
+                        const uint2 off = mma_tab[ti];
+                        umma_tf32(d_tmem, pbase + off.x, descQ0 + off.y, idesc, ti != 0 ? 1u : 0u);
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
                     if (cb == p.NCB - 1) tc_commit(smem_u32(&cs.tfull[a]));
                     if (lt == 0 && cb == p.NCB - 1) CB_TRACE_EVENT(p.trace, 6);
+                } else {
+                    ti += per_stage;
                 }
                 __syncwarp();
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..17)
+        // ------------------------------------------------------------ epilogue (warps 2 ..)
         // One scheduler cannot hide the shuffle and store latencies of a single warp, so every TMEM lane quarter is
-        // served by four warps that split the channel chunks between them.
+        // served by several warps that split the channel chunks between them.
         const int quarter = warp & 3;
         const int slot = (warp - 2) >> 2;
-        if (p.pack_in_kernel) {
-            // The epilogue warps are idle until the first tile completes: they build the resident packed filter
-            // straight from the caller's OC x IC x FH x FW filter (coalesced reads, scattered 4-byte writes into the
-            // 128-byte-swizzled K-major rows), so no separate pack kernel or scratch buffer is needed.
-            const int te = threadIdx.x - 64, ne = 32 * kEpiWarps;
-            for (uint32_t v = (uint32_t)te; v < (p.w_bytes >> 4); v += (uint32_t)ne)
-                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(w_base + v * 16u), "r"(0u) : "memory");
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
-            const int taps_s = p.FHs * p.FWs;
-            const int total_src = p.OCs * p.ICs * taps_s;
-#pragma unroll 4
-            for (int j = te; j < total_src; j += ne) {
-                const int tap = j % taps_s, r = j / taps_s;
-                const int ch_s = r % p.ICs, o_s = r / p.ICs;
-                const int fh_s = tap / p.FWs, fw_s = tap - fh_s * p.FWs;
-                int fh, fw, o, ch;
-                bool keep = true;
-                if (p.pack_mode == PACK_FWD) {
-                    fh = fh_s; fw = fw_s; o = o_s; ch = ch_s;
-                } else if (p.pack_mode == PACK_DGRAD) {
-                    fh = p.FHs - 1 - fh_s; fw = p.FWs - 1 - fw_s; o = ch_s; ch = o_s;
-                } else {
-                    int ph, pw, th, tw;
-                    s2_untap(fh_s, ph, th);
-                    s2_untap(fw_s, pw, tw);
-                    const int og = (ph * 2 + pw) * p.ICs + ch_s;
-                    if (p.pack_mode == PACK_S2_FWD) {
-                        fh = th; fw = tw; o = o_s; ch = og;
-                    } else {
-                        fh = 1 - th; fw = 1 - tw; o = og - p.out_first; ch = o_s;
-                        keep = o >= 0 && o < p.out_count;
-                    }
-                }
-                if (keep) {
-                    const uint32_t R = (uint32_t)(((fh * p.CG + (ch >> 5)) * p.FW + fw) * p.OCp + o);
-                    const uint32_t c = (uint32_t)ch & 31u;
-                    const uint32_t addr = w_base + R * kRowBytes + (((c >> 2) ^ (R & 7u)) << 4) + ((c & 3u) << 2);
-                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(__ldg(p.Wsrc + j)) : "memory");
-                }
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&cs.wbar));
-            if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 3);
-        }
+        const uint32_t my_stage = out_base + (uint32_t)(warp - 2) * 2048u;
+        uint32_t buf = 0;
         uint32_t lt = 0;
         bool ok = true;
         const long long plane = (long long)p.H * p.W;
         const int col = lane & (p.W - 1);
         const bool has_left = col > 0, has_right = col < p.W - 1;
-        for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++lt) {
+        for (int tile = tile0; tile < p.tiles && ok; tile += tile_step, ++lt) {
             const uint32_t a = lt & 1u;
             ok = mbar_wait(smem_u32(&cs.tfull[a]), (lt >> 1) & 1u, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -360,15 +361,19 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
             const int n = g / p.LPI;
             const int h0 = (g - n * p.LPI) * p.L;
             // lane x of the line is pixel (h0 + x / W, x % W): 32 consecutive floats of the output plane
-            float* out = p.Out + ((long long)n * p.Cout * p.H + h0) * p.W + lane;
+            float* img = p.Out + (long long)n * p.out_batch;
+            const int pix = h0 * p.W + lane;
             const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
-            for (int c = slot * 8; c < p.OCp; c += 8 * (kEpiWarps / 4))
-                conv_epilogue_chunk<8>(p, t_row, c, out, plane, valid, has_left, has_right);
+            for (int c = slot * 8; c < p.OCs; c += 8 * (kEpiWarps / 4), buf ^= 1u)
+                conv_epilogue_chunk<TAPS>(p, &tmOut, t_row, c, oc0, img, plane, pix, n, valid, has_left, has_right,
+                                    my_stage + buf * 1024u, lane, threadIdx.x == 64 && lt == 0 && c == 0);
             tc_fence_before();
             mbar_arrive(smem_u32(&cs.tempty[a]));
             if (threadIdx.x == 64 && lt == 0) CB_TRACE_EVENT(p.trace, 8);
             if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 10);
         }
+        // this warp's stores must be complete before its staging memory is released with the CTA
+        if (p.tma_out && lane == 0) tma_store_wait_all<0>();
     }
 
     tc_fence_before();
@@ -378,7 +383,7 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
         // CTA's shared memory and issued MMAs may still be running on its accumulators: give both a bounded chance to
         // finish before the shared memory and TMEM are released.
         if (warp == 0 && lane == 0) {
-            if (!p.pack_in_kernel) mbar_drain(smem_u32(&cs.wbar), 0, p.status);
+            mbar_drain(smem_u32(&cs.wbar), 0, p.status);
             for (int st = 0; st < p.stages; ++st)
                 if ((armed >> st) & 1u) mbar_drain(smem_u32(&cs.full[st]), (armed_parity >> st) & 1u, p.status);
         }
@@ -398,49 +403,63 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps == 8 ? 2 : 1)
     }
 }
 
-// Packs the filter for the kernel above. Row index = ((fh * CG + cg) * FWc + fw) * OCp + o, 32 floats per row; W is the
-// caller's OC x IC x FHs x FWs filter, (FHc, FWc) the taps of the convolution the kernel runs.
+// What one packed filter is made from: W is the caller's OC x IC x FHs x FWs filter, (FHc, FWc) the taps of the
+// convolution the kernel runs. Row index = ((fh * CG + cg) * FWc + fw) * OCp + o, 32 floats per row.
 //   PACK_FWD:      row[c] = W[o][cg*32 + c][fh][fw]
 //   PACK_DGRAD:    row[c] = W[cg*32 + c][o][FH-1-fh][FW-1-fw]          (o = input channel of the convolution)
 //   PACK_S2_FWD:   the stride-2 3x3 convolution as a 2x2 convolution over the 4 input phases stacked as channels
 //                  c' = phase*IC + c: row[c'] = W[o][c][s2_tap(ph, fh)][s2_tap(pw, fw)] (zero where no tap lands)
 //   PACK_S2_DGRAD: its adjoint: input channels are the OC planes of dY, output o' = out_first + o indexes (phase, c),
 //                  taps flipped: row[oc] = W[oc][c][s2_tap(ph, 1-fh)][s2_tap(pw, 1-fw)]
-__global__ void pack_filter_kernel(const float* __restrict__ W, float* __restrict__ Wp, int OC, int IC, int FHs, int FWs,
-                                   int FHc, int FWc, int OCp, int CG, int mode, int out_first, int out_count,
-                                   long long total) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i & 31);
-        long long r = i >> 5;
-        const int o = (int)(r % OCp);
-        r /= OCp;
-        const int fw = (int)(r % FWc);
-        r /= FWc;
-        const int cg = (int)(r % CG);
-        const int fh = (int)(r / CG);
-        const int ch = cg * 32 + c;
-        float v = 0.f;
-        if (mode == PACK_FWD) {
-            if (o < OC && ch < IC) v = W[(((long long)o * IC + ch) * FHs + fh) * FWs + fw];
-        } else if (mode == PACK_DGRAD) {
-            if (o < IC && ch < OC) v = W[(((long long)ch * IC + o) * FHs + (FHs - 1 - fh)) * FWs + (FWs - 1 - fw)];
-        } else if (mode == PACK_S2_FWD) {
-            if (o < OC && ch < 4 * IC) {
-                const int phase = ch / IC, cc = ch - phase * IC;
-                const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
-                if (sh >= 0 && sw >= 0) v = W[(((long long)o * IC + cc) * FHs + sh) * FWs + sw];
-            }
-        } else {
-            if (o < out_count && ch < OC) {
-                const int og = out_first + o;
-                const int phase = og / IC, cc = og - phase * IC;
-                const int sh = s2_tap(phase >> 1, 1 - fh), sw = s2_tap(phase & 1, 1 - fw);
-                if (sh >= 0 && sw >= 0) v = W[(((long long)ch * IC + cc) * FHs + sh) * FWs + sw];
-            }
+struct PackJob {
+    const float* W;
+    float* Wp;
+    int OC, IC, FHs, FWs, FHc, FWc, OCp, CG, mode, out_first, out_count;
+    long long total;  // floats of the packed filter
+};
+
+__device__ __forceinline__ float pack_value(const PackJob& j, long long i) {
+    const int c = (int)(i & 31);
+    long long r = i >> 5;
+    const int o = (int)(r % j.OCp);
+    r /= j.OCp;
+    const int fw = (int)(r % j.FWc);
+    r /= j.FWc;
+    const int cg = (int)(r % j.CG);
+    const int fh = (int)(r / j.CG);
+    const int ch = cg * 32 + c;
+    const float* W = j.W;
+    const int OC = j.OC, IC = j.IC, FHs = j.FHs, FWs = j.FWs;
+    if (j.mode == PACK_FWD) {
+        if (o < OC && ch < IC) return W[(((long long)o * IC + ch) * FHs + fh) * FWs + fw];
+    } else if (j.mode == PACK_DGRAD) {
+        if (o < IC && ch < OC) return W[(((long long)ch * IC + o) * FHs + (FHs - 1 - fh)) * FWs + (FWs - 1 - fw)];
+    } else if (j.mode == PACK_S2_FWD) {
+        if (o < OC && ch < 4 * IC) {
+            const int phase = ch / IC, cc = ch - phase * IC;
+            const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
+            if (sh >= 0 && sw >= 0) return W[(((long long)o * IC + cc) * FHs + sh) * FWs + sw];
         }
-        Wp[i] = v;
+    } else {
+        if (o < j.out_count && ch < OC) {
+            const int og = j.out_first + o;
+            const int phase = og / IC, cc = og - phase * IC;
+            const int sh = s2_tap(phase >> 1, 1 - fh), sw = s2_tap(phase & 1, 1 - fw);
+            if (sh >= 0 && sw >= 0) return W[(((long long)ch * IC + cc) * FHs + sh) * FWs + sw];
+        }
     }
+    return 0.f;
+}
+
+__global__ void pack_filter_kernel(const PackJob j) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < j.total; i += (long long)gridDim.x * blockDim.x)
+        j.Wp[i] = pack_value(j, i);
+}
+// Every cached filter of a context in one launch: blockIdx.y indexes a device table of jobs.
+__global__ void pack_filter_table_kernel(const PackJob* __restrict__ jobs) {
+    const PackJob j = jobs[blockIdx.y];
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < j.total; i += (long long)gridDim.x * blockDim.x)
+        j.Wp[i] = pack_value(j, i);
 }
 
 // ---- re-layout kernels of the stride-2 path (memory-bound, one element per thread, coalesced on the write side)
@@ -460,9 +479,9 @@ __global__ void space_to_depth2_kernel(const float* __restrict__ X, float* __res
         Xs[i] = X[((n * C + c) * H + 2 * ii + (phase >> 1)) * W + 2 * j + (phase & 1)];
     }
 }
-// dX[n][c][y][x] = dXs[group][n][o][y/2][x/2] with phase*C + c = group*per_group + o
+// dX[n][c][y][x] (+)= dXs[group][n][o][y/2][x/2] with phase*C + c = group*per_group + o
 __global__ void depth_to_space2_kernel(const float* __restrict__ dXs, float* __restrict__ dX, int N, int C, int H, int W,
-                                       int per_group, long long total) {
+                                       int per_group, long long total, int accumulate) {
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -474,7 +493,8 @@ __global__ void depth_to_space2_kernel(const float* __restrict__ dXs, float* __r
         const long long n = r / C;
         const int og = ((y & 1) * 2 + (x & 1)) * C + c;
         const int g = og / per_group, o = og - g * per_group;
-        dX[i] = dXs[((((long long)g * N + n) * per_group + o) * H2 + (y >> 1)) * W2 + (x >> 1)];
+        const float v = dXs[((((long long)g * N + n) * per_group + o) * H2 + (y >> 1)) * W2 + (x >> 1)];
+        dX[i] = accumulate ? dX[i] + v : v;
     }
 }
 // Xsub[nc][i][j] = X[nc][2i][2j]
@@ -490,9 +510,9 @@ __global__ void subsample2_kernel(const float* __restrict__ X, float* __restrict
         Xsub[i] = X[(nc * H + 2 * ii) * W + 2 * j];
     }
 }
-// dX[nc][y][x] = (y, x both even) ? dXsub[nc][y/2][x/2] : 0
+// dX[nc][y][x] (+)= (y, x both even) ? dXsub[nc][y/2][x/2] : 0
 __global__ void upsample2_zero_kernel(const float* __restrict__ dXsub, float* __restrict__ dX, int H, int W,
-                                      long long total) {
+                                      long long total, int accumulate) {
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -500,64 +520,124 @@ __global__ void upsample2_zero_kernel(const float* __restrict__ dXsub, float* __
         const long long r = i / W;
         const int y = (int)(r % H);
         const long long nc = r / H;
-        dX[i] = ((x | y) & 1) ? 0.f : dXsub[(nc * H2 + (y >> 1)) * W2 + (x >> 1)];
+        const float v = ((x | y) & 1) ? 0.f : dXsub[(nc * H2 + (y >> 1)) * W2 + (x >> 1)];
+        if (accumulate) {
+            if (!((x | y) & 1)) dX[i] += v;
+        } else {
+            dX[i] = v;
+        }
     }
 }
 
-// Where a launch takes its stream, scratch and status word from: a cb_ctx (workspace grown with cudaMalloc) or the
-// static arrays of the allocation-free entry point.
+int relayout_grid(const cb_ctx* ctx, long long n) {
+    long long g = (n + 255) / 256;
+    const long long cap = (long long)ctx->sm_count * 16;
+    return (int)(g > cap ? cap : (g < 1 ? 1 : g));
+}
+
+// Where a launch takes its stream, scratch and status word from: a cb_ctx or the static arrays of the allocation-free
+// entry point.
 struct ConvEnv {
     cudaStream_t stream;
     int sm_count, smem_optin;
-    float* pack;   // scratch for the packed filter (>= pack_bytes)
     int* status;
 };
 
 // Geometry the tensor-core forward / data-gradient kernel covers; fills the derived sizes.
 struct ConvPlan {
-    int Cin, Cout, OCp, NQ, CG, L, KS, shared_rows, nblocks, stages;
-    int ew;   // epilogue warps of the kernel instantiation: 8 (two CTAs per SM) or 16
-    size_t w_bytes;
+    int Cin, Cout, OCp, OCs, nsplit, NQ, CG, L, KS, shared_rows, nblocks, stages;
+    int ew;      // epilogue warps of the kernel instantiation: 8 or 16
+    int per_sm;  // CTAs the plan expects to share an SM (2 for narrow outputs with a small filter, else 1)
+    size_t w_bytes;       // one CTA's slice of the packed filter
+    size_t w_total_bytes; // the whole packed filter
     uint32_t block_bytes, stage_bytes;
 };
 
-static int plan_conv(ConvPlan& q, int smem_optin, const float* X, int Cin, int Cout, int IH, int IW, int FH, int FW,
-                     int pH, int pW) {
+// Development override of the output-channel split (1, 2 or 4); 0 = choose from the tile count.
+int forced_nsplit() {
+    static const int v = [] {
+        const char* e = std::getenv("CB_CONV_NSPLIT");
+        return e ? std::atoi(e) : 0;
+    }();
+    return v;
+}
+
+// Development override of the epilogue warp count (8 or 16); 0 = choose from the output width.
+int forced_ew() {
+    static const int v = [] {
+        const char* e = std::getenv("CB_CONV_EW");
+        return e ? std::atoi(e) : 0;
+    }();
+    return v;
+}
+
+int plan_conv(ConvPlan& q, int smem_optin, int sm_count, const float* X, int N, int Cin, int Cout, int IH, int IW, int FH,
+              int FW, int pH, int pW) {
     // every tap must read within one pixel of the output position: offsets fh - pH and fw - pW in [-1, 1]
     if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
     if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
+    if (FW == 1 && pW != 0) return CB_EUNSUPPORTED;  // the kernel's one-tap form reads the output's own column
     if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
     q.L = 32 / IW;
     if (IH % q.L) return CB_EUNSUPPORTED;
     q.Cin = Cin;
     q.Cout = Cout;
     q.OCp = (q.Cout + 15) / 16 * 16;
-    q.NQ = FW * q.OCp;
-    if (q.NQ > 256 || q.Cin < 1) return CB_EUNSUPPORTED;
+    if (q.Cin < 1) return CB_EUNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) != 0) return CB_EUNSUPPORTED;
     q.CG = (q.Cin + 31) / 32;
-    q.w_bytes = (size_t)FH * q.CG * q.NQ * kRowBytes;
+    q.w_total_bytes = (size_t)FH * q.CG * FW * q.OCp * kRowBytes;
     q.shared_rows = (q.L == 1 && IH % 4 == 0) ? 1 : 0;
     q.nblocks = q.shared_rows ? FH + 3 : FH * 4;
-    // narrow outputs: the 8-epilogue-warp instantiation, sized so that two CTAs fit one SM (shared memory and TMEM halves)
-    q.ew = (q.OCp <= 32 && q.w_bytes <= 40 * 1024) ? 8 : 16;
-    const long long budget = q.ew == 8 ? (long long)(smem_optin < 113 * 1024 ? smem_optin : 113 * 1024) : (long long)smem_optin;
-    const long long cap = budget - 2048 - (long long)q.w_bytes;
-    // as many K steps per stage as leaves a pipeline of at least 4 stages (fewer, larger TMA boxes)
+    const long long tiles = ((long long)N * (IH / q.L) + 3) / 4;
     const int cin8 = (q.Cin + 7) / 8;
-    q.KS = 0;
-    for (int ks = 4; ks >= 1; ks >>= 1) {
-        if (ks > cin8 && ks > 1) continue;
-        const long long st = cap / ((long long)q.nblocks * ks * kCB * kRowBytes);
-        if (st >= 4 || (ks == 1 && st >= 2)) {
-            q.KS = ks;
-            q.stages = (int)(st > kMaxStages ? kMaxStages : st);
-            break;
+    // Candidate splits of the output channels over 1, 2 or 4 CTAs per pixel tile: the widest split that still fits the
+    // resident CTA slots in one wave wins (small feature maps then fill the GPU); each candidate must be launchable.
+    int best = 0;
+    ConvPlan bestq{};
+    bool forced_hit = false;
+    for (int ns = 1; ns <= (forced_nsplit() == 4 ? 4 : 2) && !forced_hit; ns <<= 1) {
+        if (q.OCp % (16 * ns)) break;
+        ConvPlan c = q;
+        c.nsplit = ns;
+        c.OCs = q.OCp / ns;
+        c.NQ = FW * c.OCs;
+        if (c.NQ > 256) continue;
+        c.w_bytes = (size_t)FH * c.CG * c.NQ * kRowBytes;
+        // Two epilogue warps per TMEM lane quarter: with four, the waiting and draining warps took issue slots from the
+        // one thread that feeds the tensor core and the wide layers ran 15 % slower. Narrow outputs with a small filter
+        // are sized so that two CTAs fit one SM (shared memory and TMEM halves).
+        c.ew = 8;
+        if (forced_ew() == 8 || forced_ew() == 16) c.ew = forced_ew();
+        const bool two_per_sm = c.OCs <= 32 && c.w_bytes <= 40 * 1024 && c.ew <= 8;
+        const long long budget = two_per_sm ? (long long)(smem_optin < 113 * 1024 ? smem_optin : 113 * 1024) : (long long)smem_optin;
+        const long long cap = budget - 4096 - (long long)c.w_bytes - 2048LL * c.ew;  // static shared memory, alignment slack;  // 2 KB of store staging per epilogue warp
+        // as many K steps per stage as leaves at least 2 stages: fewer, larger TMA boxes measured faster than a deeper
+        // pipeline of small ones
+        c.KS = 0;
+        for (int ks = 4; ks >= 1; ks >>= 1) {
+            if (ks > cin8 && ks > 1) continue;
+            const long long st = cap / ((long long)c.nblocks * ks * kCB * kRowBytes);
+            if (st >= 2) {
+                c.KS = ks;
+                c.stages = (int)(st > kConvMaxStages ? kConvMaxStages : st);
+                break;
+            }
+        }
+        if (c.KS == 0) continue;
+        if ((cin8 + c.KS - 1) / c.KS * c.KS * FH > kMaxTileUmmas) continue;
+        c.block_bytes = (uint32_t)c.KS * kCB * kRowBytes;
+        c.stage_bytes = (uint32_t)c.nblocks * c.block_bytes;
+        c.per_sm = two_per_sm ? 2 : 1;
+        const long long slots = (long long)sm_count * c.per_sm;
+        forced_hit = forced_nsplit() == ns;
+        if (best == 0 || tiles * ns <= slots || forced_hit) {
+            best = ns;
+            bestq = c;
         }
     }
-    if (q.KS == 0) return CB_EUNSUPPORTED;
-    q.block_bytes = (uint32_t)q.KS * kCB * kRowBytes;
-    q.stage_bytes = (uint32_t)q.nblocks * q.block_bytes;
+    if (best == 0) return CB_EUNSUPPORTED;
+    q = bestq;
     return CB_OK;
 }
 
@@ -566,25 +646,33 @@ struct PackSpec {
     int mode, OC, IC, FHs, FWs, out_first, out_count;
 };
 
-// Packs the filter into env.pack and launches the kernel: Y (N x q.Cout x IH x IW) = taps (FH, FW, pH, pW) over
-// X (N x q.Cin x IH x IW). `err_ctx` may be null (allocation-free entry point).
-static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const PackSpec& ps, const float* W,
-                       const float* X, float* Y, const float* bias, int N, int IH, int IW, int FH, int FW, int pH, int pW,
-                       int relu) {
-    const bool in_kernel = env.pack == nullptr;  // no scratch given: the CTAs pack the filter themselves
-    if (!in_kernel) {
-        const long long total = (long long)q.w_bytes / 4;
-        int grid = (int)((total + 255) / 256);
-        if (grid > env.sm_count * 8) grid = env.sm_count * 8;
-        pack_filter_kernel<<<grid, 256, 0, env.stream>>>(W, env.pack, ps.OC, ps.IC, ps.FHs, ps.FWs, FH, FW, q.OCp, q.CG,
-                                                         ps.mode, ps.out_first, ps.out_count, total);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return check_cuda(err_ctx, e, "pack_filter_kernel launch");
-    }
+PackJob make_job(const PackSpec& ps, const ConvPlan& q, const float* W, float* dst, int FH, int FW) {
+    PackJob j{};
+    j.W = W; j.Wp = dst;
+    j.OC = ps.OC; j.IC = ps.IC; j.FHs = ps.FHs; j.FWs = ps.FWs; j.FHc = FH; j.FWc = FW;
+    j.OCp = q.OCp; j.CG = q.CG; j.mode = ps.mode; j.out_first = ps.out_first; j.out_count = ps.out_count;
+    j.total = (long long)q.w_total_bytes / 4;
+    return j;
+}
+
+int launch_pack(cb_ctx* err_ctx, const ConvEnv& env, const PackJob& j) {
+    int grid = (int)((j.total + 255) / 256);
+    if (grid > env.sm_count * 8) grid = env.sm_count * 8;
+    pack_filter_kernel<<<grid, 256, 0, env.stream>>>(j);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(err_ctx, e, "pack_filter_kernel launch");
+    return CB_OK;
+}
+
+// Launches the kernel on an already packed filter: Y (N x q.Cout x IH x IW) = taps (FH, FW, pH, pW) over
+// X (N x q.Cin x IH x IW). in_batch / out_batch: elements between consecutive images (0 = densely packed).
+int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const float* packed, const float* X, float* Y,
+                const ConvEpilogue& ep, int N, int IH, int IW, int FH, int FW, int pH, int pW, long long in_batch,
+                long long out_batch) {
     ConvParams p{};
     p.N = N; p.Cin = q.Cin; p.H = IH; p.W = IW; p.Cout = q.Cout;
     p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
-    p.OCp = q.OCp; p.NQ = q.NQ; p.CG = q.CG; p.KS = q.KS;
+    p.OCs = q.OCs; p.nsplit = q.nsplit; p.NQ = q.NQ; p.CG = q.CG; p.KS = q.KS;
     p.NCB = (q.Cin + q.KS * kCB - 1) / (q.KS * kCB);
     p.L = q.L; p.LPI = IH / q.L;
     p.shared_rows = q.shared_rows; p.nblocks = q.nblocks;
@@ -598,21 +686,21 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
     p.w_bytes = (uint32_t)q.w_bytes;
     p.block_bytes = q.block_bytes;
     p.stage_bytes = q.stage_bytes;
-    p.Out = Y; p.bias = bias; p.relu = relu;
+    const uint64_t plane = (uint64_t)IH * IW;
+    p.Out = Y;
+    p.out_batch = out_batch ? out_batch : (long long)q.Cout * (long long)plane;
+    p.ep = ep;
     p.status = env.status;
-    p.pack_in_kernel = in_kernel ? 1 : 0;
-    p.pack_mode = ps.mode; p.OCs = ps.OC; p.ICs = ps.IC; p.FHs = ps.FHs; p.FWs = ps.FWs;
-    p.out_first = ps.out_first; p.out_count = ps.out_count;
-    p.Wsrc = W;
     p.trace = err_ctx ? err_ctx->trace : nullptr;
+    const uint64_t in_stride = (uint64_t)(in_batch ? in_batch : (long long)q.Cin * (long long)plane) * 4;
+    if (in_stride & 15u) return fail(err_ctx, CB_EUNSUPPORTED, "convolution: the input batch stride must be a multiple of 4 floats");
 
     CUtensorMap tmIn, tmW;
     int rc;
-    const uint64_t plane = (uint64_t)IH * IW;
     if (q.shared_rows) {
         // 32-wide maps: (w, channel, row, image) so that one box of FH+3 rows lands as [row][channel][128 B]
         uint64_t dims[4] = {32, (uint64_t)q.Cin, (uint64_t)IH, (uint64_t)N};
-        uint64_t str[3] = {plane * 4, 128, (uint64_t)q.Cin * plane * 4};
+        uint64_t str[3] = {plane * 4, 128, in_stride};
         uint32_t box[4] = {32u, (uint32_t)(q.KS * kCB), (uint32_t)q.nblocks, 1u};
         rc = encode_tmap(err_ctx, &tmIn, X, 4, dims, str, box, nullptr, 129);
     } else {
@@ -622,36 +710,66 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
         // extent is below the 128-byte swizzle span would be padded to 128 bytes per inner row in shared memory, so
         // the (W, H) plane is never used as two tensor-map dimensions when W < 32.)
         uint64_t dims[3] = {plane, (uint64_t)q.Cin, (uint64_t)N};
-        uint64_t str[2] = {plane * 4, (uint64_t)q.Cin * plane * 4};
+        uint64_t str[2] = {plane * 4, in_stride};
         uint32_t box[3] = {32u, (uint32_t)(q.KS * kCB), 1u};
         rc = encode_tmap(err_ctx, &tmIn, X, 3, dims, str, box, nullptr, 129);
     }
     if (rc != CB_OK) return rc;
-    if (in_kernel) {
-        tmW = tmIn;  // unused by the kernel in this mode; any valid map will do
-    } else {
-        const uint64_t rows = (uint64_t)FH * q.CG * q.NQ;
-        uint64_t dims[3] = {32, rows, 1};
-        uint64_t str[2] = {128, rows * 128};
-        uint32_t box[3] = {32, (uint32_t)q.NQ, 1};
-        rc = encode_tmap(err_ctx, &tmW, env.pack, 3, dims, str, box, nullptr, 128);
+    {
+        // packed filter as (32 channels, OCp rows, (fh, channel group, fw) planes): a box is FW planes of OCs rows
+        const uint64_t planes = (uint64_t)FH * q.CG * FW;
+        uint64_t dims[3] = {32, (uint64_t)q.OCp, planes};
+        uint64_t str[2] = {128, (uint64_t)q.OCp * 128};
+        uint32_t box[3] = {32, (uint32_t)q.OCs, (uint32_t)FW};
+        rc = encode_tmap(err_ctx, &tmW, packed, 3, dims, str, box, nullptr, 128);
         if (rc != CB_OK) return rc;
     }
-    const size_t smem = q.w_bytes + (size_t)p.stages * q.stage_bytes + 1024;
-    static bool attr_set[64] = {};  // per device: the opt-in shared-memory size is raised to the maximum once
+    // Results leave through TMA unless the epilogue needs the old output before a ReLU, or the output is not 16-byte
+    // aligned in every plane and image (TMA's base and stride rules).
+    const long long out_stride_b = p.out_batch * 4;
+    p.tma_out = (ep.accumulate && ep.relu) ? 0 : (ep.accumulate ? 2 : 1);
+    if ((reinterpret_cast<uintptr_t>(Y) & 15u) || (out_stride_b & 15)) p.tma_out = 0;
+    CUtensorMap tmOut = tmIn;  // placeholder when unused
+    if (p.tma_out) {
+        uint64_t dims[3] = {plane, (uint64_t)q.Cout, (uint64_t)N};
+        uint64_t str[2] = {plane * 4, (uint64_t)out_stride_b};
+        uint32_t box[3] = {32u, 8u, 1u};
+        rc = encode_tmap(err_ctx, &tmOut, Y, 3, dims, str, box, nullptr, 0);
+        if (rc != CB_OK) return rc;
+    }
+    const size_t smem = q.w_bytes + (size_t)p.stages * q.stage_bytes + 2048u * (size_t)q.ew + 1024;
+    // per device: the opt-in shared-memory size is raised to the maximum once (several host threads may race here)
+    static std::once_flag attr_once[64];
+    static cudaError_t attr_error[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(umma_conv_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(umma_conv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 1024);
-        if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel attribute");
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const ConvParams);
+    static const KernelFn kernels[2][4] = {
+        {umma_conv_kernel<8, TAPS_1>, umma_conv_kernel<8, TAPS_3>, umma_conv_kernel<8, TAPS_2L>, umma_conv_kernel<8, TAPS_2R>},
+        {umma_conv_kernel<16, TAPS_1>, umma_conv_kernel<16, TAPS_3>, umma_conv_kernel<16, TAPS_2L>, umma_conv_kernel<16, TAPS_2R>}};
+    auto raise_limits = [&]() -> cudaError_t {
+        for (int a = 0; a < 2; ++a)
+            for (int b = 0; b < 4; ++b) {
+                cudaError_t e = cudaFuncSetAttribute(kernels[a][b], cudaFuncAttributeMaxDynamicSharedMemorySize, env.smem_optin - 3072);
+                if (e != cudaSuccess) return e;
+            }
+        return cudaSuccess;
+    };
+    cudaError_t attr_e;
+    if (dev >= 0 && dev < 64) {
+        std::call_once(attr_once[dev], [&] { attr_error[dev] = raise_limits(); });
+        attr_e = attr_error[dev];
+    } else {
+        attr_e = raise_limits();
     }
-    const int slots = env.sm_count * (q.ew == 8 ? 2 : 1);  // resident CTAs
-    const int grid = p.tiles < slots ? p.tiles : slots;
-    if (q.ew == 8) umma_conv_kernel<8><<<grid, 64 + 32 * 8, smem, env.stream>>>(tmIn, tmW, p);
-    else umma_conv_kernel<16><<<grid, 64 + 32 * 16, smem, env.stream>>>(tmIn, tmW, p);
+    if (attr_e != cudaSuccess) return check_cuda(err_ctx, attr_e, "umma_conv_kernel attribute");
+    const int slots = env.sm_count * q.per_sm;  // resident CTAs
+    int per_split = slots / q.nsplit;
+    if (per_split < 1) per_split = 1;
+    if (per_split > p.tiles) per_split = p.tiles;
+    const int grid = per_split * q.nsplit;
+    const int taps = FW == 1 ? TAPS_1 : (FW == 3 ? TAPS_3 : (pW == 1 ? TAPS_2L : TAPS_2R));
+    kernels[q.ew == 8 ? 0 : 1][taps]<<<grid, 64 + 32 * q.ew, smem, env.stream>>>(tmIn, tmW, tmOut, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel launch");
     return CB_OK;
@@ -659,74 +777,202 @@ static int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, c
 
 }  // namespace
 
-// Small filters are packed by the CTAs themselves (no extra launch, no scratch); large ones (a CTA would spend longer
-// packing than computing its first tile) by the pack kernel into the context workspace, fetched by TMA.
-static int launch_conv_auto(cb_ctx* ctx, ConvEnv env, const ConvPlan& q, const PackSpec& ps, const float* W, const float* X,
-                            float* Y, const float* bias, int N, int IH, int IW, int FH, int FW, int pH, int pW, int relu) {
-    const long long src = (long long)ps.OC * ps.IC * ps.FHs * ps.FWs;
-    env.pack = nullptr;
-    if (src > 12288) {
-        int rc = ensure_workspace(ctx, q.w_bytes);
-        if (rc != CB_OK) return rc;
-        env.pack = static_cast<float*>(ctx->workspace);
-        ctx->launches += 1;
-    }
-    return launch_conv(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
+int launch_space_to_depth2(cb_ctx* ctx, const float* X, float* Xs, int N, int C, int H, int W) {
+    const long long n_el = (long long)N * C * H * W;
+    space_to_depth2_kernel<<<relayout_grid(ctx, n_el), 256, 0, ctx->stream>>>(X, Xs, C, H, W, n_el);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "space_to_depth2_kernel launch");
+    ctx->launches += 1;
+    return CB_OK;
+}
+int launch_subsample2(cb_ctx* ctx, const float* X, float* Xsub, long long NC, int H, int W) {
+    const long long n_sub = NC * (H / 2) * (W / 2);
+    subsample2_kernel<<<relayout_grid(ctx, n_sub), 256, 0, ctx->stream>>>(X, Xsub, NC, H, W, n_sub);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "subsample2_kernel launch");
+    ctx->launches += 1;
+    return CB_OK;
 }
 
-int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const float* bias, int N, int IC, int IH,
-                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, int relu, bool dgrad_of) {
-    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, nullptr, ctx->d_status};
+// ------------------------------------------------------------------------------------------ packed-filter cache
+// With the cache on (cb_conv_cache_filters), a context keeps one packed copy per (filter pointer, geometry, pass) it
+// has seen and re-packs it only after the caller announced a weight update: cb_filters_changed re-packs every cached
+// filter in ONE launch, so a training step pays one pack launch instead of two per convolution. Filters the context's
+// own update calls may have touched (cb_momentum*, cb_tensor_op) are re-packed lazily by the next convolution that
+// uses them.
+struct FilterCacheEntry {
+    PackJob job;
+    long long version;  // value of cb_ctx::filter_version when the packed copy was last written
+};
+struct FilterCache {
+    std::vector<FilterCacheEntry> entries;
+    PackJob* dev_table = nullptr;
+    size_t dev_table_entries = 0;
+    long long biggest = 0;
+};
+
+static bool same_job(const PackJob& a, const PackJob& b) {
+    return a.W == b.W && a.OC == b.OC && a.IC == b.IC && a.FHs == b.FHs && a.FWs == b.FWs && a.FHc == b.FHc &&
+           a.FWc == b.FWc && a.OCp == b.OCp && a.CG == b.CG && a.mode == b.mode && a.out_first == b.out_first &&
+           a.out_count == b.out_count;
+}
+
+void filter_cache_destroy(cb_ctx* ctx) {
+    FilterCache* fc = static_cast<FilterCache*>(ctx->filter_cache);
+    if (!fc) return;
+    for (FilterCacheEntry& e : fc->entries) cudaFree(e.job.Wp);
+    if (fc->dev_table) cudaFree(fc->dev_table);
+    delete fc;
+    ctx->filter_cache = nullptr;
+}
+
+// Packed filter for this call: from the cache (packing it now if it is new or stale) or, with the cache off, packed
+// into the context workspace.
+static int packed_filter(cb_ctx* ctx, const ConvEnv& env, const ConvPlan& q, const PackSpec& ps, const float* W, int FH,
+                         int FW, const float** out) {
+    if (!ctx->filter_cache_on) {
+        int rc = ensure_workspace(ctx, q.w_total_bytes);
+        if (rc != CB_OK) return rc;
+        const PackJob j = make_job(ps, q, W, static_cast<float*>(ctx->workspace), FH, FW);
+        rc = launch_pack(ctx, env, j);
+        if (rc != CB_OK) return rc;
+        ctx->launches += 1;
+        *out = j.Wp;
+        return CB_OK;
+    }
+    if (!ctx->filter_cache) ctx->filter_cache = new FilterCache();
+    FilterCache* fc = static_cast<FilterCache*>(ctx->filter_cache);
+    PackJob want = make_job(ps, q, W, nullptr, FH, FW);
+    FilterCacheEntry* hit = nullptr;
+    for (FilterCacheEntry& e : fc->entries)
+        if (same_job(e.job, want)) { hit = &e; break; }
+    if (!hit) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return fail(ctx, CB_ENOMEM, "a convolution filter was seen for the first time while the stream is being captured: "
+                                        "run the same calls once before the capture so that its packed copy exists");
+        void* d = nullptr;
+        cudaError_t e = cudaMalloc(&d, q.w_total_bytes);
+        if (e != cudaSuccess) {
+            check_cuda(ctx, e, "packed filter cudaMalloc");
+            return CB_ENOMEM;
+        }
+        want.Wp = static_cast<float*>(d);
+        fc->entries.push_back(FilterCacheEntry{want, -1});
+        hit = &fc->entries.back();
+    }
+    if (hit->version != ctx->filter_version) {
+        int rc = launch_pack(ctx, env, hit->job);
+        if (rc != CB_OK) return rc;
+        ctx->launches += 1;
+        hit->version = ctx->filter_version;
+    }
+    *out = hit->job.Wp;
+    return CB_OK;
+}
+
+// Re-packs every cached filter in one launch and marks them current.
+int filter_cache_repack_all(cb_ctx* ctx) {
+    ctx->filter_version += 1;
+    FilterCache* fc = static_cast<FilterCache*>(ctx->filter_cache);
+    if (!ctx->filter_cache_on || !fc || fc->entries.empty()) return CB_OK;
+    if (fc->dev_table_entries != fc->entries.size()) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return CB_OK;  // filters first seen after the last table build: they re-pack lazily at their next use
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "filter table rebuild");
+        if (fc->dev_table) cudaFree(fc->dev_table);
+        fc->dev_table = nullptr;
+        std::vector<PackJob> host(fc->entries.size());
+        fc->biggest = 0;
+        for (size_t i = 0; i < host.size(); ++i) {
+            host[i] = fc->entries[i].job;
+            if (host[i].total > fc->biggest) fc->biggest = host[i].total;
+        }
+        void* d = nullptr;
+        e = cudaMalloc(&d, sizeof(PackJob) * host.size());
+        if (e == cudaSuccess) e = cudaMemcpy(d, host.data(), sizeof(PackJob) * host.size(), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "filter table upload");
+        fc->dev_table = static_cast<PackJob*>(d);
+        fc->dev_table_entries = host.size();
+    }
+    int gx = (int)((fc->biggest + 255) / 256);
+    if (gx > 64) gx = 64;
+    if (gx < 1) gx = 1;
+    pack_filter_table_kernel<<<dim3(gx, (unsigned)fc->dev_table_entries), 256, 0, ctx->stream>>>(fc->dev_table);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "pack_filter_table_kernel launch");
+    ctx->launches += 1;
+    for (FilterCacheEntry& en : fc->entries) en.version = ctx->filter_version;
+    return CB_OK;
+}
+
+static int conv_on_packed(cb_ctx* ctx, const ConvEnv& env, const ConvPlan& q, const PackSpec& ps, const float* W,
+                          const float* X, float* Y, const ConvEpilogue& ep, int N, int IH, int IW, int FH, int FW, int pH,
+                          int pW, long long in_batch, long long out_batch) {
+    const float* packed = nullptr;
+    int rc = packed_filter(ctx, env, q, ps, W, FH, FW, &packed);
+    if (rc != CB_OK) return rc;
+    rc = launch_conv(ctx, env, q, packed, X, Y, ep, N, IH, IW, FH, FW, pH, pW, in_batch, out_batch);
+    if (rc != CB_OK) return rc;
+    ctx->launches += 1;
+    return CB_OK;
+}
+
+// Forward (dgrad_of = false: Y = conv(W, X), full epilogue) or data gradient (dgrad_of = true: X is dY, Y is dX; of the
+// epilogue only `accumulate` applies). Returns CB_EUNSUPPORTED, before any work is queued, for geometries outside the
+// tensor-core kernel.
+int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
+                  int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, bool dgrad_of, long long in_batch,
+                  long long out_batch) {
+    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, ctx->d_status};
     ConvPlan q{};
     int rc;
     if (sH == 1 && sW == 1) {
         // ---- stride 1: 1x1 (pad 0) or 3x3 (pad 1) per axis
         if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
         if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
-        rc = plan_conv(q, ctx->max_smem_optin, X, dgrad_of ? OC : IC, dgrad_of ? IC : OC, IH, IW, FH, FW, pH, pW);
+        rc = plan_conv(q, ctx->max_smem_optin, ctx->sm_count, X, N, dgrad_of ? OC : IC, dgrad_of ? IC : OC, IH, IW, FH, FW, pH, pW);
         if (rc != CB_OK) return rc;
         const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, FH, FW, 0, 0};
-        rc = launch_conv_auto(ctx, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu);
+        rc = conv_on_packed(ctx, env, q, ps, W, X, Y, ep, N, IH, IW, FH, FW, pH, pW, in_batch, out_batch);
         if (rc != CB_OK) return rc;
-        ctx->launches += 1;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
-    // ---- stride 2 (square): 3x3 pad 1 through the 4 input phases, 1x1 pad 0 through phase (0,0)
+    // ---- stride 2 (square): 3x3 pad 1 through the 4 input phases, 1x1 pad 0 through phase (0,0); dense tensors only
     if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
     if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;
+    if (in_batch || out_batch) return CB_EUNSUPPORTED;
     const int H2 = IH / 2, W2 = IW / 2;
     const long long plane2 = (long long)H2 * W2;
-    const int launch_threads = 256;
-    auto grid_of = [&](long long n) {
-        long long g = (n + launch_threads - 1) / launch_threads;
-        const long long cap = (long long)ctx->sm_count * 16;
-        return (int)(g > cap ? cap : (g < 1 ? 1 : g));
-    };
+    const ConvEpilogue plain{};
     if (FH == 1) {
         // Y = W * X[:, :, ::2, ::2]  /  dX[:, :, ::2, ::2] = W^T dY, zero elsewhere
-        rc = plan_conv(q, ctx->max_smem_optin, dgrad_of ? X : nullptr /* the sub-sampled copy is aligned */, dgrad_of ? OC : IC,
-                       dgrad_of ? IC : OC, H2, W2, 1, 1, 0, 0);
+        rc = plan_conv(q, ctx->max_smem_optin, ctx->sm_count, dgrad_of ? X : nullptr /* the sub-sampled copy is aligned */, N,
+                       dgrad_of ? OC : IC, dgrad_of ? IC : OC, H2, W2, 1, 1, 0, 0);
         if (rc != CB_OK) return rc;
         const size_t sub_bytes = (size_t)N * IC * plane2 * sizeof(float);
         rc = ensure_workspace2(ctx, sub_bytes);
         if (rc != CB_OK) return rc;
         float* sub = static_cast<float*>(ctx->workspace2);
         const PackSpec ps{dgrad_of ? PACK_DGRAD : PACK_FWD, OC, IC, 1, 1, 0, 0};
-        const long long n_sub = (long long)N * IC * plane2;
         if (!dgrad_of) {
-            subsample2_kernel<<<grid_of(n_sub), launch_threads, 0, ctx->stream>>>(X, sub, (long long)N * IC, IH, IW, n_sub);
-            rc = launch_conv_auto(ctx, env, q, ps, W, sub, Y, bias, N, H2, W2, 1, 1, 0, 0, relu);
+            rc = launch_subsample2(ctx, X, sub, (long long)N * IC, IH, IW);
+            if (rc == CB_OK) rc = conv_on_packed(ctx, env, q, ps, W, sub, Y, ep, N, H2, W2, 1, 1, 0, 0, 0, 0);
         } else {
-            rc = launch_conv_auto(ctx, env, q, ps, W, X /* = dY */, sub, nullptr, N, H2, W2, 1, 1, 0, 0, 0);
+            rc = conv_on_packed(ctx, env, q, ps, W, X /* = dY */, sub, plain, N, H2, W2, 1, 1, 0, 0, 0, 0);
             const long long n_full = (long long)N * IC * IH * IW;
-            if (rc == CB_OK)
-                upsample2_zero_kernel<<<grid_of(n_full), launch_threads, 0, ctx->stream>>>(sub, Y /* = dX */, IH, IW, n_full);
+            if (rc == CB_OK) {
+                upsample2_zero_kernel<<<relayout_grid(ctx, n_full), 256, 0, ctx->stream>>>(sub, Y /* = dX */, IH, IW, n_full,
+                                                                                           ep.accumulate ? 1 : 0);
+                ctx->launches += 1;
+            }
         }
         if (rc != CB_OK) return rc;
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return check_cuda(ctx, e, "stride-2 1x1 convolution");
-        ctx->launches += 2;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
@@ -737,14 +983,13 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
         rc = ensure_workspace2(ctx, s2d_bytes);
         if (rc != CB_OK) return rc;
         float* Xs = static_cast<float*>(ctx->workspace2);
-        rc = plan_conv(q, ctx->max_smem_optin, Xs, C4, OC, H2, W2, 2, 2, 1, 1);
+        rc = plan_conv(q, ctx->max_smem_optin, ctx->sm_count, Xs, N, C4, OC, H2, W2, 2, 2, 1, 1);
         if (rc != CB_OK) return rc;
-        const long long n_el = (long long)N * C4 * plane2;
-        space_to_depth2_kernel<<<grid_of(n_el), launch_threads, 0, ctx->stream>>>(X, Xs, IC, IH, IW, n_el);
+        rc = launch_space_to_depth2(ctx, X, Xs, N, IC, IH, IW);
+        if (rc != CB_OK) return rc;
         const PackSpec ps{PACK_S2_FWD, OC, IC, 3, 3, 0, 0};
-        rc = launch_conv_auto(ctx, env, q, ps, W, Xs, Y, bias, N, H2, W2, 2, 2, 1, 1, relu);
+        rc = conv_on_packed(ctx, env, q, ps, W, Xs, Y, ep, N, H2, W2, 2, 2, 1, 1, 0, 0);
         if (rc != CB_OK) return rc;
-        ctx->launches += 2;
         ctx->last_kernel = "umma_tf32";
         return CB_OK;
     }
@@ -757,388 +1002,22 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const f
     rc = ensure_workspace2(ctx, s2d_bytes);
     if (rc != CB_OK) return rc;
     float* dXs = static_cast<float*>(ctx->workspace2);
-    rc = plan_conv(q, ctx->max_smem_optin, X /* = dY */, OC, per_group, H2, W2, 2, 2, 0, 0);
+    rc = plan_conv(q, ctx->max_smem_optin, ctx->sm_count, X /* = dY */, N, OC, per_group, H2, W2, 2, 2, 0, 0);
     if (rc != CB_OK) return rc;
     for (int g = 0; g < groups; ++g) {
         const PackSpec ps{PACK_S2_DGRAD, OC, IC, 3, 3, g * per_group, per_group};
-        rc = launch_conv_auto(ctx, env, q, ps, W, X /* = dY */, dXs + (size_t)g * N * per_group * plane2, nullptr, N, H2, W2, 2, 2,
-                         0, 0, 0);
+        rc = conv_on_packed(ctx, env, q, ps, W, X /* = dY */, dXs + (size_t)g * N * per_group * plane2, plain, N, H2, W2, 2, 2,
+                            0, 0, 0, 0);
         if (rc != CB_OK) return rc;
     }
     const long long n_full = (long long)N * IC * IH * IW;
-    depth_to_space2_kernel<<<grid_of(n_full), launch_threads, 0, ctx->stream>>>(dXs, Y /* = dX */, N, IC, IH, IW, per_group,
-                                                                                 n_full);
+    depth_to_space2_kernel<<<relayout_grid(ctx, n_full), 256, 0, ctx->stream>>>(dXs, Y /* = dX */, N, IC, IH, IW, per_group,
+                                                                                n_full, ep.accumulate ? 1 : 0);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "depth_to_space2_kernel launch");
-    ctx->launches += groups + 1;
-    ctx->last_kernel = "umma_tf32";
-    return CB_OK;
-}
-
-namespace {
-
-// ------------------------------------------------------------------------------------------ weight gradient
-// dW[oc][c][fh][fw] = sum over output pixels of dY[oc][pix] * X[c][pix shifted by (fh-pH, fw-pW)]: a contraction
-// over pixels, so both operands are K-major (32 pixels of one channel plane = one 128-byte row, standard 128-byte
-// swizzle). Per line of 32 output pixels a stage holds
-//   A: FH blocks [Cp channel rows][32 px] of X, fetched at the vertically shifted pixel offsets (UMMA M side,
-//      rows stacked as (fh, c); 128 rows per M tile), and
-//   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
-//      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
-//      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
-// Every CTA walks its share of the lines accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs),
-// writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
-struct WgradParams {
-    int N, Cin, H, W, OC;
-    int FH, FW, pH, pW;
-    int Cp, OCp, NQ, mtiles, rowsA;  // rowsA = FH * Cp valid accumulator rows
-    int L, LPI;
-    long long total_lines;
-    int stages, tmem_cols;
-    uint32_t stage_bytes, a_bytes;
-    float* partial;                  // [gridDim.x][mtiles * 128][NQ]
-    int* status;
-};
-
-struct __align__(8) WgradSmem {
-    uint64_t full[kMaxStages];
-    uint64_t empty[kMaxStages];
-    uint64_t xf[kMaxStages];
-    uint64_t tfull;
-    uint32_t tmem_base;
-    int abort_flag;
-};
-
-// 16-byte chunk q of the 128-byte row at row_addr under the standard 128-byte swizzle (chunk ^= row index mod 8)
-__device__ __forceinline__ uint32_t sw128_chunk(uint32_t row_addr, int q) {
-    return row_addr + ((((uint32_t)q) ^ ((row_addr >> 7) & 7u)) << 4);
-}
-
-constexpr int kShiftWarps = 8;  // one scheduler cannot hide the shared-memory latencies of a single warp
-
-// One 16-byte chunk (pixels 4q .. 4q+3) of the horizontally shifted copies of a dY row: row_m1 (tap offset -1: pairs
-// X[px] with dY[px + 1]) and row_p1 (tap offset +1: pairs X[px] with dY[px - 1]); zeros enter at the edges of the
-// W-wide image rows packed in the line; an address of 0 skips that copy.
-__device__ __forceinline__ void shift_dy_chunk(uint32_t src_row, uint32_t row_m1, uint32_t row_p1, int q, int W) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(sw128_chunk(src_row, q)));
-    float left = 0.f, right = 0.f;
-    if (q > 0) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(left) : "r"(sw128_chunk(src_row, q - 1) + 12u));
-    if (q < 7) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(right) : "r"(sw128_chunk(src_row, q + 1)));
-    const int x0 = 4 * q, wm = W - 1;
-    if (row_m1) {
-        const float a0 = ((x0 & wm) < wm) ? v.y : 0.f, a1 = (((x0 + 1) & wm) < wm) ? v.z : 0.f;
-        const float a2 = (((x0 + 2) & wm) < wm) ? v.w : 0.f, a3 = (((x0 + 3) & wm) < wm) ? right : 0.f;
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_m1, q)), "f"(a0), "f"(a1), "f"(a2), "f"(a3) : "memory");
-    }
-    if (row_p1) {
-        const float b0 = ((x0 & wm) >= 1) ? left : 0.f, b1 = (((x0 + 1) & wm) >= 1) ? v.x : 0.f;
-        const float b2 = (((x0 + 2) & wm) >= 1) ? v.y : 0.f, b3 = (((x0 + 3) & wm) >= 1) ? v.z : 0.f;
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_p1, q)), "f"(b0), "f"(b1), "f"(b2), "f"(b3) : "memory");
-    }
-}
-
-__global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
-    umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmdY,
-                      const WgradParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ WgradSmem ws;
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    volatile int* abort_flag = &ws.abort_flag;
-    const uint32_t st_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t set_bytes = (uint32_t)p.OCp * kRowBytes;
-    const int centre = p.pW;  // (fw, oc) rows of the N side: the unshifted copy is the tap with fw - pW == 0
-
-    if (threadIdx.x == 0) {
-        ws.abort_flag = 0;
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(smem_u32(&ws.full[s]), 1);
-            mbar_init(smem_u32(&ws.empty[s]), 1);
-            mbar_init(smem_u32(&ws.xf[s]), 32 * kShiftWarps);
-        }
-        mbar_init(smem_u32(&ws.tfull), 1);
-        mbar_fence_init();
-        tma_prefetch_desc(&tmX);
-        tma_prefetch_desc(&tmdY);
-    }
-    __syncthreads();
-    if (warp == 1) {
-        tmem_alloc(smem_u32(&ws.tmem_base), (uint32_t)p.tmem_cols);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = ws.tmem_base;
-
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        uint32_t s = 0, ph = 0;
-        bool ok = true;
-        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
-            ok = warp_wait(smem_u32(&ws.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
-            if (!ok) break;
-            if (lane == 0) {
-                const uint32_t full = smem_u32(&ws.full[s]);
-                const uint32_t stg = st_base + s * p.stage_bytes;
-                const int gi = (int)g;  // total_lines < 2^29 (checked on the host)
-                const int n = gi / p.LPI;
-                const int h0 = (gi - n * p.LPI) * p.L;
-                mbar_expect_tx(full, p.a_bytes + set_bytes);
-                for (int fh = 0; fh < p.FH; ++fh)
-                    tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
-                tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
-            }
-            __syncwarp();
-            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ UMMA issuer
-        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 0u, 0u);
-        const uint64_t desc0 = umma_smem_desc(0, 16u, 1024u, UMMA_SW_128B);  // K-major 128-byte rows; address added per stage
-        uint32_t s = 0, ph = 0;
-        bool ok = true;
-        bool first_line = true;
-        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
-            ok = warp_wait(smem_u32(&ws.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
-            if (!ok) break;
-            if (p.FW > 1) {
-                ok = warp_wait(smem_u32(&ws.xf[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM);
-                if (!ok) break;
-            }
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t stg = st_base + s * p.stage_bytes;
-                const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
-                const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
-                const uint32_t first = first_line ? 0u : 1u;
-                for (int m = 0; m < p.mtiles; ++m) {
-                    const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
-                    const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
-                    umma_tf32(d, dA, dB0, idesc, first);
-                    umma_tf32(d, dA + 2, dB0 + 2, idesc, 1u);
-                    umma_tf32(d, dA + 4, dB0 + 4, idesc, 1u);
-                    umma_tf32(d, dA + 6, dB0 + 6, idesc, 1u);
-                }
-                tc_commit(smem_u32(&ws.empty[s]));
-                if (g + gridDim.x >= p.total_lines) tc_commit(smem_u32(&ws.tfull));
-            }
-            __syncwarp();
-            first_line = false;
-            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
-        }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------ epilogue: partial sums to the workspace
-        const int quarter = warp & 3;
-        bool ok = mbar_wait(smem_u32(&ws.tfull), 0, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            tc_fence_after();
-            const int rows_tot = p.mtiles * 128;
-            for (int m = 0; m < p.mtiles; ++m) {
-                const int r = m * 128 + 32 * quarter + lane;
-                float* dst = p.partial + ((long long)blockIdx.x * rows_tot + r) * p.NQ;
-                const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
-                for (int c = 0; c < p.NQ; c += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(t_row + (uint32_t)c, v);
-                    tmem_ld_wait();
-                    if (r < p.rowsA) {
-#pragma unroll
-                        for (int e = 0; e < 16; e += 4)
-                            *reinterpret_cast<float4*>(dst + c + e) =
-                                make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
-                                            __uint_as_float(v[e + 3]));
-                    }
-                }
-            }
-        }
-    } else {
-        // ------------------------------------------------------------ shift warps: fw = 0 and fw = 2 copies of dY
-        if (p.FW > 1) {
-            const int t = threadIdx.x - 192;
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
-                ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
-                if (!ok) break;
-                for (int item = t; item < p.OCp * 8; item += 32 * kShiftWarps) {
-                    const int row = item >> 3, q = item & 7;
-                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)row * kRowBytes;
-                    const uint32_t src = b0 + (uint32_t)centre * set_bytes;
-                    const uint32_t m1 = centre >= 1 ? src - set_bytes : 0u;             // tap fw = pW - 1
-                    const uint32_t p1 = centre + 1 < p.FW ? src + set_bytes : 0u;       // tap fw = pW + 1
-                    shift_dy_chunk(src, m1, p1, q, p.W);
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ws.xf[s]));
-                if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
-            }
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
-    }
-}
-
-// dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
-// s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
-__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
-                                                           int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
-                                                           int OC, int OCp, int FH, int FW, int accumulate, int s2,
-                                                           int IC_src) {
-    // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
-    // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
-    __shared__ float red[8][33];
-    const long long total = (long long)rowsA * NQ;
-    const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
-    const int grp = threadIdx.y;
-    float s = 0.f;
-    if (i < total) {
-        const long long pstride = (long long)rows_tot * NQ;
-        const float* src = partial + i;  // (r, col) of the partial layout is exactly element i
-#pragma unroll 4
-        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * pstride);
-    }
-    red[grp][threadIdx.x] = s;
-    __syncthreads();
-    if (grp != 0 || i >= total) return;
-    float sum = 0.f;
-#pragma unroll
-    for (int g = 0; g < 8; ++g) sum += red[g][threadIdx.x];
-    const int col = (int)(i % NQ);
-    const int r = (int)(i / NQ);
-    const int fh = r / Cp, c = r - fh * Cp;
-    const int fw = col / OCp, oc = col - fw * OCp;
-    if (c >= Cin || oc >= OC) return;
-    float* dst;
-    if (!s2) {
-        dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
-    } else {
-        const int phase = c / IC_src, cc = c - phase * IC_src;
-        const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
-        if (sh < 0 || sw < 0) return;
-        dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
-    }
-    *dst = accumulate ? *dst + sum : sum;
-}
-
-}  // namespace
-
-// dW (+)= contraction over the pixels of N x Cin x IH x IW planes `X` and N x OC x IH x IW planes `dY` with taps
-// (FH, FW, pH, pW) in the same-size convention of the forward kernel. s2 / IC_src: see wgrad_reduce_kernel.
-static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int Cin, int IH, int IW, int OC, int FH,
-                      int FW, int pH, int pW, int accumulate, int s2, int IC_src) {
-    if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
-    if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
-    if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
-    const int L = 32 / IW;
-    if (IH % L) return CB_EUNSUPPORTED;
-    const int Cp = (Cin + 7) / 8 * 8;
-    const int OCp = (OC + 15) / 16 * 16;
-    const int NQ = FW * OCp;
-    const int rowsA = FH * Cp;
-    const int mtiles = (rowsA + 127) / 128;
-    if (NQ > 256 || Cp > 256 || OCp > 128 || mtiles * NQ > 512) return CB_EUNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(dY) & 15u)) return CB_EUNSUPPORTED;
-    int rows_stage = rowsA + NQ;
-    if (rows_stage < mtiles * 128) rows_stage = mtiles * 128;
-    const uint32_t stage_bytes = ((uint32_t)rows_stage * kRowBytes + 1023u) & ~1023u;
-    long long stages = ((long long)ctx->max_smem_optin - 2048) / stage_bytes;
-    if (stages < 2) return CB_EUNSUPPORTED;
-    if (stages > kMaxStages) stages = kMaxStages;
-
-    WgradParams p{};
-    p.N = N; p.Cin = Cin; p.H = IH; p.W = IW; p.OC = OC;
-    p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
-    p.Cp = Cp; p.OCp = OCp; p.NQ = NQ; p.mtiles = mtiles; p.rowsA = rowsA;
-    p.L = L; p.LPI = IH / L;
-    p.total_lines = (long long)N * p.LPI;
-    if (p.total_lines > (1LL << 29)) return CB_EUNSUPPORTED;
-    p.stages = (int)stages;
-    int cols = 32;
-    while (cols < mtiles * NQ) cols <<= 1;
-    p.tmem_cols = cols;
-    p.stage_bytes = stage_bytes;
-    p.a_bytes = (uint32_t)rowsA * kRowBytes;
-    p.status = ctx->d_status;
-    const int grid = (int)(p.total_lines < ctx->sm_count ? p.total_lines : ctx->sm_count);
-    const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
-    int rc = ensure_workspace(ctx, part_bytes);
-    if (rc != CB_OK) return rc;
-    p.partial = static_cast<float*>(ctx->workspace);
-
-    CUtensorMap tmX, tmdY;
-    {
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)Cin * IH * IW * 4};
-        uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
-        rc = encode_tmap(ctx, &tmX, X, 3, dims, str, box, nullptr, 128);
-        if (rc != CB_OK) return rc;
-    }
-    {
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)OC * IH * IW * 4};
-        uint32_t box[3] = {32u, (uint32_t)OCp, 1u};
-        rc = encode_tmap(ctx, &tmdY, dY, 3, dims, str, box, nullptr, 128);
-        if (rc != CB_OK) return rc;
-    }
-    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
-    umma_wgrad_kernel<<<grid, 192 + 32 * kShiftWarps, smem, ctx->stream>>>(tmX, tmdY, p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
-    const long long total = (long long)rowsA * NQ;
-    int rgrid = (int)((total + 31) / 32);
-    wgrad_reduce_kernel<<<rgrid, dim3(32, 8), 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
-                                                         accumulate ? 1 : 0, s2, IC_src);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
-    ctx->launches += 2;
-    ctx->last_kernel = "umma_tf32";
-    return CB_OK;
-}
-
-int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate) {
-    if (sH == 1 && sW == 1) {
-        if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
-        if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
-        return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC);
-    }
-    if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
-    if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;
-    const int H2 = IH / 2, W2 = IW / 2;
-    if (W2 != 8 && W2 != 16 && W2 != 32) return CB_EUNSUPPORTED;
-    const long long plane2 = (long long)H2 * W2;
-    auto grid_of = [&](long long n) {
-        long long g = (n + 255) / 256;
-        const long long cap = (long long)ctx->sm_count * 16;
-        return (int)(g > cap ? cap : (g < 1 ? 1 : g));
-    };
-    if (FH == 1) {
-        const long long n_sub = (long long)N * IC * plane2;
-        int rc = ensure_workspace2(ctx, (size_t)n_sub * sizeof(float));
-        if (rc != CB_OK) return rc;
-        float* sub = static_cast<float*>(ctx->workspace2);
-        subsample2_kernel<<<grid_of(n_sub), 256, 0, ctx->stream>>>(X, sub, (long long)N * IC, IH, IW, n_sub);
-        ctx->launches += 1;
-        return wgrad_core(ctx, dY, sub, dW, N, IC, H2, W2, OC, 1, 1, 0, 0, accumulate, 0, IC);
-    }
-    if (4 * IC > 256) return CB_EUNSUPPORTED;
-    const long long n_el = (long long)N * 4 * IC * plane2;
-    int rc = ensure_workspace2(ctx, (size_t)n_el * sizeof(float));
-    if (rc != CB_OK) return rc;
-    float* Xs = static_cast<float*>(ctx->workspace2);
-    space_to_depth2_kernel<<<grid_of(n_el), 256, 0, ctx->stream>>>(X, Xs, IC, IH, IW, n_el);
     ctx->launches += 1;
-    return wgrad_core(ctx, dY, Xs, dW, N, 4 * IC, H2, W2, OC, 2, 2, 1, 1, accumulate, 1, IC);
+    ctx->last_kernel = "umma_tf32";
+    return CB_OK;
 }
 
 // ------------------------------------------------------------------------------------------ allocation-free forward
@@ -1155,7 +1034,9 @@ static __device__ __align__(256) float g_noalloc_pack[kNoAllocPackFloats];
 static __device__ __align__(16) int g_noalloc_status;
 
 struct NoAllocDevice {
-    bool ready = false;
+    std::once_flag once;
+    cudaError_t init_error = cudaSuccess;
+    int major = 0;
     float* pack = nullptr;  // device address of g_noalloc_pack on this GPU (the symbol itself is a host stand-in)
     int* status = nullptr;
     int sm_count = 0;
@@ -1167,6 +1048,43 @@ NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
 int noalloc_fail(char* err, int err_len, int code, const char* msg) {
     if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", msg);
     return code;
+}
+
+// Makes `device` current for the duration of a call and puts the caller's device back on every return path.
+struct DeviceScope {
+    int prev = -1;
+    cudaError_t error;
+    explicit DeviceScope(int device) {
+        error = cudaGetDevice(&prev);
+        if (error == cudaSuccess && prev != device) error = cudaSetDevice(device);
+    }
+    ~DeviceScope() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+// Once per device, with that device current: resolves the device addresses of the static arrays and reads the
+// attributes the launch needs. Safe when several host threads make their first call at the same time.
+NoAllocDevice* noalloc_device(int device, char* err, int err_len, int* rc) {
+    NoAllocDevice& d = g_noalloc_dev[device];
+    std::call_once(d.once, [&] {
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.pack), g_noalloc_pack);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_noalloc_status);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, device);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+        d.init_error = e;
+    });
+    if (d.init_error != cudaSuccess) {
+        *rc = noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(d.init_error));
+        return nullptr;
+    }
+    if (d.major != 10) {
+        *rc = noalloc_fail(err, err_len, CB_EUNSUPPORTED, "this library only carries sm_100a code");
+        return nullptr;
+    }
+    return &d;
 }
 
 }  // namespace
@@ -1196,34 +1114,56 @@ extern "C" int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W
     }
     if (N == 0) return CB_OK;
 
-    cudaError_t e = cudaSetDevice(device);
-    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-    NoAllocDevice& d = g_noalloc_dev[device];
-    if (!d.ready) {
-        // once per device, with that device current: resolve the device addresses of the static arrays
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.pack), g_noalloc_pack);
-        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_noalloc_status);
-        if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-        int major = 0;
-        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
-        if (major != 10) return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "this library only carries sm_100a code");
-        cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
-        cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
-        d.ready = true;
-    }
+    DeviceScope scope(device);
+    if (scope.error != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(scope.error));
+    int rc = CB_OK;
+    NoAllocDevice* d = noalloc_device(device, err, err_len, &rc);
+    if (!d) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
     ConvPlan q{};
-    if (plan_conv(q, d.smem_optin, X, IC, OC, IH, IW, FH, FW, pH, pW) != CB_OK)
+    if (plan_conv(q, d->smem_optin, d->sm_count, X, N, IC, OC, IH, IW, FH, FW, pH, pW) != CB_OK)
         return noalloc_fail(err, err_len, CB_EUNSUPPORTED, "geometry outside the tensor-core convolution kernel");
-    // the scratch keeps the previous call's contents: the pack kernel rewrites all w_bytes (padding included) and
-    // the status word is cleared, both in stream order
-    e = cudaMemsetAsync(d.status, 0, sizeof(int), stream);
-    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
-    ConvEnv env{stream, d.sm_count, d.smem_optin, d.pack, d.status};
+    // The scratch keeps the previous call's contents: the pack kernel rewrites all w_bytes (padding included). The
+    // status word is NOT cleared here, so that a device-side timeout of an earlier call stays visible until
+    // cb_conv_fwd_noalloc_status reads (and clears) it.
+    ConvEnv env{stream, d->sm_count, d->smem_optin, d->status};
     const PackSpec ps{PACK_FWD, OC, IC, FH, FW, 0, 0};
-    if (launch_conv(nullptr, env, q, ps, W, X, Y, bias, N, IH, IW, FH, FW, pH, pW, relu) != CB_OK)
-        return noalloc_fail(err, err_len, CB_ECUDA, "kernel launch or tensor map encoding failed");
+    cb_ctx messages;  // host-side only: collects the text of a CUDA / tensor-map error; owns no device memory
+    messages.device = device;
+    ConvEpilogue ep{};
+    ep.bias = bias;
+    ep.relu = relu ? 1 : 0;
+    rc = launch_pack(&messages, env, make_job(ps, q, W, d->pack, FH, FW));
+    if (rc == CB_OK) rc = launch_conv(&messages, env, q, d->pack, X, Y, ep, N, IH, IW, FH, FW, pH, pW, 0, 0);
+    if (rc != CB_OK)
+        return noalloc_fail(err, err_len, rc, messages.last_error.empty() ? "kernel launch or tensor map encoding failed"
+                                                                          : messages.last_error.c_str());
+    return CB_OK;
+}
+
+extern "C" int cb_conv_fwd_noalloc_status(int device, void* cuda_stream, char* err, int err_len) {
+    using namespace cb;
+    if (err && err_len > 0) err[0] = 0;
+    if (device < 0 || device >= kNoAllocMaxDevices) return noalloc_fail(err, err_len, CB_EINVAL, "device index out of range");
+    DeviceScope scope(device);
+    if (scope.error != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(scope.error));
+    int rc = CB_OK;
+    NoAllocDevice* d = noalloc_device(device, err, err_len, &rc);
+    if (!d) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    cudaError_t e = cudaStreamSynchronize(stream);
+    int st = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&st, d->status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return noalloc_fail(err, err_len, CB_ECUDA, cudaGetErrorString(e));
+    if (st != 0) {
+        e = cudaMemsetAsync(d->status, 0, sizeof(int), stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        char msg[160];
+        snprintf(msg, sizeof(msg), "a bounded device-side wait of cb_conv_fwd_noalloc expired: device status %d (%s)", st,
+                 status_name(st));
+        return noalloc_fail(err, err_len, CB_ETIMEOUT, msg);
+    }
     return CB_OK;
 }

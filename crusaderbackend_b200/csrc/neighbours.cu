@@ -753,6 +753,7 @@ int cb_relu_grad(cb_ctx* ctx, const float* X, const float* dY, float* dX, long l
 
 int cb_tensor_op(cb_ctx* ctx, int op, float* A, const float* B, float scalar, long long n) {
     if (int rc_enter = enter(ctx)) return rc_enter;
+    ctx->filter_version += 1;  // A may be a convolution filter: cached packed copies are stale from here on
     if (n < 0 || (n > 0 && !A)) return fail(ctx, CB_EINVAL, "cb_tensor_op: bad argument");
     if (op >= CB_OP_ADD && op <= CB_OP_DIV && n > 0 && !B) return fail(ctx, CB_EINVAL, "cb_tensor_op: null B");
     float* b = const_cast<float*>(B);
@@ -902,6 +903,7 @@ int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* 
                       const long long* sizes, const unsigned char* is_weight, float lr, float beta, float l2) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (ntensors < 0) return fail(ctx, CB_EINVAL, "cb_momentum_multi: negative tensor count");
+    ctx->filter_version += 1;  // the updated tensors may be convolution filters: cached packed copies are stale
     if (ntensors == 0) return CB_OK;
     if (!w || !g || !m || !sizes) return fail(ctx, CB_EINVAL, "cb_momentum_multi: null table");
     if (ntensors > 65535) return fail(ctx, CB_EUNSUPPORTED, "cb_momentum_multi: more than 65535 tensors");
@@ -959,7 +961,9 @@ int momentum_table_launch(cb_ctx* ctx, const void* dev_table, int ntensors, long
     if (gx > 64) gx = 64;
     momentum_multi_kernel<<<dim3(gx, ntensors), kThreads, 0, ctx->stream>>>(static_cast<const MomentumTensor*>(dev_table), lr,
                                                                            beta, l2);
-    return done(ctx, "momentum step");
+    int rc = done(ctx, "momentum step");
+    if (rc != CB_OK) return rc;
+    return filter_cache_repack_all(ctx);  // the filters just changed: one launch re-packs every cached copy
 }
 }  // namespace cb
 

@@ -265,6 +265,7 @@ int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_st
     if (!out || !ctx || batch < 1 || blocks_per_stage < 1 || image_hw < 4 || classes < 1) return CB_EINVAL;
     cbt_model* m = new cbt_model();
     m->ctx = ctx; m->batch = batch; m->classes = classes;
+    cb_conv_cache_filters(ctx, 1);  // packed filters live from one weight update to the next
     int x = new_tensor(m, batch, 3, image_hw, image_hw);
     m->input = x;
     x = add_bn_relu(m, add_conv(m, x, 16, 3, 1, 1));
@@ -293,6 +294,7 @@ int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int
     if (!out || !ctx || batch < 1 || growth < 1 || layers < 1 || image_hw < 8 || (image_hw & 3) || classes < 1) return CB_EINVAL;
     cbt_model* m = new cbt_model();
     m->ctx = ctx; m->batch = batch; m->classes = classes;
+    cb_conv_cache_filters(ctx, 1);
     int x = new_tensor(m, batch, 3, image_hw, image_hw);
     m->input = x;
     x = add_conv(m, x, 2 * growth, 3, 1, 1);
@@ -357,6 +359,14 @@ int cbt_bind(cbt_model* m, float* params, float* grads, float* momentum) {
                                       &m->mom_biggest);
     if (rc != CB_OK) m->err = cb_last_error(m->ctx);
     return rc;
+}
+
+// The caller wrote to the bound parameter buffer by a route of its own (initialisation, a checkpoint, a broadcast):
+// packed copies of the filters are re-made before the next forward pass.
+int cbt_params_changed(cbt_model* m) {
+    if (!m) return CB_EINVAL;
+    CBT_TRY(cb_filters_changed(m->ctx));
+    return CB_OK;
 }
 
 // Forward pass on `images` (batch x 3 x H x W, device) with one-hot `labels` (batch x classes, device).

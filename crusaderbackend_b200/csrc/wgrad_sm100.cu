@@ -1,0 +1,385 @@
+// Tensor-core weight gradient of the convolution for sm_100a (TF32 mode), NCHW fp32.
+#include "conv_common.cuh"
+
+namespace cb {
+namespace {
+
+// ------------------------------------------------------------------------------------------ weight gradient
+// dW[oc][c][fh][fw] = sum over output pixels of dY[oc][pix] * X[c][pix shifted by (fh-pH, fw-pW)]: a contraction
+// over pixels, so both operands are K-major (32 pixels of one channel plane = one 128-byte row, standard 128-byte
+// swizzle). Per line of 32 output pixels a stage holds
+//   A: FH blocks [Cp channel rows][32 px] of X, fetched at the vertically shifted pixel offsets (UMMA M side,
+//      rows stacked as (fh, c); 128 rows per M tile), and
+//   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
+//      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
+//      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
+// Every CTA walks its share of the lines accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs),
+// writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
+struct WgradParams {
+    int N, Cin, H, W, OC;
+    int FH, FW, pH, pW;
+    int Cp, OCp, NQ, mtiles, rowsA;  // rowsA = FH * Cp valid accumulator rows
+    int L, LPI;
+    long long total_lines;
+    int stages, tmem_cols;
+    uint32_t stage_bytes, a_bytes;
+    float* partial;                  // [gridDim.x][mtiles * 128][NQ]
+    int* status;
+    long long* trace;
+};
+
+struct __align__(8) WgradSmem {
+    uint64_t full[kConvMaxStages];
+    uint64_t empty[kConvMaxStages];
+    uint64_t xf[kConvMaxStages];
+    uint64_t tfull;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// 16-byte chunk q of the 128-byte row at row_addr under the standard 128-byte swizzle (chunk ^= row index mod 8)
+__device__ __forceinline__ uint32_t sw128_chunk(uint32_t row_addr, int q) {
+    return row_addr + ((((uint32_t)q) ^ ((row_addr >> 7) & 7u)) << 4);
+}
+
+constexpr int kShiftWarps = 8;  // one scheduler cannot hide the shared-memory latencies of a single warp
+
+// One 16-byte chunk (pixels 4q .. 4q+3) of the horizontally shifted copies of a dY row: row_m1 (tap offset -1: pairs
+// X[px] with dY[px + 1]) and row_p1 (tap offset +1: pairs X[px] with dY[px - 1]); zeros enter at the edges of the
+// W-wide image rows packed in the line; an address of 0 skips that copy.
+__device__ __forceinline__ void shift_dy_chunk(uint32_t src_row, uint32_t row_m1, uint32_t row_p1, int q, int W) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(sw128_chunk(src_row, q)));
+    float left = 0.f, right = 0.f;
+    if (q > 0) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(left) : "r"(sw128_chunk(src_row, q - 1) + 12u));
+    if (q < 7) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(right) : "r"(sw128_chunk(src_row, q + 1)));
+    const int x0 = 4 * q, wm = W - 1;
+    if (row_m1) {
+        const float a0 = ((x0 & wm) < wm) ? v.y : 0.f, a1 = (((x0 + 1) & wm) < wm) ? v.z : 0.f;
+        const float a2 = (((x0 + 2) & wm) < wm) ? v.w : 0.f, a3 = (((x0 + 3) & wm) < wm) ? right : 0.f;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_m1, q)), "f"(a0), "f"(a1), "f"(a2), "f"(a3) : "memory");
+    }
+    if (row_p1) {
+        const float b0 = ((x0 & wm) >= 1) ? left : 0.f, b1 = (((x0 + 1) & wm) >= 1) ? v.x : 0.f;
+        const float b2 = (((x0 + 2) & wm) >= 1) ? v.y : 0.f, b3 = (((x0 + 3) & wm) >= 1) ? v.z : 0.f;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sw128_chunk(row_p1, q)), "f"(b0), "f"(b1), "f"(b2), "f"(b3) : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
+    umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmdY,
+                      const WgradParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ WgradSmem ws;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &ws.abort_flag;
+    const uint32_t st_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t set_bytes = (uint32_t)p.OCp * kRowBytes;
+    const int centre = p.pW;  // (fw, oc) rows of the N side: the unshifted copy is the tap with fw - pW == 0
+
+    if (threadIdx.x == 0) {
+        CB_TRACE_WALL(p.trace, 0);
+        CB_TRACE_EVENT(p.trace, 1);
+        ws.abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&ws.full[s]), 1);
+            mbar_init(smem_u32(&ws.empty[s]), 1);
+            mbar_init(smem_u32(&ws.xf[s]), 32 * kShiftWarps);
+        }
+        mbar_init(smem_u32(&ws.tfull), 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmX);
+        tma_prefetch_desc(&tmdY);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&ws.tmem_base), (uint32_t)p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ws.tmem_base;
+    if (threadIdx.x == 0) CB_TRACE_EVENT(p.trace, 2);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+            ok = conv_warp_wait(smem_u32(&ws.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
+            if (!ok) break;
+            if (lane == 0) {
+                const uint32_t full = smem_u32(&ws.full[s]);
+                const uint32_t stg = st_base + s * p.stage_bytes;
+                const int gi = (int)g;  // total_lines < 2^29 (checked on the host)
+                const int n = gi / p.LPI;
+                const int h0 = (gi - n * p.LPI) * p.L;
+                mbar_expect_tx(full, p.a_bytes + set_bytes);
+                for (int fh = 0; fh < p.FH; ++fh)
+                    tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
+                tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
+            }
+            __syncwarp();
+            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 0u, 0u);
+        const uint64_t desc0 = umma_smem_desc(0, 16u, 1024u, UMMA_SW_128B);  // K-major 128-byte rows; address added per stage
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        bool first_line = true;
+        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+            ok = conv_warp_wait(smem_u32(&ws.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
+            if (!ok) break;
+            if (p.FW > 1) {
+                ok = conv_warp_wait(smem_u32(&ws.xf[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM);
+                if (!ok) break;
+            }
+            tc_fence_after();
+            if (lane == 0 && first_line) CB_TRACE_EVENT(p.trace, 5);
+            if (lane == 0) {
+                const uint32_t stg = st_base + s * p.stage_bytes;
+                const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
+                const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
+                const uint32_t first = first_line ? 0u : 1u;
+                for (int m = 0; m < p.mtiles; ++m) {
+                    const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
+                    const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
+                    umma_tf32(d, dA, dB0, idesc, first);
+                    umma_tf32(d, dA + 2, dB0 + 2, idesc, 1u);
+                    umma_tf32(d, dA + 4, dB0 + 4, idesc, 1u);
+                    umma_tf32(d, dA + 6, dB0 + 6, idesc, 1u);
+                }
+                tc_commit(smem_u32(&ws.empty[s]));
+                if (first_line) CB_TRACE_EVENT(p.trace, 6);
+                if (g + gridDim.x >= p.total_lines) {
+                    tc_commit(smem_u32(&ws.tfull));
+                    CB_TRACE_EVENT(p.trace, 7);
+                }
+            }
+            __syncwarp();
+            first_line = false;
+            if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue: partial sums to the workspace
+        const int quarter = warp & 3;
+        bool ok = mbar_wait(smem_u32(&ws.tfull), 0, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 8);
+        if (ok) {
+            tc_fence_after();
+            const int rows_tot = p.mtiles * 128;
+            for (int m = 0; m < p.mtiles; ++m) {
+                const int r = m * 128 + 32 * quarter + lane;
+                float* dst = p.partial + ((long long)blockIdx.x * rows_tot + r) * p.NQ;
+                const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
+                for (int c = 0; c < p.NQ; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_row + (uint32_t)c, v);
+                    tmem_ld_wait();
+                    if (r < p.rowsA) {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 4)
+                            *reinterpret_cast<float4*>(dst + c + e) =
+                                make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                            __uint_as_float(v[e + 3]));
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ shift warps: fw = 0 and fw = 2 copies of dY
+        if (p.FW > 1) {
+            const int t = threadIdx.x - 192;
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+                ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
+                if (!ok) break;
+                for (int item = t; item < p.OCp * 8; item += 32 * kShiftWarps) {
+                    const int row = item >> 3, q = item & 7;
+                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)row * kRowBytes;
+                    const uint32_t src = b0 + (uint32_t)centre * set_bytes;
+                    const uint32_t m1 = centre >= 1 ? src - set_bytes : 0u;             // tap fw = pW - 1
+                    const uint32_t p1 = centre + 1 < p.FW ? src + set_bytes : 0u;       // tap fw = pW + 1
+                    shift_dy_chunk(src, m1, p1, q, p.W);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ws.xf[s]));
+                if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+            }
+        }
+    }
+
+    if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 10);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+    if (threadIdx.x == 0) {
+        CB_TRACE_EVENT(p.trace, 11);
+        CB_TRACE_WALL(p.trace, 12);
+    }
+}
+
+// dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
+// s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+                                                           int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
+                                                           int OC, int OCp, int FH, int FW, int accumulate, int s2,
+                                                           int IC_src) {
+    // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
+    // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
+    __shared__ float red[8][33];
+    const long long total = (long long)rowsA * NQ;
+    const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
+    const int grp = threadIdx.y;
+    float s = 0.f;
+    if (i < total) {
+        const long long pstride = (long long)rows_tot * NQ;
+        const float* src = partial + i;  // (r, col) of the partial layout is exactly element i
+#pragma unroll 4
+        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * pstride);
+    }
+    red[grp][threadIdx.x] = s;
+    __syncthreads();
+    if (grp != 0 || i >= total) return;
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) sum += red[g][threadIdx.x];
+    const int col = (int)(i % NQ);
+    const int r = (int)(i / NQ);
+    const int fh = r / Cp, c = r - fh * Cp;
+    const int fw = col / OCp, oc = col - fw * OCp;
+    if (c >= Cin || oc >= OC) return;
+    float* dst;
+    if (!s2) {
+        dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+    } else {
+        const int phase = c / IC_src, cc = c - phase * IC_src;
+        const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
+        if (sh < 0 || sw < 0) return;
+        dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
+    }
+    *dst = accumulate ? *dst + sum : sum;
+}
+
+}  // namespace
+
+// dW (+)= contraction over the pixels of N x Cin x IH x IW planes `X` and N x OC x IH x IW planes `dY` with taps
+// (FH, FW, pH, pW) in the same-size convention of the forward kernel. s2 / IC_src: see wgrad_reduce_kernel.
+static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int Cin, int IH, int IW, int OC, int FH,
+                      int FW, int pH, int pW, int accumulate, int s2, int IC_src, long long dy_batch, long long x_batch) {
+    if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
+    if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
+    if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
+    const int L = 32 / IW;
+    if (IH % L) return CB_EUNSUPPORTED;
+    const int Cp = (Cin + 7) / 8 * 8;
+    const int OCp = (OC + 15) / 16 * 16;
+    const int NQ = FW * OCp;
+    const int rowsA = FH * Cp;
+    const int mtiles = (rowsA + 127) / 128;
+    if (NQ > 256 || Cp > 256 || OCp > 128 || mtiles * NQ > 512) return CB_EUNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(dY) & 15u)) return CB_EUNSUPPORTED;
+    int rows_stage = rowsA + NQ;
+    if (rows_stage < mtiles * 128) rows_stage = mtiles * 128;
+    const uint32_t stage_bytes = ((uint32_t)rows_stage * kRowBytes + 1023u) & ~1023u;
+    long long stages = ((long long)ctx->max_smem_optin - 2048) / stage_bytes;
+    if (stages < 2) return CB_EUNSUPPORTED;
+    if (stages > kConvMaxStages) stages = kConvMaxStages;
+
+    WgradParams p{};
+    p.N = N; p.Cin = Cin; p.H = IH; p.W = IW; p.OC = OC;
+    p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
+    p.Cp = Cp; p.OCp = OCp; p.NQ = NQ; p.mtiles = mtiles; p.rowsA = rowsA;
+    p.L = L; p.LPI = IH / L;
+    p.total_lines = (long long)N * p.LPI;
+    if (p.total_lines > (1LL << 29)) return CB_EUNSUPPORTED;
+    p.stages = (int)stages;
+    int cols = 32;
+    while (cols < mtiles * NQ) cols <<= 1;
+    p.tmem_cols = cols;
+    p.stage_bytes = stage_bytes;
+    p.a_bytes = (uint32_t)rowsA * kRowBytes;
+    p.status = ctx->d_status;
+    p.trace = ctx->trace;
+    const int grid = (int)(p.total_lines < ctx->sm_count ? p.total_lines : ctx->sm_count);
+    const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
+    int rc = ensure_workspace(ctx, part_bytes);
+    if (rc != CB_OK) return rc;
+    p.partial = static_cast<float*>(ctx->workspace);
+
+    CUtensorMap tmX, tmdY;
+    {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(x_batch ? x_batch : (long long)Cin * IH * IW) * 4};
+        if (str[1] & 15u) return CB_EUNSUPPORTED;
+        uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
+        rc = encode_tmap(ctx, &tmX, X, 3, dims, str, box, nullptr, 128);
+        if (rc != CB_OK) return rc;
+    }
+    {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(dy_batch ? dy_batch : (long long)OC * IH * IW) * 4};
+        if (str[1] & 15u) return CB_EUNSUPPORTED;
+        uint32_t box[3] = {32u, (uint32_t)OCp, 1u};
+        rc = encode_tmap(ctx, &tmdY, dY, 3, dims, str, box, nullptr, 128);
+        if (rc != CB_OK) return rc;
+    }
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
+    umma_wgrad_kernel<<<grid, 192 + 32 * kShiftWarps, smem, ctx->stream>>>(tmX, tmdY, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
+    const long long total = (long long)rowsA * NQ;
+    int rgrid = (int)((total + 31) / 32);
+    wgrad_reduce_kernel<<<rgrid, dim3(32, 8), 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
+                                                         accumulate ? 1 : 0, s2, IC_src);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
+    ctx->launches += 2;
+    ctx->last_kernel = "umma_tf32";
+    return CB_OK;
+}
+
+int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch) {
+    if (sH == 1 && sW == 1) {
+        if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
+        if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+        return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC, dy_batch, x_batch);
+    }
+    if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
+    if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;
+    if (dy_batch || x_batch) return CB_EUNSUPPORTED;  // the stride-2 path re-lays dense tensors out
+    const int H2 = IH / 2, W2 = IW / 2;
+    if (W2 != 8 && W2 != 16 && W2 != 32) return CB_EUNSUPPORTED;
+    const long long plane2 = (long long)H2 * W2;
+    if (FH == 1) {
+        const long long n_sub = (long long)N * IC * plane2;
+        int rc = ensure_workspace2(ctx, (size_t)n_sub * sizeof(float));
+        if (rc != CB_OK) return rc;
+        float* sub = static_cast<float*>(ctx->workspace2);
+        rc = launch_subsample2(ctx, X, sub, (long long)N * IC, IH, IW);
+        if (rc != CB_OK) return rc;
+        return wgrad_core(ctx, dY, sub, dW, N, IC, H2, W2, OC, 1, 1, 0, 0, accumulate, 0, IC, 0, 0);
+    }
+    if (4 * IC > 256) return CB_EUNSUPPORTED;
+    const long long n_el = (long long)N * 4 * IC * plane2;
+    int rc = ensure_workspace2(ctx, (size_t)n_el * sizeof(float));
+    if (rc != CB_OK) return rc;
+    float* Xs = static_cast<float*>(ctx->workspace2);
+    rc = launch_space_to_depth2(ctx, X, Xs, N, IC, IH, IW);
+    if (rc != CB_OK) return rc;
+    return wgrad_core(ctx, dY, Xs, dW, N, 4 * IC, H2, W2, OC, 2, 2, 1, 1, accumulate, 1, IC, 0, 0);
+}
+
+}  // namespace cb

@@ -32,6 +32,7 @@ TRAIN_SIGNATURES = {
     "cbt_copy_tensor": (_i, [C.c_void_p, _i, _i, _f, _ll]),
     "cbt_copy_loss": (_i, [C.c_void_p, _f]),
     "cbt_set_reference_bn_grad_order": (_i, [C.c_void_p, _i]),
+    "cbt_params_changed": (_i, [C.c_void_p]),
 }
 KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
 
@@ -109,6 +110,11 @@ class ResNetTrainer:
         self.params.copy_(torch.from_numpy(np.ascontiguousarray(host, dtype=np.float32)))
         self.grads.zero_()
         self.momentum.zero_()
+        self.params_changed()
+
+    def params_changed(self):
+        """Call after writing to self.params directly: the executor re-packs its cached convolution filters."""
+        self._check(self.lib.cbt_params_changed(self.h))
 
     def set_reference_bn_grad_order(self, on: bool):
         """Store BatchNorm's d(gamma) / d(beta) in each other's slot, as the reference's operand does

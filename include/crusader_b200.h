@@ -56,6 +56,11 @@ int cb_freeze_workspace(cb_ctx* ctx, int on);
 int cb_set_deterministic(cb_ctx* ctx, int on);
 /* Waits for the stream, then reads and clears the device status word. CB_OK or CB_ETIMEOUT/CB_ECUDA. */
 int cb_synchronize(cb_ctx* ctx);
+/* Exercises the bounded-wait path without faulting the GPU: launches a one-CTA kernel whose only act is to wait, for
+ * at most limit_ms (1..1000) milliseconds, on a barrier that nothing ever arrives at. The wait gives up, the kernel
+ * records its status and returns normally; the next cb_synchronize (or this call, in sync mode) reports CB_ETIMEOUT
+ * and clears the status, after which the context is usable as before. */
+int cb_selftest_wait_timeout(cb_ctx* ctx, int limit_ms);
 const char* cb_last_error(const cb_ctx* ctx);
 /* Number of kernels this context has launched since creation (for launch accounting). */
 long long cb_launch_count(const cb_ctx* ctx);
@@ -76,6 +81,13 @@ const char* cb_version(void);
 int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
             int ldb, float* C, int ldc, int batch, long long strideA, long long strideB, long long strideC,
             int accumulate);
+
+/* Measured ceiling of the TF32 tensor pipe on this GPU: runs, on every SM, a loop that only issues
+ * tcgen05.mma.kind::tf32 (M = 128, N = n, K = 8) on operands resident in shared memory — no global traffic, no
+ * epilogue — `iters` groups of four per SM, timed with CUDA events, and returns the rate in TFLOP/s. p_mn / q_mn select
+ * the operand layouts (0 = K-major, 1 = MN-major), which the rate depends on. Used as the roofline denominator of the
+ * GEMM and convolution kernels. Synchronous. */
+int cb_measure_umma_peak(cb_ctx* ctx, int n, int p_mn, int q_mn, int iters, float* tflops);
 
 /* Name of the kernel family the last cb_gemm / cb_conv_* call dispatched to ("umma_tf32",
  * "umma_3xtf32", "simt_fp32"); for tests and launch accounting. */
@@ -99,6 +111,54 @@ int cb_conv_dgrad(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N
  * ih = oh*sH - pH + fh for every stride. Replaces seblas::convError (seblas/operations/cuConv.cu:793). */
 int cb_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
                   int FH, int FW, int sH, int sW, int pH, int pW, int accumulate);
+/*
+ * Extended forms. cb_conv_fwd_ex applies, while the accumulator is written out and in this order:
+ *   y = conv(W, X);  y = y * scale + shift (if scale != NULL);  y += bias[oc] (if bias);  y += Y (if accumulate);
+ *   y = max(y, 0) (if relu).
+ * scale / shift hold OC values, or OC*OH*OW values (one per output position, the shape of the reference's BatchNorm
+ * parameters, seann/operands/seblas/BatchNorm.cuh:27-33) when per_position != 0: a BatchNorm whose statistics are
+ * already known folds into the convolution this way. x_batch_stride / y_batch_stride are the element distances between
+ * consecutive images of X and Y (0 = densely packed): a convolution can read a channel prefix of, or write a channel
+ * slice of, a wider N x C_total x H x W buffer without a copy, which is how a DenseNet block's channel concatenation
+ * (seblas::concat, seblas/operations/cuConcat.cu:33-49) is avoided. The reference has no counterpart of these forms;
+ * with ep == NULL cb_conv_fwd_ex is cb_conv_fwd without bias and ReLU.
+ * cb_conv_dgrad_ex / cb_conv_wgrad_ex: `accumulate` adds the result onto dX / dW — the dA += dAReserve hand-over every
+ * operand's xGrads begins with (seann/operands/seblas/Conv2D.cu:19-21) folded into the kernel — and the strides as above.
+ */
+typedef struct cb_epilogue {
+    const float* bias;
+    const float* scale;
+    const float* shift;
+    int per_position;
+    int relu;
+    int accumulate;
+    long long x_batch_stride;
+    long long y_batch_stride;
+} cb_epilogue;
+int cb_conv_fwd_ex(cb_ctx* ctx, const float* W, const float* X, float* Y, int N, int IC, int IH, int IW, int OC, int FH,
+                   int FW, int sH, int sW, int pH, int pW, const cb_epilogue* ep);
+int cb_conv_dgrad_ex(cb_ctx* ctx, const float* W, const float* dY, float* dX, int N, int IC, int IH, int IW, int OC,
+                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch_stride,
+                     long long dx_batch_stride);
+int cb_conv_wgrad_ex(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
+                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch_stride,
+                     long long x_batch_stride);
+
+/*
+ * Packed-filter cache. The tensor-core forward and data-gradient kernels read the filter in a packed, padded layout
+ * that a small kernel produces from W before every call. With the cache on, the context keeps the packed copy of every
+ * (filter pointer, geometry, pass) it has seen and reuses it until the filter's values change:
+ *   - cb_momentum, cb_momentum_multi and cb_tensor_op on the same context mark every cached copy stale (each is
+ *     re-packed by the next convolution that uses it);
+ *   - after writing to a filter by any other route the caller must call cb_filters_changed, which re-packs every cached
+ *     filter in ONE launch on the context's stream (a training step then pays one pack launch instead of two per
+ *     convolution).
+ * Packed copies are device allocations made at a filter's first use (do that before capturing a CUDA graph) and
+ * released by cb_destroy. Default: off — every call packs its filter into the context workspace.
+ */
+int cb_conv_cache_filters(cb_ctx* ctx, int on);
+int cb_filters_changed(cb_ctx* ctx);
+
 /* Y[n,c,:,:] += bias[c]. Replaces seblas::convBias (seblas/operations/cuConv.cu:808). */
 int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW);
 /* db[c] (+)= sum over (n,h,w) of dY: the bias gradient cuConv2D takes from cuDNN
@@ -205,13 +265,18 @@ int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* 
  *  - The first call on a device resolves the device address of the static array (cudaGetSymbolAddress) and reads
  *    the device attributes; make that first call before any stream capture begins.
  *  - Every call on a device shares the one array (it keeps the previous call's contents; each call rewrites the
- *    part it uses and clears the status word in stream order). Calls that overlap on the GPU — different streams,
- *    or different host threads — race on it: issue them on one stream.
+ *    part it uses). Calls that overlap on the GPU — different streams, or different host threads — race on it: issue
+ *    them on one stream. Several host threads may make their first call at the same time.
+ *  - The caller's current device is unchanged on return (the call makes `device` current only while it runs).
  *  - `err` (nullable) receives a message of at most err_len bytes when the return value is not CB_OK.
+ *  - The call is asynchronous and returns CB_OK once the work is queued. Whether a bounded device-side wait expired
+ *    while it ran is reported by cb_conv_fwd_noalloc_status, which waits for `cuda_stream`, reads the static status
+ *    word (no allocation either) and returns CB_OK, or CB_ETIMEOUT with the reason in `err` after clearing the word.
  */
 int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W, const float* X, float* Y, const float* bias,
                         int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW,
                         int relu, char* err, int err_len);
+int cb_conv_fwd_noalloc_status(int device, void* cuda_stream, char* err, int err_len);
 
 #ifdef __cplusplus
 }

@@ -39,6 +39,11 @@ int cbt_op_count(const cbt_model* m);
 /* Binds the flat device buffers (cbt_param_count floats each, 16-byte aligned; gradients start at zero). */
 int cbt_bind(cbt_model* m, float* params, float* grads, float* momentum);
 
+/* Must be called after the caller wrote to the bound parameter buffer by any route other than cbt_update (initial
+ * values, a checkpoint, a broadcast between replicas): the executor keeps packed copies of the convolution filters
+ * from one update to the next (cb_conv_cache_filters) and re-makes them here. */
+int cbt_params_changed(cbt_model* m);
+
 /* One training step in three asynchronous parts on the context's stream. */
 int cbt_forward(cbt_model* m, const float* images, const float* labels_onehot);
 int cbt_backward(cbt_model* m);
