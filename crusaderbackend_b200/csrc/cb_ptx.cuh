@@ -105,6 +105,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return mbar_wait_for(bar, parity, abort_flag, status, code, CB_WAIT_LIMIT_NS);
 }
 
+// Whole-warp wait for the roles that wait long and in numbers (epilogue warps waiting for a tile's accumulator, the
+// transform warps waiting for a stage): only lane 0 polls, and with max_sleep_ns != 0 it sleeps between polls (32 ns,
+// doubling up to max_sleep_ns), so that hundreds of waiting threads do not take issue slots from the one thread that
+// feeds the tensor core; the other lanes then read the completed phase themselves. Sleeping pays in the GEMM's long
+// main loops (+1..6 %); the convolution kernels' short ones lose to the wake-up latency and keep mbar_wait.
+// Same bound and abort behaviour as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane, volatile int* abort_flag,
+                                               int* status, int code, uint32_t max_sleep_ns) {
+    int ok = 1;
+    if (lane == 0 && !mbar_try_wait(bar, parity)) {
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t ns = 32;
+        for (;;) {
+            if (max_sleep_ns) {
+                __nanosleep(ns);
+                if (ns < max_sleep_ns) ns <<= 1;
+            }
+            if (mbar_try_wait(bar, parity)) break;
+            if (*abort_flag) { ok = 0; break; }
+            if (globaltimer_ns() - t0 > CB_WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                ok = 0;
+                break;
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok)
+        for (int i = 0; i < 1024 && !mbar_try_wait(bar, parity); ++i) {}
+    return ok != 0;
+}
+
 // After an abort: gives work that is still in flight a bounded chance to land before the CTA releases what it targets.
 // Waits (at most ~1 ms) for the given phase of `bar`; records CBK_TIMEOUT_DRAIN when it does not complete.
 __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, int* status) {

@@ -279,8 +279,8 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
                 const bool relu_now = p.relu && ch == nchunks - 1;
                 for (int m = 0; m < p.mi && ok; ++m, ++sub) {
                     const uint32_t a = sub & 1u;
-                    ok = mbar_wait(smem_u32(&ps.tfull[a]), (sub >> 1) & 1u, abort_flag, p.status, CBK_TIMEOUT_TMEM_FULL);
-                    ok = __all_sync(0xffffffffu, ok);
+                    ok = mbar_wait_warp(smem_u32(&ps.tfull[a]), (sub >> 1) & 1u, lane, abort_flag, p.status,
+                                        CBK_TIMEOUT_TMEM_FULL, 512);
                     if (!ok) break;
                     tc_fence_after();
                     const int i = it.i0 + 128 * m + 32 * quarter + lane;
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
                 const WorkItem it = decode_work(p, w);
                 for (int kb = it.kb0; kb < it.kb1; ++kb) {
-                    ok = mbar_wait(smem_u32(&ps.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
+                    ok = mbar_wait_warp(smem_u32(&ps.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL, 64);
                     if (!ok) break;
                     const uint32_t src = tiles_base + s * stage_bytes;
                     const uint32_t dst = src + hi_bytes;

@@ -1,4 +1,6 @@
 // Tensor-core weight gradient of the convolution for sm_100a (TF32 mode), NCHW fp32.
+#include <cstdlib>
+
 #include "conv_common.cuh"
 
 namespace cb {
@@ -13,17 +15,22 @@ namespace {
 //   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
 //      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
 //      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
-// Every CTA walks its share of the lines accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs),
-// writes its partial to the workspace, and a second kernel adds the partials in a fixed order (deterministic).
+// A pipeline stage carries `lps` such lines (1, 2 or 4: as many as leave at least three stages), so that the per-stage
+// hand-offs between the producer, the shift warps and the MMA issuer are paid once per 32*lps pixels. Every CTA walks
+// its share of the line groups accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs), writes its
+// partial to the workspace column by column (the 32 lanes of a warp hold 32 consecutive rows: full 128-byte lines), and a second
+// kernel adds the partials in a fixed order (deterministic).
 struct WgradParams {
     int N, Cin, H, W, OC;
     int FH, FW, pH, pW;
     int Cp, OCp, NQ, mtiles, rowsA;  // rowsA = FH * Cp valid accumulator rows
     int L, LPI;
     long long total_lines;
+    int lps;                         // lines per pipeline stage
+    int groups;                      // ceil(total_lines / lps)
     int stages, tmem_cols;
-    uint32_t stage_bytes, a_bytes;
-    float* partial;                  // [gridDim.x][mtiles * 128][NQ]
+    uint32_t line_bytes, stage_bytes, a_bytes;  // one line slot of a stage / lps of them / the A part of a line slot
+    float* partial;                  // [gridDim.x][NQ][mtiles * 128]
     int* status;
     long long* trace;
 };
@@ -107,19 +114,22 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
         // ------------------------------------------------------------ TMA producer
         uint32_t s = 0, ph = 0;
         bool ok = true;
-        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+        for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
             ok = conv_warp_wait(smem_u32(&ws.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
             if (!ok) break;
             if (lane == 0) {
                 const uint32_t full = smem_u32(&ws.full[s]);
-                const uint32_t stg = st_base + s * p.stage_bytes;
-                const int gi = (int)g;  // total_lines < 2^29 (checked on the host)
-                const int n = gi / p.LPI;
-                const int h0 = (gi - n * p.LPI) * p.L;
-                mbar_expect_tx(full, p.a_bytes + set_bytes);
-                for (int fh = 0; fh < p.FH; ++fh)
-                    tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
-                tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
+                mbar_expect_tx(full, (uint32_t)p.lps * (p.a_bytes + set_bytes));
+                for (int l = 0; l < p.lps; ++l) {
+                    const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
+                    // lines past the end use an image index >= N: their boxes are zero-filled and add nothing
+                    const int gi = g * p.lps + l;  // total_lines < 2^29 (checked on the host)
+                    const int n = gi / p.LPI;
+                    const int h0 = (gi - n * p.LPI) * p.L;
+                    for (int fh = 0; fh < p.FH; ++fh)
+                        tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
+                    tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
+                }
             }
             __syncwarp();
             if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
@@ -131,39 +141,65 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
         uint32_t s = 0, ph = 0;
         bool ok = true;
         bool first_line = true;
-        for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+#ifdef CB_TRACE
+        long long t_full = 0, t_xf = 0, t_issue = 0;
+#endif
+        for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
+#ifdef CB_TRACE
+            const long long c0 = clock64();
+#endif
             ok = conv_warp_wait(smem_u32(&ws.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
             if (!ok) break;
+#ifdef CB_TRACE
+            const long long c1 = clock64();
+#endif
             if (p.FW > 1) {
                 ok = conv_warp_wait(smem_u32(&ws.xf[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_XFORM);
                 if (!ok) break;
             }
             tc_fence_after();
+#ifdef CB_TRACE
+            const long long c2 = clock64();
+            t_full += c1 - c0;
+            t_xf += c2 - c1;
+#endif
             if (lane == 0 && first_line) CB_TRACE_EVENT(p.trace, 5);
             if (lane == 0) {
-                const uint32_t stg = st_base + s * p.stage_bytes;
-                const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
-                const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
-                const uint32_t first = first_line ? 0u : 1u;
-                for (int m = 0; m < p.mtiles; ++m) {
-                    const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
-                    const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
-                    umma_tf32(d, dA, dB0, idesc, first);
-                    umma_tf32(d, dA + 2, dB0 + 2, idesc, 1u);
-                    umma_tf32(d, dA + 4, dB0 + 4, idesc, 1u);
-                    umma_tf32(d, dA + 6, dB0 + 6, idesc, 1u);
+                for (int l = 0; l < p.lps; ++l) {
+                    const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
+                    const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
+                    const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
+                    const uint32_t first = (first_line && l == 0) ? 0u : 1u;
+                    for (int m = 0; m < p.mtiles; ++m) {
+                        const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
+                        const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
+                        umma_tf32(d, dA, dB0, idesc, first);
+                        umma_tf32(d, dA + 2, dB0 + 2, idesc, 1u);
+                        umma_tf32(d, dA + 4, dB0 + 4, idesc, 1u);
+                        umma_tf32(d, dA + 6, dB0 + 6, idesc, 1u);
+                    }
                 }
                 tc_commit(smem_u32(&ws.empty[s]));
                 if (first_line) CB_TRACE_EVENT(p.trace, 6);
-                if (g + gridDim.x >= p.total_lines) {
+                if (g + (int)gridDim.x >= p.groups) {
                     tc_commit(smem_u32(&ws.tfull));
                     CB_TRACE_EVENT(p.trace, 7);
                 }
             }
             __syncwarp();
+#ifdef CB_TRACE
+            t_issue += clock64() - c2;
+#endif
             first_line = false;
             if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
         }
+#ifdef CB_TRACE
+        if (lane == 0 && p.trace) {
+            p.trace[(long long)blockIdx.x * 16 + 13] = t_full;
+            p.trace[(long long)blockIdx.x * 16 + 14] = t_xf;
+            p.trace[(long long)blockIdx.x * 16 + 15] = t_issue;
+        }
+#endif
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue: partial sums to the workspace
         const int quarter = warp & 3;
@@ -175,7 +211,9 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             const int rows_tot = p.mtiles * 128;
             for (int m = 0; m < p.mtiles; ++m) {
                 const int r = m * 128 + 32 * quarter + lane;
-                float* dst = p.partial + ((long long)blockIdx.x * rows_tot + r) * p.NQ;
+                if (m * 128 + 32 * quarter >= p.rowsA) continue;  // warp-uniform: no valid row in this quarter
+                // partial[cta][col][row]: for one column the warp's 32 rows are 128 contiguous bytes
+                float* dst = p.partial + (long long)blockIdx.x * p.NQ * rows_tot + r;
                 const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
                 for (int c = 0; c < p.NQ; c += 16) {
                     uint32_t v[16];
@@ -183,10 +221,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                     tmem_ld_wait();
                     if (r < p.rowsA) {
 #pragma unroll
-                        for (int e = 0; e < 16; e += 4)
-                            *reinterpret_cast<float4*>(dst + c + e) =
-                                make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
-                                            __uint_as_float(v[e + 3]));
+                        for (int e = 0; e < 16; ++e) dst[(long long)(c + e) * rows_tot] = __uint_as_float(v[e]);
                     }
                 }
             }
@@ -197,12 +232,14 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             const int t = threadIdx.x - 192;
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (long long g = blockIdx.x; g < p.total_lines && ok; g += gridDim.x) {
+            const int per_line = p.OCp * 8;
+            for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
                 ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
                 if (!ok) break;
-                for (int item = t; item < p.OCp * 8; item += 32 * kShiftWarps) {
-                    const int row = item >> 3, q = item & 7;
-                    const uint32_t b0 = st_base + s * p.stage_bytes + p.a_bytes + (uint32_t)row * kRowBytes;
+                for (int item = t; item < p.lps * per_line; item += 32 * kShiftWarps) {
+                    const int l = item / per_line, rem = item - l * per_line;
+                    const int row = rem >> 3, q = rem & 7;
+                    const uint32_t b0 = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes + p.a_bytes + (uint32_t)row * kRowBytes;
                     const uint32_t src = b0 + (uint32_t)centre * set_bytes;
                     const uint32_t m1 = centre >= 1 ? src - set_bytes : 0u;             // tap fw = pW - 1
                     const uint32_t p1 = centre + 1 < p.FW ? src + set_bytes : 0u;       // tap fw = pW + 1
@@ -228,7 +265,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     }
 }
 
-// dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fh*Cp + c][fw*OCp + oc], summed in CTA order.
+// dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fw*OCp + oc][fh*Cp + c], summed in CTA order.
 // s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
@@ -237,24 +274,24 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
     // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
     // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
     __shared__ float red[8][33];
-    const long long total = (long long)rowsA * NQ;
+    const long long total = (long long)rows_tot * NQ;
     const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
     const int grp = threadIdx.y;
+    const int col = (int)(i / rows_tot);
+    const int r = (int)(i - (long long)col * rows_tot);
+    const bool live = i < total && r < rowsA;
     float s = 0.f;
-    if (i < total) {
-        const long long pstride = (long long)rows_tot * NQ;
-        const float* src = partial + i;  // (r, col) of the partial layout is exactly element i
+    if (live) {
+        const float* src = partial + i;  // element i of the [col][row] partial layout
 #pragma unroll 4
-        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * pstride);
+        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * total);
     }
     red[grp][threadIdx.x] = s;
     __syncthreads();
-    if (grp != 0 || i >= total) return;
+    if (grp != 0 || !live) return;
     float sum = 0.f;
 #pragma unroll
     for (int g = 0; g < 8; ++g) sum += red[g][threadIdx.x];
-    const int col = (int)(i % NQ);
-    const int r = (int)(i / NQ);
     const int fh = r / Cp, c = r - fh * Cp;
     const int fw = col / OCp, oc = col - fw * OCp;
     if (c >= Cin || oc >= OC) return;
@@ -268,6 +305,23 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
         dst = dW + (((long long)oc * IC_src + cc) * 3 + sh) * 3 + sw;
     }
     *dst = accumulate ? *dst + sum : sum;
+}
+
+// Development override of the lines per stage (1, 2 or 4); 0 = choose from the stage size.
+int forced_lps() {
+    static const int v = [] {
+        const char* e = std::getenv("CB_WGRAD_LPS");
+        return e ? std::atoi(e) : 0;
+    }();
+    return v;
+}
+// Development override of the fewest line groups a CTA takes; 0 = from the 256-pixel rule.
+int forced_min_groups() {
+    static const int v = [] {
+        const char* e = std::getenv("CB_WGRAD_MINGROUPS");
+        return e ? std::atoi(e) : 0;
+    }();
+    return v;
 }
 
 }  // namespace
@@ -290,9 +344,15 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(dY) & 15u)) return CB_EUNSUPPORTED;
     int rows_stage = rowsA + NQ;
     if (rows_stage < mtiles * 128) rows_stage = mtiles * 128;
-    const uint32_t stage_bytes = ((uint32_t)rows_stage * kRowBytes + 1023u) & ~1023u;
-    long long stages = ((long long)ctx->max_smem_optin - 2048) / stage_bytes;
-    if (stages < 2) return CB_EUNSUPPORTED;
+    const uint32_t line_bytes = ((uint32_t)rows_stage * kRowBytes + 1023u) & ~1023u;
+    const long long smem_cap = (long long)ctx->max_smem_optin - 2048;
+    if (smem_cap / line_bytes < 2) return CB_EUNSUPPORTED;
+    int lps = 1;
+    for (int cand = 4; cand >= 2; cand >>= 1)
+        if (smem_cap / ((long long)cand * line_bytes) >= 3) { lps = cand; break; }
+    if (forced_lps() && smem_cap / ((long long)forced_lps() * line_bytes) >= 2) lps = forced_lps();
+    const uint32_t stage_bytes = (uint32_t)lps * line_bytes;
+    long long stages = smem_cap / stage_bytes;
     if (stages > kConvMaxStages) stages = kConvMaxStages;
 
     WgradParams p{};
@@ -306,11 +366,19 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     int cols = 32;
     while (cols < mtiles * NQ) cols <<= 1;
     p.tmem_cols = cols;
+    p.line_bytes = line_bytes;
     p.stage_bytes = stage_bytes;
     p.a_bytes = (uint32_t)rowsA * kRowBytes;
+    p.lps = lps;
+    p.groups = (int)((p.total_lines + lps - 1) / lps);
     p.status = ctx->d_status;
     p.trace = ctx->trace;
-    const int grid = (int)(p.total_lines < ctx->sm_count ? p.total_lines : ctx->sm_count);
+    // One CTA per line group up to the SM count: fewer, longer CTAs (fewer partial sums to write and reduce) measured
+    // slower on every layer shape of the models.
+    int min_groups = forced_min_groups() ? forced_min_groups() : 1;
+    int grid = p.groups / min_groups;
+    if (grid < 1) grid = 1;
+    if (grid > ctx->sm_count) grid = ctx->sm_count;
     const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
     int rc = ensure_workspace(ctx, part_bytes);
     if (rc != CB_OK) return rc;
@@ -339,7 +407,7 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     umma_wgrad_kernel<<<grid, 192 + 32 * kShiftWarps, smem, ctx->stream>>>(tmX, tmdY, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
-    const long long total = (long long)rowsA * NQ;
+    const long long total = (long long)mtiles * 128 * NQ;
     int rgrid = (int)((total + 31) / 32);
     wgrad_reduce_kernel<<<rgrid, dim3(32, 8), 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
                                                          accumulate ? 1 : 0, s2, IC_src);
