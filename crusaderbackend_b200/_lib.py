@@ -57,6 +57,8 @@ SIGNATURES = {
     "cb_bn_paramgrad": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_bwd_fused": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_fwd_relu": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_fwd_add_relu": (_i, [_ctx, _f, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_bwd_fused_res": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _f, _i, _i, _ll]),
     "cb_add_relu": (_i, [_ctx, _f, _f, _f, _ll]),
     "cb_relu_grad2": (_i, [_ctx, _f, _f, _f, _f, _ll]),
     "cb_relu": (_i, [_ctx, _f, _f, _ll]),
@@ -71,6 +73,8 @@ SIGNATURES = {
     "cb_global_avgpool_back": (_i, [_ctx, _f, _f, _ll, _i]),
     "cb_softmax": (_i, [_ctx, _f, _f, _i, _i]),
     "cb_cross_entropy": (_i, [_ctx, _f, _f, _f, _f, _ll]),
+    "cb_head_fwd": (_i, [_ctx] + [_f] * 9 + [_i] * 4),
+    "cb_head_bwd": (_i, [_ctx] + [_f] * 8 + [_i] * 4),
     "cb_momentum": (_i, [_ctx, _f, _f, _f, _ll, _fl, _fl, _fl, _i]),
     "cb_conv_fwd_noalloc": (_i, [_i, C.c_void_p, _f, _f, _f, _f] + [_i] * 12 + [C.c_char_p, _i]),
     "cb_conv_fwd_noalloc_status": (_i, [_i, C.c_void_p, C.c_char_p, _i]),

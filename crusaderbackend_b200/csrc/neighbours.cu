@@ -218,7 +218,8 @@ template <int SPT>
 __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict__ X, const float* __restrict__ beta,
                                                          const float* __restrict__ gamma, float* __restrict__ mean,
                                                          float* __restrict__ var, float* __restrict__ Y,
-                                                         float* __restrict__ xhat, int N, long long P, int relu) {
+                                                         float* __restrict__ xhat, const float* __restrict__ res, int N,
+                                                         long long P, int relu) {
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
             const float4 h = make_float4((x[i].x - m.x) * inv.x, (x[i].y - m.y) * inv.y, (x[i].z - m.z) * inv.z,
                                          (x[i].w - m.w) * inv.w);
             float4 y = make_float4(h.x * ga.x + be.x, h.y * ga.y + be.y, h.z * ga.z + be.z, h.w * ga.w + be.w);
+            if (res) y = f4_add(y, *reinterpret_cast<const float4*>(res + (long long)n * P + p));  // shortcut add
             if (relu) y = make_float4(fmaxf(y.x, 0.f), fmaxf(y.y, 0.f), fmaxf(y.z, 0.f), fmaxf(y.w, 0.f));
             *reinterpret_cast<float4*>(Y + (long long)n * P + p) = y;
             if (xhat) *reinterpret_cast<float4*>(xhat + (long long)n * P + p) = h;
@@ -272,7 +274,8 @@ template <int SPT>
 __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
                                                          const float* __restrict__ X, float* __restrict__ dX,
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                                         const float* __restrict__ relu_out, int N, long long P) {
+                                                         const float* __restrict__ relu_out, float* __restrict__ dres,
+                                                         int dres_add, int N, long long P) {
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -289,6 +292,10 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
             const float4 r = *reinterpret_cast<const float4*>(relu_out + (long long)n * P + p);
             dy[i] = make_float4(r.x > 0.f ? dy[i].x : 0.f, r.y > 0.f ? dy[i].y : 0.f, r.z > 0.f ? dy[i].z : 0.f,
                                 r.w > 0.f ? dy[i].w : 0.f);
+        }
+        if (dres && on) {  // the shortcut that was added before that ReLU receives the same masked gradient
+            float4* d = reinterpret_cast<float4*>(dres + (long long)n * P + p);
+            *d = dres_add ? f4_add(*d, dy[i]) : dy[i];
         }
         s = f4_add(s, x[i]);
     }
@@ -376,14 +383,14 @@ inline int bn_spt(int N) {
 
 template <int SPT>
 void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
-                       float* xhat, int N, long long P, int relu) {
-    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P, relu);
+                       float* xhat, const float* res, int N, long long P, int relu) {
+    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, res, N, P, relu);
 }
 template <int SPT>
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                       float* dbeta, const float* relu_out, int N, long long P) {
-    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, relu_out, N,
-                                                                                            P);
+                       float* dbeta, const float* relu_out, float* dres, int dres_add, int N, long long P) {
+    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, relu_out,
+                                                                                            dres, dres_add, N, P);
 }
 #define BN_SPT_SWITCH(spt, CALL)            \
     switch (spt) {                          \
@@ -629,6 +636,91 @@ __global__ void slice_add_kernel(float* __restrict__ dst, const float* __restric
     }
 }
 
+// ------------------------------------------------------------------ classifier head in one kernel per direction
+// Forward, one CTA per sample: global average pooling over the H*W plane of every channel, the dense layer
+// logits = W pooled + b, the softmax y = exp(x - max) / (sum + 1e-10), the loss gradient y - label and the sample's
+// loss -sum(log(y + 1e-10) * label): what GlobalAvgPool, Linear, Softmax and the cross-entropy pair do in four launches.
+__global__ void __launch_bounds__(256) head_fwd_kernel(const float* __restrict__ X, const float* __restrict__ W,
+                                                       const float* __restrict__ b, const float* __restrict__ labels,
+                                                       float* __restrict__ pooled, float* __restrict__ logits,
+                                                       float* __restrict__ probs, float* __restrict__ dlogits,
+                                                       float* __restrict__ loss_n, int C, int HW, int M) {
+    extern __shared__ float sh[];  // pooled[C]
+    const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* Xn = X + (long long)n * C * HW;
+    for (int c = warp; c < C; c += 8) {
+        float s = 0.f;
+        for (int i = lane; i < HW; i += 32) s += Xn[(long long)c * HW + i];
+        s = warp_sum(s);
+        if (lane == 0) {
+            sh[c] = s / (float)HW;
+            pooled[(long long)n * C + c] = sh[c];
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float logit = -1e15f;
+    if (lane < M) {
+        float a = b ? b[lane] : 0.f;
+        for (int c = 0; c < C; ++c) a = fmaf(W[(long long)lane * C + c], sh[c], a);
+        logit = a;
+        logits[(long long)n * M + lane] = a;
+    }
+    const float mx = warp_max(logit);
+    const float e = lane < M ? expf(logit - mx) : 0.f;
+    const float sum = warp_sum(e);
+    const float y = e * (1.0f / (sum + 1e-10f));
+    float l = 0.f;
+    if (lane < M) {
+        const float lab = labels[(long long)n * M + lane];
+        probs[(long long)n * M + lane] = y;
+        dlogits[(long long)n * M + lane] = y - lab;
+        l = -logf(y + 1e-10f) * lab;
+    }
+    l = warp_sum(l);
+    if (lane == 0) loss_n[n] = l;
+}
+
+// Backward. CTA n < N: dX[n][c][:] = (sum_m W[m][c] dlogits[n][m]) / HW (dense-layer data gradient and the pooling
+// gradient). CTA N: dW[m][c] += sum_n dlogits[n][m] pooled[n][c], db[m] += sum_n dlogits[n][m], and the batch's summed
+// loss, every sum in sample order (deterministic).
+__global__ void __launch_bounds__(256) head_bwd_kernel(const float* __restrict__ dlogits, const float* __restrict__ pooled,
+                                                       const float* __restrict__ W, float* __restrict__ dX,
+                                                       float* __restrict__ dW, float* __restrict__ db,
+                                                       const float* __restrict__ loss_n, float* __restrict__ loss_sum, int N,
+                                                       int C, int HW, int M) {
+    extern __shared__ float sh[];  // dpooled[C]
+    const int n = blockIdx.x;
+    if (n < N) {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float a = 0.f;
+            for (int m = 0; m < M; ++m) a = fmaf(W[(long long)m * C + c], dlogits[(long long)n * M + m], a);
+            sh[c] = a / (float)HW;
+        }
+        __syncthreads();
+        float* out = dX + (long long)n * C * HW;
+        for (int i = threadIdx.x; i < C * HW; i += blockDim.x) out[i] = sh[i / HW];
+        return;
+    }
+    for (int i = threadIdx.x; i < M * C; i += blockDim.x) {
+        const int m = i / C, c = i - m * C;
+        float a = 0.f;
+        for (int k = 0; k < N; ++k) a = fmaf(dlogits[(long long)k * M + m], pooled[(long long)k * C + c], a);
+        dW[i] += a;
+    }
+    if (db)
+        for (int m = threadIdx.x; m < M; m += blockDim.x) {
+            float a = 0.f;
+            for (int k = 0; k < N; ++k) a += dlogits[(long long)k * M + m];
+            db[m] += a;
+        }
+    if (threadIdx.x == 0 && loss_sum) {
+        float a = 0.f;
+        for (int k = 0; k < N; ++k) a += loss_n[k];
+        *loss_sum = a;
+    }
+}
+
 int done(cb_ctx* ctx, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, what);
@@ -652,7 +744,7 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(Y) && (!xhat || aligned16(xhat));
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(beta) && aligned16(gamma) && (!mean || aligned16(mean)) && (!var || aligned16(var))) {
-#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, N, P, 0)
+#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, nullptr, N, P, 0)
         BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
         return done(ctx, "cb_bn_fwd");
@@ -670,7 +762,7 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(gamma)) {
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, nullptr, 0, N, P)
         BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
         return done(ctx, "cb_bn_bwd");
@@ -695,34 +787,52 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
     return done(ctx, "cb_bn_paramgrad");
 }
 
-int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                    float* dbeta, const float* relu_out, int N, long long P) {
+static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                             float* dbeta, const float* relu_out, float* dres, int dres_add, int N, long long P) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!dY || !gamma || !X || !dX || !dgamma || !dbeta) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: null operand");
     const int spt = bn_spt(N);
     const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
-                    aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out));
+                    aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out)) && (!dres || aligned16(dres));
     if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, N, P)
     BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
     return done(ctx, "cb_bn_bwd_fused");
 }
+int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                    float* dbeta, const float* relu_out, int N, long long P) {
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, nullptr, 0, N, P);
+}
+int cb_bn_bwd_fused_res(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                        float* dbeta, const float* relu_out, float* dR, int accumulate_dR, int N, long long P) {
+    if (ctx && (!relu_out || !dR)) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused_res: null ReLU output or shortcut gradient");
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dR, accumulate_dR ? 1 : 0, N, P);
+}
 
-int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {
+static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
+                            long long P) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: negative extent");
     if (N == 0 || P == 0) return CB_OK;
     if (!X || !beta || !gamma || !Y) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: null operand");
     const int spt = bn_spt(N);
-    if (!((P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(Y) && aligned16(beta) && aligned16(gamma)))
+    if (!((P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(Y) && aligned16(beta) && aligned16(gamma) && (!R || aligned16(R))))
         return fail(ctx, CB_EUNSUPPORTED, "cb_bn_fwd_relu: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, N, P, 1)
+#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, R, N, P, 1)
     BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
     return done(ctx, "cb_bn_fwd_relu");
+}
+int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {
+    return bn_fwd_relu_impl(ctx, X, beta, gamma, nullptr, Y, N, P);
+}
+int cb_bn_fwd_add_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
+                       long long P) {
+    if (ctx && !R) return fail(ctx, CB_EINVAL, "cb_bn_fwd_add_relu: null addend");
+    return bn_fwd_relu_impl(ctx, X, beta, gamma, R, Y, N, P);
 }
 
 int cb_add_relu(cb_ctx* ctx, const float* A, const float* B, float* Out, long long n) {
@@ -835,6 +945,31 @@ int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY
     if (n == 0) return CB_OK;
     cross_entropy_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(Y, labels, dY, loss_sum, n);
     return done(ctx, "cb_cross_entropy");
+}
+
+int cb_head_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, const float* labels, float* pooled, float* logits,
+                float* probs, float* dlogits, float* loss_per_sample, int N, int C, int HW, int M) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (N < 0 || C < 1 || HW < 1 || M < 1) return fail(ctx, CB_EINVAL, "cb_head_fwd: bad extent");
+    if (M > 32 || C > 8192) return fail(ctx, CB_EUNSUPPORTED, "cb_head_fwd: at most 32 classes and 8192 channels");
+    if (N == 0) return CB_OK;
+    if (!X || !W || !labels || !pooled || !logits || !probs || !dlogits || !loss_per_sample)
+        return fail(ctx, CB_EINVAL, "cb_head_fwd: null operand");
+    head_fwd_kernel<<<N, 256, (size_t)C * sizeof(float), ctx->stream>>>(X, W, b, labels, pooled, logits, probs, dlogits,
+                                                                        loss_per_sample, C, HW, M);
+    return done(ctx, "cb_head_fwd");
+}
+
+int cb_head_bwd(cb_ctx* ctx, const float* dlogits, const float* pooled, const float* W, float* dX, float* dW, float* db,
+                const float* loss_per_sample, float* loss_sum, int N, int C, int HW, int M) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (N < 0 || C < 1 || HW < 1 || M < 1) return fail(ctx, CB_EINVAL, "cb_head_bwd: bad extent");
+    if (C > 8192) return fail(ctx, CB_EUNSUPPORTED, "cb_head_bwd: at most 8192 channels");
+    if (N == 0) return CB_OK;
+    if (!dlogits || !pooled || !W || !dX || !dW || (loss_sum && !loss_per_sample)) return fail(ctx, CB_EINVAL, "cb_head_bwd: null operand");
+    head_bwd_kernel<<<N + 1, 256, (size_t)C * sizeof(float), ctx->stream>>>(dlogits, pooled, W, dX, dW, db, loss_per_sample,
+                                                                            loss_sum, N, C, HW, M);
+    return done(ctx, "cb_head_bwd");
 }
 
 int cb_conv_bias(cb_ctx* ctx, float* Y, const float* bias, int N, int C, int HW) {

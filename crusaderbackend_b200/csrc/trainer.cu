@@ -20,7 +20,7 @@
 
 namespace {
 
-enum OpKind { OP_CONV, OP_BN, OP_RELU, OP_ADD, OP_GAP, OP_LINEAR, OP_SOFTMAX_CE, OP_CONCAT, OP_AVGPOOL };
+enum OpKind { OP_CONV, OP_BN, OP_RELU, OP_ADD, OP_GAP, OP_LINEAR, OP_SOFTMAX_CE, OP_CONCAT, OP_AVGPOOL, OP_HEAD };
 
 struct TensorBuf {
     int n = 0, c = 0, h = 0, w = 0;
@@ -37,7 +37,9 @@ struct Op {
     long long w_off = -1, b_off = -1;   // offsets into the flat parameter buffer (conv filter / BN gamma / FC weight; BN beta / FC bias)
     int xhat = -1;                      // BN: tensor id of x-hat
     bool in0_grad_accumulate = false;   // backward adds into in0's gradient instead of overwriting it
+    bool in1_grad_accumulate = false;   // likewise for the second input (shortcut of a fused BatchNorm-add-ReLU)
     bool relu = false;                  // BN / ADD: a ReLU is folded into this op (out is the activated tensor)
+    int pooled = -1, logits = -1, probs = -1;  // HEAD: tensors holding the pooled features, logits and softmax
 };
 
 struct ParamEntry {
@@ -63,6 +65,7 @@ struct cbt_model {
     long long scratch_elems = 0;
     float* labels = nullptr;       // device copy of the one-hot labels of the current step (caller-owned pointer)
     float* loss_dev = nullptr;     // device word: summed loss of the current step
+    float* loss_n = nullptr;       // per-sample losses of the current step (fused head)
     int input = -1, logits = -1, probs = -1;
     std::vector<void*> owned;      // device allocations released by cbt_destroy
     std::string err;
@@ -100,13 +103,15 @@ int add_conv(cbt_model* m, int in, int oc, int f, int stride, int pad) {
     return o.out;
 }
 
-int add_bn(cbt_model* m, int in) {
+// gamma_off / beta_off >= 0: parameters reserved earlier (the flat layout follows the reference's operand order, in
+// which a block's second BatchNorm precedes its shortcut convolution, while the fused op must run after it)
+int add_bn(cbt_model* m, int in, long long gamma_off = -1, long long beta_off = -1) {
     const TensorBuf x = m->t[in];
     Op o{};
     o.kind = OP_BN; o.in0 = in;
     const long long p = (long long)x.c * x.h * x.w;
-    o.w_off = add_param(m, p, 0, 1, 1, x.c, x.h, x.w);   // gamma, shape (1,C,H,W): BatchNorm.cuh:27-33
-    o.b_off = add_param(m, p, 0, 2, 1, x.c, x.h, x.w);   // beta
+    o.w_off = gamma_off >= 0 ? gamma_off : add_param(m, p, 0, 1, 1, x.c, x.h, x.w);   // gamma, shape (1,C,H,W): BatchNorm.cuh:27-33
+    o.b_off = beta_off >= 0 ? beta_off : add_param(m, p, 0, 2, 1, x.c, x.h, x.w);     // beta
     // x-hat is only stored when the fused backward (which recomputes it from X) cannot serve this shape
     const bool fused = x.n <= 256 && (p % 4) == 0;
     o.xhat = fused ? -1 : new_tensor(m, x.n, x.c, x.h, x.w);
@@ -123,6 +128,19 @@ int add_bn_relu(cbt_model* m, int in) {
     if (!(x.n <= 256 && (p % 4) == 0)) return add_relu(m, add_bn(m, in));
     const int out = add_bn(m, in);
     m->ops.back().relu = true;
+    return out;
+}
+
+// out = relu(BatchNorm(in) + shortcut): the end of a residual block as one op when the fused kernels cover the shape;
+// otherwise BatchNorm, add-ReLU as separate ops
+int add_add_relu(cbt_model* m, int a, int b);
+int add_bn_add_relu(cbt_model* m, int in, int shortcut, long long gamma_off, long long beta_off) {
+    const TensorBuf x = m->t[in];
+    const long long p = (long long)x.c * x.h * x.w;
+    if (!(x.n <= 256 && (p % 4) == 0)) return add_add_relu(m, add_bn(m, in, gamma_off, beta_off), shortcut);
+    const int out = add_bn(m, in, gamma_off, beta_off);
+    m->ops.back().relu = true;
+    m->ops.back().in1 = shortcut;
     return out;
 }
 
@@ -206,9 +224,23 @@ int dev_alloc(cbt_model* m, float** p, long long elems) {
 
 // Head (global average pooling, dense layer, softmax cross-entropy), gradient-accumulation flags and buffers.
 int finalize_model(cbt_model* m, int x, int classes) {
-    x = add_gap(m, x);
-    m->logits = add_linear(m, x, classes);
-    {
+    const TensorBuf xin = m->t[x];
+    if (classes <= 32 && xin.c <= 8192) {
+        // one op: cb_head_fwd / cb_head_bwd
+        Op o{};
+        o.kind = OP_HEAD; o.in0 = x; o.oc = classes;
+        o.w_off = add_param(m, (long long)classes * xin.c, 1, 3, classes, xin.c, 1, 1);
+        o.b_off = add_param(m, classes, 0, 4, classes, 1, 1, 1);
+        o.pooled = new_tensor(m, xin.n, xin.c, 1, 1);
+        o.logits = new_tensor(m, xin.n, classes, 1, 1);
+        o.probs = new_tensor(m, xin.n, classes, 1, 1);
+        o.out = o.probs;
+        m->logits = o.logits;
+        m->probs = o.probs;
+        m->ops.push_back(o);
+    } else {
+        x = add_gap(m, x);
+        m->logits = add_linear(m, x, classes);
         Op o{};
         o.kind = OP_SOFTMAX_CE; o.in0 = m->logits;
         o.out = new_tensor(m, m->batch, classes, 1, 1);
@@ -216,13 +248,8 @@ int finalize_model(cbt_model* m, int x, int classes) {
         m->ops.push_back(o);
     }
     m->param_count = (m->param_count + 3) & ~3LL;
-    // activations, gradients, and the accumulate flags of tensors with two consumers
-    std::vector<int> consumers(m->t.size(), 0);
-    for (Op& o : m->ops) {
-        if (o.in0 >= 0) consumers[o.in0]++;
-        if (o.in1 >= 0) consumers[o.in1]++;
-    }
-    // in backward order the LAST forward consumer writes first; every earlier consumer must accumulate
+    // in backward order the LAST forward consumer of a tensor writes its gradient first; every earlier consumer must
+    // accumulate onto it
     std::vector<int> seen(m->t.size(), 0);
     for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
         Op& o = m->ops[i];
@@ -230,19 +257,26 @@ int finalize_model(cbt_model* m, int x, int classes) {
             o.in0_grad_accumulate = seen[o.in0] > 0;
             seen[o.in0]++;
         }
-        if (o.in1 >= 0) seen[o.in1]++;  // OP_ADD writes its second input first (see backward)
+        if (o.in1 >= 0) {
+            o.in1_grad_accumulate = seen[o.in1] > 0;
+            seen[o.in1]++;
+        }
     }
     long long biggest = 0;
     for (size_t i = 0; i < m->t.size(); ++i) {
         TensorBuf& b = m->t[i];
-        int rc = dev_alloc(m, &b.a, b.size());
-        if (rc == CB_OK && (int)i != m->input) rc = dev_alloc(m, &b.d, b.size());
+        int rc = CB_OK;
+        if ((int)i != m->input) {  // the network input is read straight from the caller's batch buffer
+            rc = dev_alloc(m, &b.a, b.size());
+            if (rc == CB_OK) rc = dev_alloc(m, &b.d, b.size());
+        }
         if (rc != CB_OK) return rc;
         if (b.size() > biggest) biggest = b.size();
     }
     m->scratch_elems = biggest;
     int rc = dev_alloc(m, &m->scratch, biggest);
     if (rc == CB_OK) rc = dev_alloc(m, &m->loss_dev, 4);
+    if (rc == CB_OK) rc = dev_alloc(m, &m->loss_n, m->batch);
     return rc;
 }
 
@@ -275,10 +309,14 @@ int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_st
         for (int b = 0; b < blocks_per_stage; ++b) {
             const int stride = (stage > 0 && b == 0) ? 2 : 1;
             int y = add_bn_relu(m, add_conv(m, x, oc, 3, stride, 1));
-            y = add_bn(m, add_conv(m, y, oc, 3, 1, 1));
+            y = add_conv(m, y, oc, 3, 1, 1);
+            const TensorBuf ty = m->t[y];
+            const long long bn_p = (long long)ty.c * ty.h * ty.w;
+            const long long g_off = add_param(m, bn_p, 0, 1, 1, ty.c, ty.h, ty.w);
+            const long long b_off = add_param(m, bn_p, 0, 2, 1, ty.c, ty.h, ty.w);
             int sc = x;
             if (stride != 1 || ch != oc) sc = add_conv(m, x, oc, 1, stride, 0);  // bare 1x1 projection
-            x = add_add_relu(m, y, sc);
+            x = add_bn_add_relu(m, y, sc, g_off, b_off);
             ch = oc;
         }
     }
@@ -369,15 +407,15 @@ int cbt_params_changed(cbt_model* m) {
     return CB_OK;
 }
 
-// Forward pass on `images` (batch x 3 x H x W, device) with one-hot `labels` (batch x classes, device).
-// Leaves the softmax in the last tensor and the summed loss in the model's device loss word.
+// Forward pass on `images` (batch x 3 x H x W, device) with one-hot `labels` (batch x classes, device). The images are
+// read in place (no copy): they must stay unchanged until cbt_backward has run. Leaves the softmax in the last tensor
+// and the summed loss in the model's device loss word (after cbt_backward for models with the fused head).
 int cbt_forward(cbt_model* m, const float* images, const float* labels) {
-    if (!m || !m->P) return CB_EINVAL;
+    if (!m || !m->P || !images || !labels) return CB_EINVAL;
     cb_ctx* ctx = m->ctx;
-    TensorBuf& in = m->t[m->input];
-    cudaError_t e = cudaMemcpyAsync(in.a, images, (size_t)in.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
-    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    m->t[m->input].a = const_cast<float*>(images);
     m->labels = const_cast<float*>(labels);
+    cudaError_t e;
     for (const Op& o : m->ops) {
         const TensorBuf& x = m->t[o.in0];
         TensorBuf& y = m->t[o.out];
@@ -387,6 +425,11 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                                     o.stride, o.pad, o.pad, 0));
                 break;
             case OP_BN:
+                if (o.in1 >= 0) {
+                    CBT_TRY(cb_bn_fwd_add_relu(ctx, x.a, m->P + o.b_off, m->P + o.w_off, m->t[o.in1].a, y.a, x.n,
+                                               (long long)x.c * x.h * x.w));
+                    break;
+                }
                 if (o.relu) {
                     CBT_TRY(cb_bn_fwd_relu(ctx, x.a, m->P + o.b_off, m->P + o.w_off, y.a, x.n, (long long)x.c * x.h * x.w));
                     break;
@@ -408,13 +451,9 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
             }
             case OP_CONCAT: {
                 const TensorBuf& x1 = m->t[o.in1];
-                const size_t pl = (size_t)x.h * x.w * 4;
-                e = cudaMemcpy2DAsync(y.a, (size_t)y.c * pl, x.a, (size_t)x.c * pl, (size_t)x.c * pl, x.n,
-                                      cudaMemcpyDeviceToDevice, ctx->stream);
-                if (e == cudaSuccess)
-                    e = cudaMemcpy2DAsync(y.a + (size_t)x.c * x.h * x.w, (size_t)y.c * pl, x1.a, (size_t)x1.c * pl,
-                                          (size_t)x1.c * pl, x.n, cudaMemcpyDeviceToDevice, ctx->stream);
-                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                const float* src[2] = {x.a, x1.a};
+                const int ch[2] = {x.c, x1.c};
+                CBT_TRY(cb_concat_channels(ctx, 2, src, ch, y.a, x.n, x.h * x.w));
                 break;
             }
             case OP_AVGPOOL: CBT_TRY(cb_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h, x.w, 2, 2)); break;
@@ -425,6 +464,10 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
             case OP_SOFTMAX_CE:
                 CBT_TRY(cb_softmax(ctx, x.a, y.a, x.n, x.c));
                 CBT_TRY(cb_cross_entropy(ctx, y.a, labels, m->t[o.in0].d, m->loss_dev, y.size()));
+                break;
+            case OP_HEAD:
+                CBT_TRY(cb_head_fwd(ctx, x.a, m->P + o.w_off, m->P + o.b_off, labels, m->t[o.pooled].a, m->t[o.logits].a,
+                                    m->t[o.probs].a, m->t[o.logits].d, m->loss_n, x.n, x.c, x.h * x.w, o.oc));
                 break;
         }
     }
@@ -440,10 +483,17 @@ int cbt_backward(cbt_model* m) {
         const Op& o = m->ops[i];
         TensorBuf& x = m->t[o.in0];
         TensorBuf& y = m->t[o.out];
-        // where this op's data gradient goes: straight into x.d, or into scratch followed by x.d += scratch
-        float* dx = o.in0_grad_accumulate ? m->scratch : x.d;
+        const bool to_input = o.in0 == m->input;  // the network input needs no gradient
+        // Ops whose kernel can add onto an existing gradient write x.d directly; the others go through the scratch
+        // buffer followed by x.d += scratch when an earlier consumer already wrote x.d.
+        const bool native_acc = o.kind == OP_CONV || o.kind == OP_ADD;
+        float* dx = (o.in0_grad_accumulate && !native_acc) ? m->scratch : x.d;
         switch (o.kind) {
             case OP_SOFTMAX_CE: break;  // the forward already wrote softmax - labels into the logits' gradient
+            case OP_HEAD:
+                CBT_TRY(cb_head_bwd(ctx, m->t[o.logits].d, m->t[o.pooled].a, m->P + o.w_off, dx, m->G + o.w_off, m->G + o.b_off,
+                                    m->loss_n, m->loss_dev, x.n, x.c, x.h * x.w, o.oc));
+                break;
             case OP_LINEAR:
                 CBT_TRY(cb_linear_paramgrad(ctx, y.d, x.a, m->G + o.w_off, m->G + o.b_off, x.n, x.c * x.h * x.w, o.oc));
                 CBT_TRY(cb_linear_xgrad(ctx, y.d, m->P + o.w_off, dx, x.n, x.c * x.h * x.w, o.oc));
@@ -466,41 +516,49 @@ int cbt_backward(cbt_model* m) {
             case OP_ADD: {
                 // both inputs receive dY (ShortcutEndpoint::xGrads routes the same gradient to the skip path)
                 TensorBuf& x1 = m->t[o.in1];
-                if (o.relu && !o.in0_grad_accumulate) {
+                if (o.relu && !o.in0_grad_accumulate && !o.in1_grad_accumulate) {
                     CBT_TRY(cb_relu_grad2(ctx, y.a, y.d, x.d, x1.d, y.size()));
                     continue;
                 }
                 if (o.relu) CBT_TRY(cb_relu_grad2(ctx, y.a, y.d, y.d, nullptr, y.size()));  // mask in place, then route
-                cudaError_t e = cudaMemcpyAsync(x1.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
-                if (e == cudaSuccess && !o.in0_grad_accumulate)
-                    e = cudaMemcpyAsync(x.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
-                if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
-                if (o.in0_grad_accumulate) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, y.d, 0.f, x.size()));
+                for (int k = 0; k < 2; ++k) {
+                    TensorBuf& t = k ? x1 : x;
+                    const bool acc = k ? o.in1_grad_accumulate : o.in0_grad_accumulate;
+                    if (acc) {
+                        CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, t.d, y.d, 0.f, t.size()));
+                    } else {
+                        cudaError_t e = cudaMemcpyAsync(t.d, y.d, (size_t)y.size() * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+                        if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                    }
+                }
                 continue;
             }
             case OP_BN: {
                 // where d(gamma) and d(beta) are stored: their own slots, or each other's (reference order)
                 float* dgamma = m->G + (m->bn_grad_swap ? o.b_off : o.w_off);
                 float* dbeta = m->G + (m->bn_grad_swap ? o.w_off : o.b_off);
-                if (o.xhat < 0) {
-                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta,
-                                            o.relu ? y.a : nullptr, x.n, (long long)x.c * x.h * x.w));
+                const long long P = (long long)x.c * x.h * x.w;
+                if (o.in1 >= 0) {
+                    CBT_TRY(cb_bn_bwd_fused_res(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, y.a, m->t[o.in1].d,
+                                                o.in1_grad_accumulate ? 1 : 0, x.n, P));
+                } else if (o.xhat < 0) {
+                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, o.relu ? y.a : nullptr, x.n, P));
                 } else {
-                    CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, dgamma, dbeta, x.n,
-                                            (long long)x.c * x.h * x.w));
-                    CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, (long long)x.c * x.h * x.w));
+                    CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, dgamma, dbeta, x.n, P));
+                    CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, P));
                 }
                 break;
             }
             case OP_CONV:
                 CBT_TRY(cb_conv_wgrad(ctx, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
                                       o.stride, o.pad, o.pad, 1));
-                if (o.in0 != m->input)
-                    CBT_TRY(cb_conv_dgrad(ctx, m->P + o.w_off, y.d, dx, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
-                                          o.stride, o.pad, o.pad));
+                if (!to_input)
+                    CBT_TRY(cb_conv_dgrad_ex(ctx, m->P + o.w_off, y.d, x.d, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                             o.stride, o.pad, o.pad, o.in0_grad_accumulate ? 1 : 0, 0, 0));
                 break;
         }
-        if (o.in0_grad_accumulate && o.in0 != m->input) CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
+        if (o.in0_grad_accumulate && !native_acc && !to_input)
+            CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
     }
     return CB_OK;
 }
@@ -529,7 +587,14 @@ int cbt_loss(cbt_model* m, float* loss_mean) {
     if (!m || !loss_mean) return CB_EINVAL;
     float s = 0.f;
     cudaError_t e = cudaStreamSynchronize(m->ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpy(&s, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && !m->ops.empty() && m->ops.back().kind == OP_HEAD) {
+        // fused head: the forward pass leaves one loss per sample; they are summed here in sample order
+        std::vector<float> per((size_t)m->batch);
+        e = cudaMemcpy(per.data(), m->loss_n, sizeof(float) * per.size(), cudaMemcpyDeviceToHost);
+        for (float v : per) s += v;
+    } else if (e == cudaSuccess) {
+        e = cudaMemcpy(&s, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost);
+    }
     if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
     *loss_mean = s / (float)m->batch;
     return CB_OK;
@@ -544,7 +609,8 @@ float* cbt_tensor_ptr(cbt_model* m, int id, int grad) {
     return grad ? m->t[id].d : m->t[id].a;
 }
 float* cbt_loss_ptr(cbt_model* m) { return m ? m->loss_dev : nullptr; }
-// Copies the summed loss word of the last forward pass to a caller-owned device float, in stream order.
+// Copies the summed loss word of the last step (written by the backward pass for models with the fused head) to a
+// caller-owned device float, in stream order.
 int cbt_copy_loss(cbt_model* m, float* dst) {
     if (!m || !dst) return CB_EINVAL;
     cudaError_t e = cudaMemcpyAsync(dst, m->loss_dev, sizeof(float), cudaMemcpyDeviceToDevice, m->ctx->stream);

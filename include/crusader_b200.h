@@ -196,6 +196,15 @@ int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const floa
 /* Y = relu(batchNorm(X)) in one pass (the BatchNorm -> ReLU pair of the operand graph, seann/operands/seblas/BatchNorm.cu:14
  * followed by activate/ReLU.cu:8); same limits as cb_bn_bwd_fused. */
 int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P);
+/* Y = relu(batchNorm(X) + R): the BatchNorm that ends a residual block, the shortcut add
+ * (seann/operands/controlling/ShortcutEndpoint.cu:57-74) and the ReLU after it (archive/Resnet56:14-15) in one pass; and
+ * the matching backward pass: dY is masked by relu_out > 0, the masked gradient is written (or, with accumulate_dR,
+ * added) to the shortcut's gradient dR — what ShortcutEndpoint::xGrads routes to the skip path
+ * (ShortcutEndpoint.cu:76-99) — and goes on through the BatchNorm as in cb_bn_bwd_fused. Same limits as cb_bn_bwd_fused. */
+int cb_bn_fwd_add_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
+                       long long P);
+int cb_bn_bwd_fused_res(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                        float* dbeta, const float* relu_out, float* dR, int accumulate_dR, int N, long long P);
 
 /* seblas::relu / reluGradFast (seblas/operations/cuActivation.cu:268,296). */
 int cb_relu(cb_ctx* ctx, const float* X, float* Y, long long n);
@@ -235,6 +244,18 @@ int cb_global_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC
  * dY and loss_sum may be NULL. */
 int cb_softmax(cb_ctx* ctx, const float* X, float* Y, int rows, int step);
 int cb_cross_entropy(cb_ctx* ctx, const float* Y, const float* labels, float* dY, float* loss_sum, long long n);
+
+/* The classifier head of the models as one kernel per direction. Forward: global average pooling of X (N x C x HW)
+ * (seblas::globalAvgPool, seblas/operations/cuPool.cu:171-176), the dense layer logits = W pooled + b with W M x C
+ * (seblas::linear, cuLinear.cu:1052), the softmax (cuReduce.cu:296), the loss gradient dlogits = softmax - labels
+ * (cuLoss.cu:231) and each sample's loss -sum(log(y + 1e-10) * label) (cuLoss.cu:220) — four launches of the operand
+ * graph (GlobalAvgPool, Linear, Softmax, crossEntropyLoss / crossEntropyCalc). Backward: dX = pooling gradient of the
+ * dense layer's data gradient, dW += dlogits^T pooled, db += column sums (accumulated like every seblas parameter
+ * gradient; db nullable), and loss_sum (nullable) = sum of the per-sample losses. M <= 32 classes. */
+int cb_head_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, const float* labels, float* pooled, float* logits,
+                float* probs, float* dlogits, float* loss_per_sample, int N, int C, int HW, int M);
+int cb_head_bwd(cb_ctx* ctx, const float* dlogits, const float* pooled, const float* W, float* dX, float* dW, float* db,
+                const float* loss_per_sample, float* loss_sum, int N, int C, int HW, int M);
 
 /* Momentum step of seann (seann/optimizers/Optimizers.cu:17-22 over seblas::momentumApply,
  * seblas/operations/cuOptim.cu:38-46): w *= (1 - l2) if is_weight; m = beta m + (1 - beta) g; w -= lr m; g = 0.
