@@ -487,3 +487,50 @@ void orc_momentum_f32(float* w, float* g, float* m, i64 n, float lr, float beta,
         g[i] = 0.0f;
     }
 }
+
+/* ---- fp32 OpenMP BatchNorm (timed CPU baseline only; the checker uses the fp64 versions above) ------------------
+ * Same arithmetic as seblas::batchNorm / batchNormGrad / batchNormParamGrads (seblas/operations/cuBatchNorm.cu:14-147):
+ * statistics per position p over the batch, eps = 1e-8, the backward pass recomputes them from X. Optional tail of the
+ * forward pass: + res (shortcut add), then ReLU. */
+void orc_bn_fwd_f32(const float* X, const float* beta, const float* gamma, const float* res, float* Y, int N, long long P,
+                    int relu) {
+#pragma omp parallel for schedule(static)
+    for (long long p = 0; p < P; ++p) {
+        float m = 0.f, v = 0.f;
+        for (int n = 0; n < N; ++n) m += X[n * P + p];
+        m /= (float)N;
+        for (int n = 0; n < N; ++n) { const float d = X[n * P + p] - m; v += d * d; }
+        v /= (float)N;
+        const float inv = 1.0f / sqrtf(v + 1e-8f);
+        for (int n = 0; n < N; ++n) {
+            float y = (X[n * P + p] - m) * inv * gamma[p] + beta[p];
+            if (res) y += res[n * P + p];
+            if (relu && y < 0.f) y = 0.f;
+            Y[n * P + p] = y;
+        }
+    }
+}
+
+void orc_bn_bwd_f32(const float* dY, const float* gamma, const float* X, float* dX, float* dgamma, float* dbeta, int N,
+                    long long P) {
+    const float invN = 1.0f / (float)N;
+#pragma omp parallel for schedule(static)
+    for (long long p = 0; p < P; ++p) {
+        float m = 0.f, v = 0.f;
+        for (int n = 0; n < N; ++n) m += X[n * P + p];
+        m *= invN;
+        float sdx = 0.f, sd = 0.f, sxc = 0.f;
+        for (int n = 0; n < N; ++n) {
+            const float xc = X[n * P + p] - m, dy = dY[n * P + p];
+            v += xc * xc; sdx += dy * xc; sd += dy; sxc += xc;
+        }
+        const float inv = 1.0f / sqrtf(v * invN + 1e-8f);
+        const float g = gamma[p];
+        const float dvar = g * sdx * -0.5f * inv * inv * inv;
+        const float dmean = -g * sd * inv + dvar * (-2.0f * sxc) * invN;
+        for (int n = 0; n < N; ++n)
+            dX[n * P + p] = dY[n * P + p] * g * inv + dvar * (X[n * P + p] - m) * 2.0f * invN + dmean * invN;
+        dbeta[p] = sd;
+        dgamma[p] = sdx * inv;
+    }
+}

@@ -264,6 +264,29 @@ def bn_paramgrad(dY, xhat):
 
 
 # ------------------------------------------------------------------ activations, pooling, loss, optimizer
+def bn_fwd_f32(X, beta, gamma, res=None, relu=False) -> np.ndarray:
+    """fp32 OpenMP BatchNorm forward (+ shortcut add, + ReLU) for the timed CPU baseline."""
+    X = _f32(X)
+    N, P = X.shape[0], X.size // X.shape[0]
+    Y = np.empty_like(X)
+    f = lib().orc_bn_fwd_f32
+    f.argtypes = [_fp, _fp, _fp, C.c_void_p, _fp, _i, _ll, _i]
+    f(X, _f32(beta).ravel(), _f32(gamma).ravel(), _opt(res), Y, N, P, int(relu))
+    return Y
+
+
+def bn_bwd_f32(dY, gamma, X):
+    """fp32 OpenMP BatchNorm backward for the timed CPU baseline: (dX, dgamma, dbeta)."""
+    X, dY = _f32(X), _f32(dY)
+    N, P = X.shape[0], X.size // X.shape[0]
+    dX = np.empty_like(X)
+    dg, db = np.empty(P, dtype=np.float32), np.empty(P, dtype=np.float32)
+    f = lib().orc_bn_bwd_f32
+    f.argtypes = [_fp, _fp, _fp, _fp, _fp, _fp, _i, _ll]
+    f(dY, _f32(gamma).ravel(), X, dX, dg, db, N, P)
+    return dX, dg, db
+
+
 def relu(X) -> np.ndarray:
     X = _f32(X)
     Y = np.empty(X.shape)
