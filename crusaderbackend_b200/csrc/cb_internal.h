@@ -101,6 +101,12 @@ bool umma_gemm_eligible(const GemmCall& g);
 int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3);
 int launch_simt_gemm(cb_ctx* ctx, const GemmCall& g);
 
+// BatchNorm on one group of samples of a batch (statistics per group; neighbours.cu).
+int bn_fwd_group(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int relu, int N,
+                 long long P);
+int bn_bwd_group(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma, float* dbeta,
+                 const float* relu_out, float* dR, int accumulate_dR, int add_param_grads, int N, long long P);
+
 // Momentum descriptor table resident on the device (see neighbours.cu).
 int momentum_table_build(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
                          const long long* sizes, const unsigned char* is_weight, void** dev_table, long long* biggest);

@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
                                                          const float* __restrict__ X, float* __restrict__ dX,
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                          const float* __restrict__ relu_out, float* __restrict__ dres,
-                                                         int dres_add, int N, long long P) {
+                                                         int dres_add, int pg_add, int N, long long P) {
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -343,9 +343,14 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
         }
     }
     if (g == 0 && dgamma && dbeta) {
-        *reinterpret_cast<float4*>(dbeta + p) = sd;
-        *reinterpret_cast<float4*>(dgamma + p) =
-            make_float4(sdx.x * o_inv[0], sdx.y * o_inv[1], sdx.z * o_inv[2], sdx.w * o_inv[3]);  // sum dy * xhat
+        float4 gb = sd;
+        float4 gg = make_float4(sdx.x * o_inv[0], sdx.y * o_inv[1], sdx.z * o_inv[2], sdx.w * o_inv[3]);  // sum dy * xhat
+        if (pg_add) {  // a later group of a batch whose statistics are taken per group
+            gb = f4_add(gb, *reinterpret_cast<const float4*>(dbeta + p));
+            gg = f4_add(gg, *reinterpret_cast<const float4*>(dgamma + p));
+        }
+        *reinterpret_cast<float4*>(dbeta + p) = gb;
+        *reinterpret_cast<float4*>(dgamma + p) = gg;
     }
 }
 
@@ -388,9 +393,9 @@ void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const flo
 }
 template <int SPT>
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                       float* dbeta, const float* relu_out, float* dres, int dres_add, int N, long long P) {
+                       float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
     bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, relu_out,
-                                                                                            dres, dres_add, N, P);
+                                                                                            dres, dres_add, pg_add, N, P);
 }
 #define BN_SPT_SWITCH(spt, CALL)            \
     switch (spt) {                          \
@@ -762,7 +767,7 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(gamma)) {
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, nullptr, 0, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, nullptr, 0, 0, N, P)
         BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
         return done(ctx, "cb_bn_bwd");
@@ -788,7 +793,7 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
 }
 
 static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                             float* dbeta, const float* relu_out, float* dres, int dres_add, int N, long long P) {
+                             float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
     if (N == 0 || P == 0) return CB_OK;
@@ -797,20 +802,43 @@ static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, c
     const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
                     aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out)) && (!dres || aligned16(dres));
     if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, N, P)
+#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P)
     BN_SPT_SWITCH(spt, CB_CALL)
 #undef CB_CALL
     return done(ctx, "cb_bn_bwd_fused");
 }
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                     float* dbeta, const float* relu_out, int N, long long P) {
-    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, nullptr, 0, N, P);
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, nullptr, 0, 0, N, P);
 }
 int cb_bn_bwd_fused_res(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                         float* dbeta, const float* relu_out, float* dR, int accumulate_dR, int N, long long P) {
     if (ctx && (!relu_out || !dR)) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused_res: null ReLU output or shortcut gradient");
-    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dR, accumulate_dR ? 1 : 0, N, P);
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dR, accumulate_dR ? 1 : 0, 0, N, P);
 }
+}  // extern "C"
+
+extern "C" {
+static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
+                            long long P);
+}
+
+namespace cb {
+// One group of a batch whose BatchNorm statistics are taken per group of samples (the executor's model of per-GPU
+// statistics in data-parallel training): the group's slices of the tensors, parameter gradients added onto what the
+// earlier groups left when `add_param_grads`.
+int bn_bwd_group(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma, float* dbeta,
+                 const float* relu_out, float* dR, int accumulate_dR, int add_param_grads, int N, long long P) {
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dR, accumulate_dR, add_param_grads, N, P);
+}
+int bn_fwd_group(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int relu, int N,
+                 long long P) {
+    if (relu) return bn_fwd_relu_impl(ctx, X, beta, gamma, R, Y, N, P);
+    return cb_bn_fwd(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, N, P);
+}
+}  // namespace cb
+
+extern "C" {
 
 static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
                             long long P) {

@@ -12,7 +12,10 @@
 //     (seann/optimizers/Optimizers.cu:17-22, seblas/operations/cuOptim.cu:38-46).
 // Parameters, gradients and momentum live in three flat caller-owned device buffers (same layout), so a
 // data-parallel caller sum-allreduces ONE gradient buffer between cbt_backward and cbt_update.
+#include <dlfcn.h>
+
 #include <cstdio>
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -40,6 +43,47 @@ struct Op {
     bool in1_grad_accumulate = false;   // likewise for the second input (shortcut of a fused BatchNorm-add-ReLU)
     bool relu = false;                  // BN / ADD: a ReLU is folded into this op (out is the activated tensor)
     int pooled = -1, logits = -1, probs = -1;  // HEAD: tensors holding the pooled features, logits and softmax
+};
+
+// The few NCCL entry points the data-parallel step needs, resolved at run time (dlopen of libnccl.so.2) so that the
+// library carries no link-time dependency on NCCL; declarations follow nccl.h (ncclUniqueId is 128 opaque bytes passed
+// by value, ncclFloat32 = 7, ncclSum = 0, ncclSuccess = 0).
+struct NcclId { char internal[128]; };
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(NcclId*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+NcclApi* nccl_api(std::string* err) {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h) {
+            api.GetUniqueId = reinterpret_cast<int (*)(NcclId*)>(dlsym(h, "ncclGetUniqueId"));
+            api.CommInitRank = reinterpret_cast<int (*)(void**, int, NcclId, int)>(dlsym(h, "ncclCommInitRank"));
+            api.CommDestroy = reinterpret_cast<int (*)(void*)>(dlsym(h, "ncclCommDestroy"));
+            api.AllReduce = reinterpret_cast<int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t)>(dlsym(h, "ncclAllReduce"));
+            api.GetErrorString = reinterpret_cast<const char* (*)(int)>(dlsym(h, "ncclGetErrorString"));
+            if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce) api.lib = h;
+        }
+    }
+    if (!api.lib) {
+        if (err) *err = "NCCL is not available (libnccl.so.2 could not be loaded)";
+        return nullptr;
+    }
+    return &api;
+}
+
+constexpr int kMaxBuckets = 8;
+struct GradBucket {
+    long long offset = 0, count = 0;
+    int release_op = 0;  // the bucket's gradients are complete once backward has processed this op
 };
 
 struct ParamEntry {
@@ -71,6 +115,14 @@ struct cbt_model {
     std::string err;
     void* mom_table = nullptr;     // device descriptor table of the Momentum step, built by cbt_bind
     int bn_grad_swap = 0;          // 1: BatchNorm's two parameter gradients land in each other's slot, as in the reference
+    int bn_groups = 1;             // BatchNorm statistics are taken per group of batch / bn_groups consecutive samples
+    // data-parallel state (cbt_dp_init)
+    void* comm = nullptr;
+    int world = 1, rank = 0;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t bucket_ready[kMaxBuckets] = {};
+    cudaEvent_t reduce_done = nullptr;
+    std::vector<GradBucket> buckets;
     long long mom_biggest = 1;
 };
 
@@ -357,6 +409,14 @@ int cbt_destroy(cbt_model* m) {
     cudaStreamSynchronize(m->ctx->stream);
     for (void* p : m->owned) cudaFree(p);
     if (m->mom_table) cudaFree(m->mom_table);
+    if (m->comm) {
+        cudaStreamSynchronize(m->comm_stream);
+        if (NcclApi* api = nccl_api(nullptr)) api->CommDestroy(m->comm);
+        for (cudaEvent_t ev : m->bucket_ready)
+            if (ev) cudaEventDestroy(ev);
+        if (m->reduce_done) cudaEventDestroy(m->reduce_done);
+        cudaStreamDestroy(m->comm_stream);
+    }
     delete m;
     return CB_OK;
 }
@@ -425,6 +485,21 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                                     o.stride, o.pad, o.pad, 0));
                 break;
             case OP_BN:
+                if (m->bn_groups > 1) {
+                    // statistics per group of consecutive samples: what each GPU of a data-parallel run computes on its shard
+                    const long long P = (long long)x.c * x.h * x.w;
+                    const int ng = x.n / m->bn_groups;
+                    if (o.xhat >= 0 || x.n % m->bn_groups) {
+                        m->err = "BatchNorm groups need the fused kernels (N <= 256, C*H*W % 4 == 0) and a batch divisible by the group count";
+                        return CB_EUNSUPPORTED;
+                    }
+                    for (int g = 0; g < m->bn_groups; ++g) {
+                        const long long off = (long long)g * ng * P;
+                        CBT_TRY(cb::bn_fwd_group(ctx, x.a + off, m->P + o.b_off, m->P + o.w_off,
+                                                 o.in1 >= 0 ? m->t[o.in1].a + off : nullptr, y.a + off, o.relu ? 1 : 0, ng, P));
+                    }
+                    break;
+                }
                 if (o.in1 >= 0) {
                     CBT_TRY(cb_bn_fwd_add_relu(ctx, x.a, m->P + o.b_off, m->P + o.w_off, m->t[o.in1].a, y.a, x.n,
                                                (long long)x.c * x.h * x.w));
@@ -469,6 +544,28 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                 CBT_TRY(cb_head_fwd(ctx, x.a, m->P + o.w_off, m->P + o.b_off, labels, m->t[o.pooled].a, m->t[o.logits].a,
                                     m->t[o.probs].a, m->t[o.logits].d, m->loss_n, x.n, x.c, x.h * x.w, o.oc));
                 break;
+        }
+    }
+    return CB_OK;
+}
+
+// Data-parallel gradient exchange: every bucket (a contiguous range of the flat gradient buffer) whose last parameter
+// gradient was produced by op `op_index` is sum-allreduced on the communication stream, which waits for the compute
+// stream at that point only — the rest of the backward pass overlaps the transfer.
+static int dp_release_buckets(cbt_model* m, int op_index) {
+    NcclApi* api = nccl_api(&m->err);
+    if (!api) return CB_EUNSUPPORTED;
+    for (size_t b = 0; b < m->buckets.size(); ++b) {
+        const GradBucket& bk = m->buckets[b];
+        if (bk.release_op != op_index || bk.count == 0) continue;
+        cudaError_t e = cudaEventRecord(m->bucket_ready[b], m->ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(m->comm_stream, m->bucket_ready[b], 0);
+        if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+        const int rc = api->AllReduce(m->G + bk.offset, m->G + bk.offset, (size_t)bk.count, 7 /* ncclFloat32 */, 0 /* ncclSum */,
+                                      m->comm, m->comm_stream);
+        if (rc != 0) {
+            m->err = std::string("ncclAllReduce: ") + (api->GetErrorString ? api->GetErrorString(rc) : "failed");
+            return CB_ECUDA;
         }
     }
     return CB_OK;
@@ -538,7 +635,15 @@ int cbt_backward(cbt_model* m) {
                 float* dgamma = m->G + (m->bn_grad_swap ? o.b_off : o.w_off);
                 float* dbeta = m->G + (m->bn_grad_swap ? o.w_off : o.b_off);
                 const long long P = (long long)x.c * x.h * x.w;
-                if (o.in1 >= 0) {
+                if (m->bn_groups > 1) {
+                    const int ng = x.n / m->bn_groups;
+                    for (int g = 0; g < m->bn_groups; ++g) {
+                        const long long off = (long long)g * ng * P;
+                        CBT_TRY(cb::bn_bwd_group(ctx, y.d + off, m->P + o.w_off, x.a + off, dx + off, dgamma, dbeta,
+                                                 o.relu ? y.a + off : nullptr, o.in1 >= 0 ? m->t[o.in1].d + off : nullptr,
+                                                 o.in1_grad_accumulate ? 1 : 0, g > 0 ? 1 : 0, ng, P));
+                    }
+                } else if (o.in1 >= 0) {
                     CBT_TRY(cb_bn_bwd_fused_res(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, y.a, m->t[o.in1].d,
                                                 o.in1_grad_accumulate ? 1 : 0, x.n, P));
                 } else if (o.xhat < 0) {
@@ -559,6 +664,16 @@ int cbt_backward(cbt_model* m) {
         }
         if (o.in0_grad_accumulate && !native_acc && !to_input)
             CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
+        if (m->comm) {
+            int rc = dp_release_buckets(m, i);
+            if (rc != CB_OK) return rc;
+        }
+    }
+    if (m->comm) {
+        // the gradients are summed over the ranks by the time anything later on the context's stream reads them
+        cudaError_t e = cudaEventRecord(m->reduce_done, m->comm_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, m->reduce_done, 0);
+        if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
     }
     return CB_OK;
 }
@@ -573,6 +688,77 @@ int cbt_set_reference_bn_grad_order(cbt_model* m, int on) {
     m->bn_grad_swap = on ? 1 : 0;
     return CB_OK;
 }
+
+// BatchNorm statistics per group of batch / groups consecutive samples (1 = the whole batch, the default). A run on
+// one GPU with G groups computes exactly what G data-parallel ranks compute on their shards of the same batch, which
+// is how the sharded step is validated against the oracle.
+int cbt_set_bn_groups(cbt_model* m, int groups) {
+    if (!m || groups < 1 || m->batch % groups) return CB_EINVAL;
+    m->bn_groups = groups;
+    return CB_OK;
+}
+
+// ---- data-parallel training: one process per GPU, each with its own model on its shard of the batch
+// Rank 0 creates the 128-byte rendezvous id and sends it to the other ranks by any host-side channel.
+int cbt_dp_unique_id(char* id128) {
+    if (!id128) return CB_EINVAL;
+    NcclApi* api = nccl_api(nullptr);
+    if (!api) return CB_EUNSUPPORTED;
+    NcclId id;
+    if (api->GetUniqueId(&id) != 0) return CB_ECUDA;
+    std::memcpy(id128, id.internal, 128);
+    return CB_OK;
+}
+
+// Joins the communicator (collective over all ranks) and splits the flat gradient buffer into `buckets` ranges of
+// roughly equal size (1..8). From then on cbt_backward sum-allreduces each range over the ranks on a communication
+// stream as soon as its last gradient has been produced, and the gradients are the sums over all ranks when
+// cbt_backward's work is done. Call before capturing the step in a CUDA graph.
+int cbt_dp_init(cbt_model* m, const char* id128, int world, int rank, int buckets) {
+    if (!m || !id128 || world < 1 || rank < 0 || rank >= world || buckets < 1 || buckets > kMaxBuckets) return CB_EINVAL;
+    if (m->comm) return CB_EINVAL;
+    NcclApi* api = nccl_api(&m->err);
+    if (!api) return CB_EUNSUPPORTED;
+    NcclId id;
+    std::memcpy(id.internal, id128, 128);
+    void* comm = nullptr;
+    const int rc = api->CommInitRank(&comm, world, id, rank);
+    if (rc != 0) {
+        m->err = std::string("ncclCommInitRank: ") + (api->GetErrorString ? api->GetErrorString(rc) : "failed");
+        return CB_ECUDA;
+    }
+    cudaError_t e = cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking);
+    for (int b = 0; b < buckets && e == cudaSuccess; ++b) e = cudaEventCreateWithFlags(&m->bucket_ready[b], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->reduce_done, cudaEventDisableTiming);
+    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+    m->comm = comm; m->world = world; m->rank = rank;
+    // bucket b covers parameter entries whose offsets fall in [lo_b, hi_b); it is released by the FIRST op (in forward
+    // order) owning one of them, the last of them to be reached by the backward pass
+    m->buckets.assign((size_t)buckets, GradBucket{});
+    const long long total = m->param_count;
+    for (int b = 0; b < buckets; ++b) {
+        long long lo = total * b / buckets, hi = total * (b + 1) / buckets;
+        lo &= ~3LL;
+        hi = b + 1 == buckets ? total : (hi & ~3LL);
+        m->buckets[b].offset = lo;
+        m->buckets[b].count = hi - lo;
+        m->buckets[b].release_op = (int)m->ops.size();
+    }
+    auto claim = [&](long long off, long long size, int op) {
+        for (GradBucket& bk : m->buckets)
+            if (off < bk.offset + bk.count && off + size > bk.offset && op < bk.release_op) bk.release_op = op;
+    };
+    for (int i = 0; i < (int)m->ops.size(); ++i) {
+        const Op& o = m->ops[i];
+        for (const ParamEntry& pe : m->params)
+            if (pe.offset == o.w_off || pe.offset == o.b_off) claim(pe.offset, pe.size, i);
+    }
+    for (GradBucket& bk : m->buckets)
+        if (bk.release_op >= (int)m->ops.size()) bk.release_op = 0;  // no parameters inside (padding only)
+    return CB_OK;
+}
+
+int cbt_dp_world(const cbt_model* m) { return m ? m->world : 0; }
 
 // One Momentum step over every parameter tensor (one launch). BN parameter gradients are assigned, not
 // accumulated, by cb_bn_paramgrad, exactly like the reference kernel (cuBatchNorm.cu:128-147).

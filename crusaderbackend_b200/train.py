@@ -1,7 +1,8 @@
 """Python face of the training-step executor (include/crusader_b200_train.h) for tests and bench.py.
 
-torch owns the flat parameter / gradient / momentum buffers and, under torchrun, performs the one collective of a
-data-parallel step: a sum-allreduce of the flat gradient buffer (NCCL) between backward and update."""
+torch owns the flat parameter / gradient / momentum buffers. Under torchrun the executor itself performs the
+collective of a data-parallel step (cbt_dp_init: bucketed NCCL sum-allreduce of the gradients on a communication
+stream, overlapped with the backward pass); torch.distributed only carries the 128-byte rendezvous id."""
 from __future__ import annotations
 
 import ctypes as C
@@ -33,6 +34,10 @@ TRAIN_SIGNATURES = {
     "cbt_copy_loss": (_i, [C.c_void_p, _f]),
     "cbt_set_reference_bn_grad_order": (_i, [C.c_void_p, _i]),
     "cbt_params_changed": (_i, [C.c_void_p]),
+    "cbt_set_bn_groups": (_i, [C.c_void_p, _i]),
+    "cbt_dp_unique_id": (_i, [C.c_char_p]),
+    "cbt_dp_init": (_i, [C.c_void_p, C.c_char_p, _i, _i, _i]),
+    "cbt_dp_world": (_i, [C.c_void_p]),
 }
 KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
 
@@ -69,6 +74,8 @@ class ResNetTrainer:
         self.grads = torch.zeros(self.n_params, device=dev)
         self.momentum = torch.zeros(self.n_params, device=dev)
         self._check(self.lib.cbt_bind(h, self.params.data_ptr(), self.grads.data_ptr(), self.momentum.data_ptr()))
+        if distributed:
+            self._dp_init()
         self.entries = []
         for i in range(self.lib.cbt_param_entries(h)):
             off, size, isw, kind = _ll(), _ll(), _i(), _i()
@@ -128,10 +135,25 @@ class ResNetTrainer:
     def backward(self):
         self._check(self.lib.cbt_backward(self.h))
 
+    def _dp_init(self, buckets: int = 3):
+        """Joins the executor's own NCCL communicator: rank 0's rendezvous id travels over torch.distributed."""
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(), dist.get_rank()
+        buf = C.create_string_buffer(128)
+        if rank == 0:
+            self._check(self.lib.cbt_dp_unique_id(buf))
+        t = torch.tensor(list(buf.raw), dtype=torch.uint8, device=self.params.device)
+        dist.broadcast(t, 0)
+        ident = bytes(t.cpu().tolist())
+        self._check(self.lib.cbt_dp_init(self.h, ident, world, rank, buckets))
+
+    def set_bn_groups(self, groups: int):
+        """BatchNorm statistics per group of batch/groups consecutive samples (what `groups` data-parallel ranks compute)."""
+        self._check(self.lib.cbt_set_bn_groups(self.h, groups))
+
     def allreduce_grads(self):
-        if self.distributed:
-            import torch.distributed as dist
-            dist.all_reduce(self.grads, op=dist.ReduceOp.SUM)
+        """Kept for callers of the three-call form: with a distributed trainer cbt_backward has already summed the
+        gradients over the ranks."""
 
     def update(self, lr: float, beta: float = 0.9, l2: float = 1e-4):
         self._check(self.lib.cbt_update(self.h, lr, beta, l2))
@@ -144,12 +166,16 @@ class ResNetTrainer:
 
     # ---- whole step as one CUDA graph (launch-bound otherwise: ~700 kernels per ResNet-56 step)
     def capture_step(self, images, labels_onehot, lr, beta=0.9, l2=1e-4, warmup=2, include_allreduce=True):
-        """Runs `warmup` eager steps (workspace growth, NCCL set-up), then records forward + backward
-        (+ gradient allreduce) + update into a torch.cuda.CUDAGraph that reads the given static input tensors.
-        Returns the graph; call .replay() after refreshing images / labels in place."""
+        """Runs `warmup` eager steps (workspace growth, packed filters, NCCL set-up), then records forward + backward
+        (with the gradient allreduce of a distributed trainer) + update into a torch.cuda.CUDAGraph that reads the
+        given static input tensors, and freezes the context's workspace (a later call on the same context that needed a
+        larger scratch block would otherwise free memory the graph still uses). Returns the graph; call .replay()
+        after refreshing images / labels in place."""
         for _ in range(warmup):
             self.step(images, labels_onehot, lr, beta, l2)
         torch.cuda.synchronize()
+        # the graph keeps the addresses of the context's scratch blocks: no reallocation from here on
+        self.ctx._check(self.ctx.lib.cb_freeze_workspace(self.ctx.h, 1))
         graph = torch.cuda.CUDAGraph()
         old = self.ctx._stream
         with torch.cuda.graph(graph):

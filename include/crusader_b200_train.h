@@ -49,6 +49,24 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels_onehot);
 int cbt_backward(cbt_model* m);
 int cbt_update(cbt_model* m, float lr, float beta, float l2);
 
+/* BatchNorm statistics per group of batch / groups consecutive samples instead of over the whole batch (default 1).
+ * On one GPU, G groups compute exactly what G data-parallel ranks compute on their shards of the same batch. */
+int cbt_set_bn_groups(cbt_model* m, int groups);
+
+/*
+ * Data-parallel training, one process per GPU (the batch sharded by rank, weights replicated; the reference trains on
+ * one GPU only, seann/containers/Sequential.cu:107-163). Rank 0 obtains a 128-byte rendezvous id with
+ * cbt_dp_unique_id and hands it to the other ranks over any host channel; every rank then calls cbt_dp_init
+ * (collective). From then on cbt_backward sum-allreduces the flat gradient buffer over the ranks with NCCL, in
+ * `buckets` contiguous ranges (1..8), each issued on a communication stream as soon as the backward pass has
+ * produced its last gradient, so the exchange overlaps the rest of the backward pass; everything queued on the
+ * context's stream after cbt_backward sees the summed gradients. Every rank then applies the same cbt_update, so the
+ * replicas stay bit-identical without a broadcast. NCCL is loaded at run time (libnccl.so.2); CB_EUNSUPPORTED without it.
+ */
+int cbt_dp_unique_id(char* id128);
+int cbt_dp_init(cbt_model* m, const char* id128, int world, int rank, int buckets);
+int cbt_dp_world(const cbt_model* m);
+
 /* on = 1: store BatchNorm's two parameter gradients in each other's slot, which is what the reference's operand does
  * (seann/operands/seblas/BatchNorm.cu:24 passes beta's and gamma's gradient tensors to seblas::batchNormParamGrads in
  * swapped order); for step-by-step comparisons with the reference's own operand graph. Default 0: the right slots. */
