@@ -78,6 +78,8 @@ SIGNATURES = {
     "cb_momentum": (_i, [_ctx, _f, _f, _f, _ll, _fl, _fl, _fl, _i]),
     "cb_conv_fwd_noalloc": (_i, [_i, C.c_void_p, _f, _f, _f, _f] + [_i] * 12 + [C.c_char_p, _i]),
     "cb_conv_fwd_noalloc_status": (_i, [_i, C.c_void_p, C.c_char_p, _i]),
+    "cb_crseq_inspect": (_i, [C.c_char_p, C.POINTER(C.c_uint), C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong), C.c_char_p, _i]),
+    "cb_crseq_read_params": (_i, [C.c_char_p, C.c_void_p, C.c_ulonglong, C.c_char_p, _i]),
     "cb_selftest_wait_timeout": (_i, [_ctx, _i]),
     "cb_momentum_multi": (_i, [_ctx, _i, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                C.POINTER(_ll), C.POINTER(C.c_ubyte), _fl, _fl, _fl]),

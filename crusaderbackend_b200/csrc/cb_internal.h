@@ -107,6 +107,21 @@ int bn_fwd_group(cb_ctx* ctx, const float* X, const float* beta, const float* ga
 int bn_bwd_group(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma, float* dbeta,
                  const float* relu_out, float* dR, int accumulate_dR, int add_param_grads, int N, long long P);
 
+// One operand of a parsed .crseq file (crseq.cu): its id, the words of its info record, and for convolutions the sizes
+// of its parameter blobs (filter, bias). Branch operands of a ShortcutEndpoint follow their endpoint with in_branch set.
+struct CrseqOperand {
+    uint32_t id = 0;
+    uint32_t info[9] = {};
+    uint64_t param_floats[2] = {};
+    int in_branch = 0;
+};
+struct CrseqModel {
+    uint32_t epoch = 0;
+    std::vector<CrseqOperand> operands;
+    size_t params_begin = 0, param_bytes = 0;
+};
+bool crseq_parse(const std::vector<uint8_t>& file, CrseqModel& out, std::string& err);
+
 // Momentum descriptor table resident on the device (see neighbours.cu).
 int momentum_table_build(cb_ctx* ctx, int ntensors, float* const* w, float* const* g, float* const* m,
                          const long long* sizes, const unsigned char* is_weight, void** dev_table, long long* biggest);

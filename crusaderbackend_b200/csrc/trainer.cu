@@ -124,6 +124,11 @@ struct cbt_model {
     cudaEvent_t reduce_done = nullptr;
     std::vector<GradBucket> buckets;
     long long mom_biggest = 1;
+    // .crseq image of the model (ResNets): top-level operand ids, the words of the info section (uuid words flagged: a
+    // file's own block numbering is accepted on load), and the parameter entries in the order the file stores them
+    std::vector<uint32_t> crseq_ids, crseq_info;
+    std::vector<uint8_t> crseq_info_is_uuid;
+    std::vector<int> crseq_params;
 };
 
 namespace {
@@ -354,26 +359,73 @@ int cbt_resnet_create(cbt_model** out, cb_ctx* ctx, int batch, int blocks_per_st
     cb_conv_cache_filters(ctx, 1);  // packed filters live from one weight update to the next
     int x = new_tensor(m, batch, 3, image_hw, image_hw);
     m->input = x;
-    x = add_bn_relu(m, add_conv(m, x, 16, 3, 1, 1));
+    // the same network as the reference's operand list (archive/Resnet56: cuConv2D, BatchNorm, ReLU, then per block
+    // ShortcutEndpoint begin, cuConv2D, BatchNorm, ReLU, cuConv2D, BatchNorm, ShortcutEndpoint end [1x1 cuConv2D], ReLU;
+    // GlobalAvgPool, Linear, Softmax), recorded for the .crseq reader / writer as the model is built
+    auto info_word = [&](uint32_t v, bool is_uuid = false) {
+        m->crseq_info.push_back(v);
+        m->crseq_info_is_uuid.push_back(is_uuid ? 1 : 0);
+    };
+    auto conv_info = [&](int oc_, int ic_, int f_, int stride_, int pad_) {
+        for (uint32_t v : {(uint32_t)oc_, (uint32_t)ic_, (uint32_t)f_, (uint32_t)f_, (uint32_t)stride_, (uint32_t)stride_,
+                           (uint32_t)pad_, (uint32_t)pad_, 0u})
+            info_word(v);
+    };
+    auto last_entry = [&]() { return (int)m->params.size() - 1; };
+    auto bn_entries = [&]() {  // the file stores beta before gamma (BatchNorm.cu:50-55)
+        m->crseq_params.push_back(last_entry());
+        m->crseq_params.push_back(last_entry() - 1);
+    };
+    x = add_conv(m, x, 16, 3, 1, 1);
+    m->crseq_ids = {0xd002u, 0x0003u, 0xa002u};
+    conv_info(16, 3, 3, 1, 1);
+    m->crseq_params.push_back(last_entry());
+    x = add_bn_relu(m, x);
+    bn_entries();
     int ch = 16;
+    uint32_t uuid = 1;
     for (int stage = 0; stage < 3; ++stage) {
         const int oc = 16 << stage;
         for (int b = 0; b < blocks_per_stage; ++b) {
             const int stride = (stage > 0 && b == 0) ? 2 : 1;
-            int y = add_bn_relu(m, add_conv(m, x, oc, 3, stride, 1));
+            for (uint32_t id : {0xf002u, 0xd002u, 0x0003u, 0xa002u, 0xd002u, 0x0003u, 0xf003u, 0xa002u}) m->crseq_ids.push_back(id);
+            info_word(uuid, true);
+            info_word(0);
+            int y = add_conv(m, x, oc, 3, stride, 1);
+            conv_info(oc, ch, 3, stride, 1);
+            m->crseq_params.push_back(last_entry());
+            y = add_bn_relu(m, y);
+            bn_entries();
             y = add_conv(m, y, oc, 3, 1, 1);
+            conv_info(oc, oc, 3, 1, 1);
+            m->crseq_params.push_back(last_entry());
             const TensorBuf ty = m->t[y];
             const long long bn_p = (long long)ty.c * ty.h * ty.w;
             const long long g_off = add_param(m, bn_p, 0, 1, 1, ty.c, ty.h, ty.w);
             const long long b_off = add_param(m, bn_p, 0, 2, 1, ty.c, ty.h, ty.w);
+            bn_entries();
             int sc = x;
-            if (stride != 1 || ch != oc) sc = add_conv(m, x, oc, 1, stride, 0);  // bare 1x1 projection
+            const bool projection = stride != 1 || ch != oc;
+            info_word(uuid, true);
+            info_word(projection ? 1 : 0);
+            if (projection) {
+                sc = add_conv(m, x, oc, 1, stride, 0);  // bare 1x1 projection
+                info_word(0xd002u);
+                conv_info(oc, ch, 1, stride, 0);
+                m->crseq_params.push_back(last_entry());
+            }
             x = add_bn_add_relu(m, y, sc, g_off, b_off);
             ch = oc;
+            ++uuid;
         }
     }
     *out = m;
-    return finalize_model(m, x, classes);
+    const int rc = finalize_model(m, x, classes);
+    for (uint32_t id : {0xb002u, 0x0001u, 0x0005u}) m->crseq_ids.push_back(id);
+    info_word((uint32_t)classes);
+    m->crseq_params.push_back(last_entry() - 1);  // Linear: weights, then biases
+    m->crseq_params.push_back(last_entry());
+    return rc;
 }
 
 // DenseNet-BC (growth k, `layers` bottleneck layers per dense block, compression 0.5): stem 3x3 conv to 2k, three dense
@@ -465,6 +517,112 @@ int cbt_params_changed(cbt_model* m) {
     if (!m) return CB_EINVAL;
     CBT_TRY(cb_filters_changed(m->ctx));
     return CB_OK;
+}
+
+// Writes the bound parameters as a .crseq file the reference's loadSequence reads (seio/modelcache/codec.cu:8-39 is the
+// writer this mirrors; the file is replaced, where the reference appends to an existing one). ResNet models only.
+int cbt_save_crseq(cbt_model* m, const char* path, unsigned epoch) {
+    if (!m || !path || !m->P) return CB_EINVAL;
+    if (m->crseq_ids.empty()) {
+        m->err = "no .crseq image is defined for this model family";
+        return CB_EUNSUPPORTED;
+    }
+    std::vector<float> host((size_t)m->param_count);
+    if (cudaStreamSynchronize(m->ctx->stream) != cudaSuccess ||
+        cudaMemcpy(host.data(), m->P, host.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        m->err = "reading the parameters back failed";
+        return CB_ECUDA;
+    }
+    FILE* f = std::fopen(path, "wb");
+    if (!f) {
+        m->err = std::string("cannot open ") + path + " for writing";
+        return CB_EINVAL;
+    }
+    const uint32_t head[3] = {0x7921aedfu, (uint32_t)m->crseq_ids.size(), (uint32_t)epoch};
+    bool ok = std::fwrite(head, 4, 3, f) == 3;
+    ok = ok && std::fwrite(m->crseq_ids.data(), 4, m->crseq_ids.size(), f) == m->crseq_ids.size();
+    ok = ok && std::fwrite(m->crseq_info.data(), 4, m->crseq_info.size(), f) == m->crseq_info.size();
+    for (int e : m->crseq_params) {
+        const ParamEntry& pe = m->params[(size_t)e];
+        ok = ok && std::fwrite(host.data() + pe.offset, 4, (size_t)pe.size, f) == (size_t)pe.size;
+    }
+    ok = (std::fclose(f) == 0) && ok;
+    if (!ok) {
+        m->err = std::string("writing ") + path + " failed";
+        return CB_EINVAL;
+    }
+    return CB_OK;
+}
+
+// Loads the parameters of a .crseq file written by the reference's saveSequence (or by cbt_save_crseq) into the bound
+// parameter buffer. The file's operand list and every geometry word must describe this model (block uuids are free);
+// anything else is refused with the first difference named. *epoch receives the file's epoch id.
+int cbt_load_crseq(cbt_model* m, const char* path, unsigned* epoch) {
+    if (!m || !path || !m->P) return CB_EINVAL;
+    if (m->crseq_ids.empty()) {
+        m->err = "no .crseq image is defined for this model family";
+        return CB_EUNSUPPORTED;
+    }
+    std::vector<uint8_t> bytes;
+    {
+        FILE* f = std::fopen(path, "rb");
+        if (!f) {
+            m->err = std::string("cannot open ") + path;
+            return CB_EINVAL;
+        }
+        std::fseek(f, 0, SEEK_END);
+        const long len = std::ftell(f);
+        std::fseek(f, 0, SEEK_SET);
+        bytes.resize(len > 0 ? (size_t)len : 0);
+        const bool ok = bytes.empty() || std::fread(bytes.data(), 1, bytes.size(), f) == bytes.size();
+        std::fclose(f);
+        if (!ok) {
+            m->err = std::string("reading ") + path + " failed";
+            return CB_EINVAL;
+        }
+    }
+    cb::CrseqModel parsed;
+    if (!cb::crseq_parse(bytes, parsed, m->err)) return CB_EINVAL;
+    const size_t n_ids = m->crseq_ids.size(), n_info = m->crseq_info.size();
+    const size_t info_begin = 12 + 4 * n_ids;
+    uint32_t file_count = 0;
+    std::memcpy(&file_count, bytes.data() + 4, 4);
+    if (file_count != n_ids || parsed.params_begin != info_begin + 4 * n_info) {
+        m->err = "the file describes another network (" + std::to_string(file_count) + " operands, model has " + std::to_string(n_ids) + ")";
+        return CB_EINVAL;
+    }
+    for (size_t i = 0; i < n_ids + n_info; ++i) {
+        uint32_t v = 0;
+        std::memcpy(&v, bytes.data() + 12 + 4 * i, 4);
+        const bool is_id = i < n_ids;
+        const uint32_t want = is_id ? m->crseq_ids[i] : m->crseq_info[i - n_ids];
+        if (!is_id && m->crseq_info_is_uuid[i - n_ids]) continue;
+        if (v != want) {
+            m->err = std::string("the file describes another network: ") + (is_id ? "operand id " : "info word ") +
+                     std::to_string(is_id ? i : i - n_ids) + " is " + std::to_string(v) + ", the model has " + std::to_string(want);
+            return CB_EINVAL;
+        }
+    }
+    size_t total = 0;
+    for (int e : m->crseq_params) total += (size_t)m->params[(size_t)e].size;
+    if (total * 4 != parsed.param_bytes) {
+        m->err = "the file holds " + std::to_string(parsed.param_bytes / 4) + " parameter floats, the model has " + std::to_string(total);
+        return CB_EINVAL;
+    }
+    std::vector<float> host((size_t)m->param_count, 0.f);
+    size_t pos = parsed.params_begin;
+    for (int e : m->crseq_params) {
+        const ParamEntry& pe = m->params[(size_t)e];
+        std::memcpy(host.data() + pe.offset, bytes.data() + pos, (size_t)pe.size * 4);
+        pos += (size_t)pe.size * 4;
+    }
+    if (cudaStreamSynchronize(m->ctx->stream) != cudaSuccess ||
+        cudaMemcpy(m->P, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+        m->err = "copying the parameters to the device failed";
+        return CB_ECUDA;
+    }
+    if (epoch) *epoch = parsed.epoch;
+    return cbt_params_changed(m);
 }
 
 // Forward pass on `images` (batch x 3 x H x W, device) with one-hot `labels` (batch x classes, device). The images are

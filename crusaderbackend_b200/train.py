@@ -38,8 +38,29 @@ TRAIN_SIGNATURES = {
     "cbt_dp_unique_id": (_i, [C.c_char_p]),
     "cbt_dp_init": (_i, [C.c_void_p, C.c_char_p, _i, _i, _i]),
     "cbt_dp_world": (_i, [C.c_void_p]),
+    "cbt_save_crseq": (_i, [C.c_void_p, C.c_char_p, C.c_uint]),
+    "cbt_load_crseq": (_i, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint)]),
 }
 KINDS = {0: "conv", 1: "bn_gamma", 2: "bn_beta", 3: "fc_weight", 4: "fc_bias"}
+
+
+def seeded_params(entries, n_params, seed_key="init") -> np.ndarray:
+    """The flat parameter vector init_params binds: entry i of `entries` (dicts with kind, offset, size, dims) drawn
+    from the generator keyed by (seed_key, i)."""
+    from . import seeds
+    host = np.zeros(n_params, dtype=np.float32)
+    for i, e in enumerate(entries):
+        sl = slice(e["offset"], e["offset"] + e["size"])
+        if e["kind"] == "conv":
+            oc, ic, fh, fw = e["dims"]
+            host[sl] = seeds.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / (ic * fh * fw))))
+        elif e["kind"] == "fc_weight":
+            host[sl] = seeds.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["dims"][1])))
+        elif e["kind"] == "fc_bias":
+            host[sl] = seeds.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["size"])))
+        elif e["kind"] == "bn_gamma":
+            host[sl] = 1.0
+    return host
 
 
 def _load():
@@ -97,19 +118,7 @@ class ResNetTrainer:
     def init_params(self, seed_key="init") -> np.ndarray:
         """He-normal filters and dense weights, gamma = 1, beta = 0 — the reference's randFillNetParams
         (seann/operands/seblas/Conv2D.cu:45-50, Linear.cu:42-46, BatchNorm.cu:8-11) with seeded draws."""
-        from . import seeds as orc
-        host = np.zeros(self.n_params, dtype=np.float32)
-        for i, e in enumerate(self.entries):
-            sl = slice(e["offset"], e["offset"] + e["size"])
-            if e["kind"] == "conv":
-                oc, ic, fh, fw = e["dims"]
-                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / (ic * fh * fw))))
-            elif e["kind"] == "fc_weight":
-                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["dims"][1])))
-            elif e["kind"] == "fc_bias":
-                host[sl] = orc.normal((e["size"],), seed_key, i, std=float(np.sqrt(2.0 / e["size"])))
-            elif e["kind"] == "bn_gamma":
-                host[sl] = 1.0
+        host = seeded_params(self.entries, self.n_params, seed_key)
         self.set_params(host)
         return host
 
@@ -122,6 +131,17 @@ class ResNetTrainer:
     def params_changed(self):
         """Call after writing to self.params directly: the executor re-packs its cached convolution filters."""
         self._check(self.lib.cbt_params_changed(self.h))
+
+    def save_crseq(self, path: str, epoch: int = 0):
+        """Write the parameters as a .crseq file the reference's loadSequence reads (seio/modelcache/codec.cu:41-97)."""
+        self._check(self.lib.cbt_save_crseq(self.h, str(path).encode(), int(epoch)))
+
+    def load_crseq(self, path: str) -> int:
+        """Load the parameters of a .crseq file written by the reference's saveSequence (seio/modelcache/codec.cu:8-39)
+        or by save_crseq; returns the file's epoch id."""
+        epoch = C.c_uint(0)
+        self._check(self.lib.cbt_load_crseq(self.h, str(path).encode(), C.byref(epoch)))
+        return int(epoch.value)
 
     def set_reference_bn_grad_order(self, on: bool):
         """Store BatchNorm's d(gamma) / d(beta) in each other's slot, as the reference's operand does

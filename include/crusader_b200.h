@@ -299,6 +299,16 @@ int cb_conv_fwd_noalloc(int device, void* cuda_stream, const float* W, const flo
                         int relu, char* err, int err_len);
 int cb_conv_fwd_noalloc_status(int device, void* cuda_stream, char* err, int err_len);
 
+/*
+ * Host-only readers of a .crseq model file (seio/modelcache/codec.cuh:14-70 file layout): operand count (branch
+ * operands of shortcut endpoints included), epoch id and the number of parameter floats; and the parameter section as
+ * the file stores it (operand order; BatchNorm beta before gamma). No GPU is touched. CB_EINVAL with a message in
+ * `err` for a file that is not .crseq, is truncated, or names an operand outside the supported vocabulary.
+ */
+int cb_crseq_inspect(const char* path, unsigned* operand_count, unsigned* epoch, unsigned long long* param_floats,
+                     char* err, int err_len);
+int cb_crseq_read_params(const char* path, float* out, unsigned long long count, char* err, int err_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -72,6 +72,18 @@ int cbt_dp_world(const cbt_model* m);
  * swapped order); for step-by-step comparisons with the reference's own operand graph. Default 0: the right slots. */
 int cbt_set_reference_bn_grad_order(cbt_model* m, int on);
 
+/*
+ * The reference's model files (.crseq; writer seio/modelcache/codec.cu:8-39 saveSequence, reader :41-97 loadSequence,
+ * records seann/operands/<operand>::encodeInfo / encodeNetParams and seann/containers/NetParam.cuh:45-72), for ResNet
+ * models, whose operand list is the reference's own (cuConv2D, BatchNorm, ReLU, ShortcutEndpoint pairs with the 1x1
+ * projection as branch operand, GlobalAvgPool, Linear, Softmax). cbt_save_crseq writes the bound parameters in that
+ * format (replacing the file; block uuids 1, 2, ...); cbt_load_crseq checks that the file describes this very network
+ * and loads its parameters, returning the file's epoch id. Both wait for the context's stream. CB_EUNSUPPORTED for
+ * other model families, CB_EINVAL with cbt_last_error naming the first difference for a file of another network.
+ */
+int cbt_save_crseq(cbt_model* m, const char* path, unsigned epoch);
+int cbt_load_crseq(cbt_model* m, const char* path, unsigned* epoch);
+
 /* Mean cross-entropy per sample of the last forward pass (synchronises the stream), as Sequential::train logs it. */
 int cbt_loss(cbt_model* m, float* loss_mean);
 /* Device pointers for tests: value (grad = 0) / gradient (grad = 1) of tensor id; -1 = logits, -2 = softmax. */

@@ -50,7 +50,40 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
     _run_pair(torch, lib, ctx, "na1", 8, 64, 32, 64, 3, bias=False, relu=False)
     _run_pair(torch, lib, ctx, "na2", 4, 16, 16, 12, 3, bias=True, relu=True)
     _run_pair(torch, lib, ctx, "na3", 4, 40, 8, 48, 1, bias=True, relu=False)
+    # no bounded device-side wait expired in any of the three calls
+    err = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.cb_conv_fwd_noalloc_status(0, ctypes.c_void_p(stream), err, 256) == 0, err.value.decode()
     ctx.close()
+
+
+def test_noalloc_leaves_device_memory_and_current_device_alone():
+    """The property the entry point exists for: a call (after the first one on the device, which only resolves symbol
+    addresses) takes no device memory — the driver reports the same free byte count before and after — and the
+    caller's current device is what it was."""
+    import torch
+    from crusaderbackend_b200 import _lib
+    lib = _lib.load()
+    W = torch.from_numpy(orc.he_normal_filter(32, 32, 3, 3, "na_mem")).cuda()
+    X = torch.from_numpy(orc.normal((8, 32, 16, 16), "na_mem", "X")).cuda()
+    Y = torch.empty(8, 32, 16, 16, device="cuda")
+    err = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.cb_conv_fwd_noalloc(0, ctypes.c_void_p(stream), W.data_ptr(), X.data_ptr(), Y.data_ptr(), None, 8, 32, 16,
+                                     16, 32, 3, 3, 1, 1, 1, 1, 0, err, 256)
+        assert rc == 0, err.value.decode()
+        torch.cuda.synchronize()
+
+    call()  # first call on this device: set-up
+    before = torch.cuda.current_device()
+    free0, _ = torch.cuda.mem_get_info()   # cudaMemGetInfo: the driver's count, not torch's allocator's
+    for _ in range(3):
+        call()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert torch.cuda.current_device() == before
 
 
 def test_noalloc_rejects_what_does_not_fit():
