@@ -111,6 +111,11 @@ class ResNetTrainer:
 
     def close(self):
         if getattr(self, "h", None):
+            # NCCL does not release a communicator while a CUDA graph that captured one of its collectives is alive
+            # (ncclCommDestroy waits for the graph), so the graphs of capture_step go first
+            for g in getattr(self, "_graphs", []):
+                g.reset()
+            self._graphs = []
             self.lib.cbt_destroy(self.h)
             self.h = None
 
@@ -208,6 +213,9 @@ class ResNetTrainer:
             self.update(lr, beta, l2)
         self.ctx._check(self.ctx.lib.cb_set_stream(self.ctx.h, C.c_void_p(old.cuda_stream)))
         torch.cuda.synchronize()
+        if not hasattr(self, "_graphs"):
+            self._graphs = []
+        self._graphs.append(graph)   # close() resets them before the executor (and its communicator) goes
         return graph
 
     def loss_tensor(self) -> torch.Tensor:

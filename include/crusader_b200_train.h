@@ -62,6 +62,8 @@ int cbt_set_bn_groups(cbt_model* m, int groups);
  * produced its last gradient, so the exchange overlaps the rest of the backward pass; everything queued on the
  * context's stream after cbt_backward sees the summed gradients. Every rank then applies the same cbt_update, so the
  * replicas stay bit-identical without a broadcast. NCCL is loaded at run time (libnccl.so.2); CB_EUNSUPPORTED without it.
+ * A CUDA graph that captured cbt_backward of a data-parallel model must be destroyed before cbt_destroy: NCCL keeps
+ * a communicator alive, and ncclCommDestroy waiting, for as long as a graph holds one of its collectives.
  */
 int cbt_dp_unique_id(char* id128);
 int cbt_dp_init(cbt_model* m, const char* id128, int world, int rank, int buckets);
