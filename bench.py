@@ -138,9 +138,9 @@ def resnet56_step(torch, local, world, rank, steps, warmup, weak=False, sampler=
         d_lab[b].copy_(h_lab)
     lr = 0.01 / gb
     tr.step(d_img[0], d_lab[0], lr)                      # first use: scratch, packed filters, NCCL set-up
-    l0 = ctx.launches
+    l0 = tr.launches
     tr.step(d_img[0], d_lab[0], lr)
-    kernels_per_step = ctx.launches - l0                 # steady state
+    kernels_per_step = tr.launches - l0                  # steady state, all of the executor's streams
     graphs = [tr.capture_step(d_img[b], d_lab[b], lr, warmup=1 if b == 0 else 0) for b in range(2)]
     loss_dev = torch.empty(1, device="cuda")
     h_loss = torch.empty(1).pin_memory()
@@ -345,9 +345,9 @@ def densenet_section(torch, local):
     lab = torch.zeros(64, 10, device="cuda")
     lab[torch.arange(64), torch.from_numpy(seeds.rng_for("dn100", "lab").integers(0, 10, 64)).cuda()] = 1
     tr.step(img, lab, 0.01 / 64)
-    l0 = ctx.launches
+    l0 = tr.launches
     tr.step(img, lab, 0.01 / 64)
-    kernels = ctx.launches - l0
+    kernels = tr.launches - l0
     g = tr.capture_step(img, lab, 0.01 / 64, warmup=1)
     for _ in range(3):
         g.replay()

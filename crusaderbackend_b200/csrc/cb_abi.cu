@@ -1,5 +1,6 @@
 // C-ABI entry points: context management, error reporting and the GEMM dispatcher.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -176,6 +177,7 @@ int cb_create(cb_ctx** out, int device, void* cuda_stream) {
     ctx->stream = static_cast<cudaStream_t>(cuda_stream);
     ctx->sm_count = prop.multiProcessorCount;
     ctx->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (const char* e = std::getenv("CB_PDL")) ctx->pdl = std::atoi(e) != 0;  // development switch, default on
     if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
         delete ctx;
         return CB_ENOMEM;

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/crusader_b200.h"
@@ -33,6 +34,7 @@ struct cb_ctx {
     int filter_cache_on = 0;       // packed convolution filters are kept between calls (cb_conv_cache_filters)
     long long filter_version = 0;  // bumped by every call that may have changed a filter's values
     void* filter_cache = nullptr;  // the cache itself (conv_sm100.cu)
+    int pdl = 1;                   // launch kernels that call griddep_wait with programmatic stream serialization
 };
 
 namespace cb {
@@ -43,6 +45,29 @@ int check_cuda(cb_ctx* ctx, cudaError_t e, const char* what);
 const char* status_name(int s);
 // Returns after an optional sync; maps a non-zero device status word to CB_ETIMEOUT.
 int finish(cb_ctx* ctx, const char* what);
+// Launches `kernel` on the context's stream; with ctx->pdl the launch carries the programmatic-stream-serialization
+// attribute, so ONLY for kernels whose every thread calls griddep_wait() before its first access to global memory
+// that an earlier kernel may have written or may still read.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep_on(cudaStream_t stream, bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep(cb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    return launch_dep_on(ctx->stream, ctx->pdl != 0, kernel, grid, block, smem, std::forward<Args>(args)...);
+}
+
 // CB_OK when ctx is non-null and its device is the current one.
 int enter(cb_ctx* ctx);
 // Grows one of the context's scratch blocks to at least `bytes`; growth waits for the whole device before the old

@@ -85,6 +85,13 @@ enum : int {
 
 // Bounded wait: gives up after CB_WAIT_LIMIT_NS of wall time (or when another role raised the abort
 // flag). Returns true when the phase completed, false on abort/timeout.
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start while
+// the kernel before it on the stream is still running: griddep_wait returns once that kernel has completed and its
+// writes are visible (immediately for a kernel launched without the attribute), so everything before it must touch
+// no global memory another kernel produces; griddep_launch lets the kernel after this one begin the same way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                               int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -225,6 +225,11 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Up to here nothing has touched global memory (barriers, descriptor prefetch of kernel parameters, TMEM): the
+    // kernel before this one may still be running. From here on its results are complete, and the kernel after this
+    // one may begin its own preamble.
+    griddep_wait();
+    griddep_launch();
     const uint32_t tmem_base = cs.tmem_base;
     const uint32_t acc_stride = (uint32_t)p.tmem_cols >> 1;
     uint32_t armed = 0, armed_parity = 0;  // producer lane: stages armed at least once / parity of their last arming
@@ -457,6 +462,8 @@ __global__ void pack_filter_kernel(const PackJob j) {
 }
 // Every cached filter of a context in one launch: blockIdx.y indexes a device table of jobs.
 __global__ void pack_filter_table_kernel(const PackJob* __restrict__ jobs) {
+    griddep_wait();
+    griddep_launch();
     const PackJob j = jobs[blockIdx.y];
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < j.total; i += (long long)gridDim.x * blockDim.x)
         j.Wp[i] = pack_value(j, i);
@@ -466,6 +473,8 @@ __global__ void pack_filter_table_kernel(const PackJob* __restrict__ jobs) {
 // Xs[n][phase*C + c][i][j] = X[n][c][2i + (phase >> 1)][2j + (phase & 1)]
 __global__ void space_to_depth2_kernel(const float* __restrict__ X, float* __restrict__ Xs, int C, int H, int W,
                                        long long total) {
+    griddep_wait();
+    griddep_launch();
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -482,6 +491,8 @@ __global__ void space_to_depth2_kernel(const float* __restrict__ X, float* __res
 // dX[n][c][y][x] (+)= dXs[group][n][o][y/2][x/2] with phase*C + c = group*per_group + o
 __global__ void depth_to_space2_kernel(const float* __restrict__ dXs, float* __restrict__ dX, int N, int C, int H, int W,
                                        int per_group, long long total, int accumulate) {
+    griddep_wait();
+    griddep_launch();
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -500,6 +511,8 @@ __global__ void depth_to_space2_kernel(const float* __restrict__ dXs, float* __r
 // Xsub[nc][i][j] = X[nc][2i][2j]
 __global__ void subsample2_kernel(const float* __restrict__ X, float* __restrict__ Xsub, long long NC, int H, int W,
                                   long long total) {
+    griddep_wait();
+    griddep_launch();
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -513,6 +526,8 @@ __global__ void subsample2_kernel(const float* __restrict__ X, float* __restrict
 // dX[nc][y][x] (+)= (y, x both even) ? dXsub[nc][y/2][x/2] : 0
 __global__ void upsample2_zero_kernel(const float* __restrict__ dXsub, float* __restrict__ dX, int H, int W,
                                       long long total, int accumulate) {
+    griddep_wait();
+    griddep_launch();
     const int H2 = H / 2, W2 = W / 2;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -769,8 +784,9 @@ int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const fl
     if (per_split > p.tiles) per_split = p.tiles;
     const int grid = per_split * q.nsplit;
     const int taps = FW == 1 ? TAPS_1 : (FW == 3 ? TAPS_3 : (pW == 1 ? TAPS_2L : TAPS_2R));
-    kernels[q.ew == 8 ? 0 : 1][taps]<<<grid, 64 + 32 * q.ew, smem, env.stream>>>(tmIn, tmW, tmOut, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dep_on(env.stream, err_ctx && err_ctx->pdl, kernels[q.ew == 8 ? 0 : 1][taps], dim3((unsigned)grid),
+                                  dim3((unsigned)(64 + 32 * q.ew)), smem, tmIn, tmW, tmOut, p);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(err_ctx, e, "umma_conv_kernel launch");
     return CB_OK;
 }
@@ -779,16 +795,16 @@ int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const fl
 
 int launch_space_to_depth2(cb_ctx* ctx, const float* X, float* Xs, int N, int C, int H, int W) {
     const long long n_el = (long long)N * C * H * W;
-    space_to_depth2_kernel<<<relayout_grid(ctx, n_el), 256, 0, ctx->stream>>>(X, Xs, C, H, W, n_el);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dep(ctx, space_to_depth2_kernel, dim3((unsigned)relayout_grid(ctx, n_el)), dim3(256), 0, X, Xs, C, H, W, n_el);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "space_to_depth2_kernel launch");
     ctx->launches += 1;
     return CB_OK;
 }
 int launch_subsample2(cb_ctx* ctx, const float* X, float* Xsub, long long NC, int H, int W) {
     const long long n_sub = NC * (H / 2) * (W / 2);
-    subsample2_kernel<<<relayout_grid(ctx, n_sub), 256, 0, ctx->stream>>>(X, Xsub, NC, H, W, n_sub);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dep(ctx, subsample2_kernel, dim3((unsigned)relayout_grid(ctx, n_sub)), dim3(256), 0, X, Xsub, NC, H, W, n_sub);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "subsample2_kernel launch");
     ctx->launches += 1;
     return CB_OK;
@@ -900,8 +916,9 @@ int filter_cache_repack_all(cb_ctx* ctx) {
     int gx = (int)((fc->biggest + 255) / 256);
     if (gx > 64) gx = 64;
     if (gx < 1) gx = 1;
-    pack_filter_table_kernel<<<dim3(gx, (unsigned)fc->dev_table_entries), 256, 0, ctx->stream>>>(fc->dev_table);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dep(ctx, pack_filter_table_kernel, dim3((unsigned)gx, (unsigned)fc->dev_table_entries), dim3(256), 0,
+                               (const PackJob*)fc->dev_table);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "pack_filter_table_kernel launch");
     ctx->launches += 1;
     for (FilterCacheEntry& en : fc->entries) en.version = ctx->filter_version;
@@ -965,8 +982,8 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const C
             rc = conv_on_packed(ctx, env, q, ps, W, X /* = dY */, sub, plain, N, H2, W2, 1, 1, 0, 0, 0, 0);
             const long long n_full = (long long)N * IC * IH * IW;
             if (rc == CB_OK) {
-                upsample2_zero_kernel<<<relayout_grid(ctx, n_full), 256, 0, ctx->stream>>>(sub, Y /* = dX */, IH, IW, n_full,
-                                                                                           ep.accumulate ? 1 : 0);
+                launch_dep(ctx, upsample2_zero_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0, (const float*)sub,
+                           Y /* = dX */, IH, IW, n_full, ep.accumulate ? 1 : 0);
                 ctx->launches += 1;
             }
         }
@@ -1011,9 +1028,9 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const C
         if (rc != CB_OK) return rc;
     }
     const long long n_full = (long long)N * IC * IH * IW;
-    depth_to_space2_kernel<<<relayout_grid(ctx, n_full), 256, 0, ctx->stream>>>(dXs, Y /* = dX */, N, IC, IH, IW, per_group,
-                                                                                n_full, ep.accumulate ? 1 : 0);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dep(ctx, depth_to_space2_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0,
+                               (const float*)dXs, Y /* = dX */, N, IC, IH, IW, per_group, n_full, ep.accumulate ? 1 : 0);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "depth_to_space2_kernel launch");
     ctx->launches += 1;
     ctx->last_kernel = "umma_tf32";

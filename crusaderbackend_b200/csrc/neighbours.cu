@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "cb_internal.h"
+#include "cb_ptx.cuh"
 
 namespace cb {
 namespace {
@@ -220,6 +221,8 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
                                                          float* __restrict__ var, float* __restrict__ Y,
                                                          float* __restrict__ xhat, const float* __restrict__ res, int N,
                                                          long long P, int relu) {
+    griddep_wait();
+    griddep_launch();
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -276,6 +279,8 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                          const float* __restrict__ relu_out, float* __restrict__ dres,
                                                          int dres_add, int pg_add, int N, long long P) {
+    griddep_wait();
+    griddep_launch();
     __shared__ float4 red[16][16];
     const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
     const bool live = p < P;
@@ -389,13 +394,14 @@ inline int bn_spt(int N) {
 template <int SPT>
 void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
                        float* xhat, const float* res, int N, long long P, int relu) {
-    bn_fwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, res, N, P, relu);
+    launch_dep(ctx, bn_fwd_par_kernel<SPT>, dim3((unsigned)((P / 4 + 15) / 16)), dim3(16, 16), 0, X, beta, gamma, mean, var, Y, xhat, res,
+               N, P, relu);
 }
 template <int SPT>
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                        float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
-    bn_bwd_par_kernel<SPT><<<(unsigned)((P / 4 + 15) / 16), dim3(16, 16), 0, ctx->stream>>>(dY, gamma, X, dX, dgamma, dbeta, relu_out,
-                                                                                            dres, dres_add, pg_add, N, P);
+    launch_dep(ctx, bn_bwd_par_kernel<SPT>, dim3((unsigned)((P / 4 + 15) / 16)), dim3(16, 16), 0, dY, gamma, X, dX, dgamma, dbeta,
+               relu_out, dres, dres_add, pg_add, N, P);
 }
 #define BN_SPT_SWITCH(spt, CALL)            \
     switch (spt) {                          \
@@ -593,6 +599,8 @@ struct MomentumTensor {
 };
 // blockIdx.y = tensor. w *= (1 - l2) for weight tensors, m = beta m + (1 - beta) g, w -= lr m, g = 0.
 __global__ void momentum_multi_kernel(const MomentumTensor* __restrict__ ts, float lr, float beta, float l2) {
+    griddep_wait();
+    griddep_launch();
     const MomentumTensor t = ts[blockIdx.y];
     const float decay = t.is_weight ? (1.0f - l2) : 1.0f;
     const float omb = 1.0f - beta;
@@ -650,6 +658,8 @@ __global__ void __launch_bounds__(256) head_fwd_kernel(const float* __restrict__
                                                        float* __restrict__ pooled, float* __restrict__ logits,
                                                        float* __restrict__ probs, float* __restrict__ dlogits,
                                                        float* __restrict__ loss_n, int C, int HW, int M) {
+    griddep_wait();
+    griddep_launch();
     extern __shared__ float sh[];  // pooled[C]
     const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* Xn = X + (long long)n * C * HW;
@@ -694,6 +704,8 @@ __global__ void __launch_bounds__(256) head_bwd_kernel(const float* __restrict__
                                                        float* __restrict__ dW, float* __restrict__ db,
                                                        const float* __restrict__ loss_n, float* __restrict__ loss_sum, int N,
                                                        int C, int HW, int M) {
+    griddep_wait();
+    griddep_launch();
     extern __shared__ float sh[];  // dpooled[C]
     const int n = blockIdx.x;
     if (n < N) {
@@ -983,8 +995,8 @@ int cb_head_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, con
     if (N == 0) return CB_OK;
     if (!X || !W || !labels || !pooled || !logits || !probs || !dlogits || !loss_per_sample)
         return fail(ctx, CB_EINVAL, "cb_head_fwd: null operand");
-    head_fwd_kernel<<<N, 256, (size_t)C * sizeof(float), ctx->stream>>>(X, W, b, labels, pooled, logits, probs, dlogits,
-                                                                        loss_per_sample, C, HW, M);
+    launch_dep(ctx, head_fwd_kernel, dim3((unsigned)N), dim3(256), (size_t)C * sizeof(float), X, W, b, labels, pooled, logits, probs,
+               dlogits, loss_per_sample, C, HW, M);
     return done(ctx, "cb_head_fwd");
 }
 
@@ -995,8 +1007,8 @@ int cb_head_bwd(cb_ctx* ctx, const float* dlogits, const float* pooled, const fl
     if (C > 8192) return fail(ctx, CB_EUNSUPPORTED, "cb_head_bwd: at most 8192 channels");
     if (N == 0) return CB_OK;
     if (!dlogits || !pooled || !W || !dX || !dW || (loss_sum && !loss_per_sample)) return fail(ctx, CB_EINVAL, "cb_head_bwd: null operand");
-    head_bwd_kernel<<<N + 1, 256, (size_t)C * sizeof(float), ctx->stream>>>(dlogits, pooled, W, dX, dW, db, loss_per_sample,
-                                                                            loss_sum, N, C, HW, M);
+    launch_dep(ctx, head_bwd_kernel, dim3((unsigned)(N + 1)), dim3(256), (size_t)C * sizeof(float), dlogits, pooled, W, dX, dW, db,
+               loss_per_sample, loss_sum, N, C, HW, M);
     return done(ctx, "cb_head_bwd");
 }
 
@@ -1091,8 +1103,8 @@ int cb_momentum_multi(cb_ctx* ctx, int ntensors, float* const* w, float* const* 
     int gx = (int)((biggest / 4 + kThreads - 1) / kThreads);
     if (gx < 1) gx = 1;
     if (gx > 64) gx = 64;
-    momentum_multi_kernel<<<dim3(gx, ntensors), kThreads, 0, ctx->stream>>>(
-        static_cast<const MomentumTensor*>(ctx->workspace), lr, beta, l2);
+    launch_dep(ctx, momentum_multi_kernel, dim3((unsigned)gx, (unsigned)ntensors), dim3(kThreads), 0,
+               static_cast<const MomentumTensor*>(ctx->workspace), lr, beta, l2);
     return done(ctx, "cb_momentum_multi");
 }
 
@@ -1122,8 +1134,8 @@ int momentum_table_launch(cb_ctx* ctx, const void* dev_table, int ntensors, long
     int gx = (int)((biggest / 4 + kThreads - 1) / kThreads);
     if (gx < 1) gx = 1;
     if (gx > 64) gx = 64;
-    momentum_multi_kernel<<<dim3(gx, ntensors), kThreads, 0, ctx->stream>>>(static_cast<const MomentumTensor*>(dev_table), lr,
-                                                                           beta, l2);
+    launch_dep(ctx, momentum_multi_kernel, dim3((unsigned)gx, (unsigned)ntensors), dim3(kThreads), 0,
+               static_cast<const MomentumTensor*>(dev_table), lr, beta, l2);
     int rc = done(ctx, "momentum step");
     if (rc != CB_OK) return rc;
     return filter_cache_repack_all(ctx);  // the filters just changed: one launch re-packs every cached copy

@@ -14,7 +14,9 @@
 // data-parallel caller sum-allreduces ONE gradient buffer between cbt_backward and cbt_update.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -124,12 +126,22 @@ struct cbt_model {
     cudaEvent_t reduce_done = nullptr;
     std::vector<GradBucket> buckets;
     long long mom_biggest = 1;
+    // weight-gradient streams (cbt_set_wgrad_streams): each has a context of its own (own scratch blocks) whose kernels
+    // report into the main context's status word
+    std::vector<cb_ctx*> side;
+    std::vector<cudaStream_t> side_stream;
+    std::vector<cudaEvent_t> side_fork, side_join;
+    std::vector<int*> side_own_status;
+    std::vector<char> side_used;
+    int side_next = 0;
     // .crseq image of the model (ResNets): top-level operand ids, the words of the info section (uuid words flagged: a
     // file's own block numbering is accepted on load), and the parameter entries in the order the file stores them
     std::vector<uint32_t> crseq_ids, crseq_info;
     std::vector<uint8_t> crseq_info_is_uuid;
     std::vector<int> crseq_params;
 };
+
+extern "C" int cbt_set_wgrad_streams(cbt_model* m, int n);
 
 namespace {
 
@@ -334,7 +346,27 @@ int finalize_model(cbt_model* m, int x, int classes) {
     int rc = dev_alloc(m, &m->scratch, biggest);
     if (rc == CB_OK) rc = dev_alloc(m, &m->loss_dev, 4);
     if (rc == CB_OK) rc = dev_alloc(m, &m->loss_n, m->batch);
+    if (rc == CB_OK) {
+        const char* env = std::getenv("CBT_WGRAD_STREAMS");
+        int n = env ? std::atoi(env) : 2;
+        n = n < 0 ? 0 : (n > 4 ? 4 : n);
+        rc = cbt_set_wgrad_streams(m, n);
+    }
     return rc;
+}
+
+void release_side_streams(cbt_model* m) {
+    for (size_t s = 0; s < m->side.size(); ++s) {
+        cudaStreamSynchronize(m->side_stream[s]);
+        m->side[s]->d_status = m->side_own_status[s];
+        m->side[s]->stream = nullptr;
+        cb_destroy(m->side[s]);
+        cudaEventDestroy(m->side_fork[s]);
+        cudaEventDestroy(m->side_join[s]);
+        cudaStreamDestroy(m->side_stream[s]);
+    }
+    m->side.clear(); m->side_stream.clear(); m->side_fork.clear(); m->side_join.clear(); m->side_own_status.clear();
+    m->side_used.clear();
 }
 
 #define CBT_TRY(expr)                                              \
@@ -456,9 +488,50 @@ int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int
     return finalize_model(m, x, classes);
 }
 
+// The convolution weight gradients of the backward pass run on `n` streams of their own (0..4; 0 = on the context's
+// stream like everything else). They are off the critical path of the backward pass (only the update needs them), so
+// they fill the SMs the chain of data-gradient and BatchNorm kernels leaves idle. Each stream forks from the context's
+// stream where the layer's output gradient is complete and joins it again at the end of cbt_backward. Not while the
+// stream is being captured. New models start with the value of the environment variable CBT_WGRAD_STREAMS (default 2).
+int cbt_set_wgrad_streams(cbt_model* m, int n) {
+    if (!m || n < 0 || n > 4) return CB_EINVAL;
+    cudaStreamSynchronize(m->ctx->stream);
+    release_side_streams(m);
+    for (int s = 0; s < n; ++s) {
+        cudaStream_t st = nullptr;
+        cudaEvent_t ef = nullptr, ej = nullptr;
+        cb_ctx* c = nullptr;
+        cudaError_t e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ef, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ej, cudaEventDisableTiming);
+        if (e != cudaSuccess || cb_create(&c, m->ctx->device, st) != CB_OK) {
+            m->err = "creating a weight-gradient stream failed";
+            if (ef) cudaEventDestroy(ef);
+            if (ej) cudaEventDestroy(ej);
+            if (st) cudaStreamDestroy(st);
+            release_side_streams(m);
+            return CB_ECUDA;
+        }
+        m->side_own_status.push_back(c->d_status);
+        c->d_status = m->ctx->d_status;
+        m->side.push_back(c); m->side_stream.push_back(st); m->side_fork.push_back(ef); m->side_join.push_back(ej);
+    }
+    m->side_used.assign((size_t)n, 0);
+    return CB_OK;
+}
+
+// Kernel launches made so far on the weight-gradient streams (the context's own counter does not see them).
+long long cbt_side_launches(const cbt_model* m) {
+    long long n = 0;
+    if (m)
+        for (const cb_ctx* c : m->side) n += c->launches;
+    return n;
+}
+
 int cbt_destroy(cbt_model* m) {
     if (!m) return CB_EINVAL;
     cudaStreamSynchronize(m->ctx->stream);
+    release_side_streams(m);
     for (void* p : m->owned) cudaFree(p);
     if (m->mom_table) cudaFree(m->mom_table);
     if (m->comm) {
@@ -718,6 +791,12 @@ static int dp_release_buckets(cbt_model* m, int op_index) {
         if (bk.release_op != op_index || bk.count == 0) continue;
         cudaError_t e = cudaEventRecord(m->bucket_ready[b], m->ctx->stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(m->comm_stream, m->bucket_ready[b], 0);
+        // weight gradients of the bucket may still be in flight on their own streams
+        for (size_t s = 0; s < m->side.size() && e == cudaSuccess; ++s) {
+            if (!m->side_used[s]) continue;
+            e = cudaEventRecord(m->side_join[s], m->side_stream[s]);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(m->comm_stream, m->side_join[s], 0);
+        }
         if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
         const int rc = api->AllReduce(m->G + bk.offset, m->G + bk.offset, (size_t)bk.count, 7 /* ncclFloat32 */, 0 /* ncclSum */,
                                       m->comm, m->comm_stream);
@@ -734,6 +813,8 @@ static int dp_release_buckets(cbt_model* m, int op_index) {
 int cbt_backward(cbt_model* m) {
     if (!m || !m->G) return CB_EINVAL;
     cb_ctx* ctx = m->ctx;
+    m->side_next = 0;
+    std::fill(m->side_used.begin(), m->side_used.end(), 0);
     for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
         const Op& o = m->ops[i];
         TensorBuf& x = m->t[o.in0];
@@ -812,13 +893,29 @@ int cbt_backward(cbt_model* m) {
                 }
                 break;
             }
-            case OP_CONV:
-                CBT_TRY(cb_conv_wgrad(ctx, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
-                                      o.stride, o.pad, o.pad, 1));
+            case OP_CONV: {
+                cb_ctx* wc = ctx;
+                if (!m->side.empty()) {
+                    // fork: the weight gradient needs this layer's output gradient (complete at this point of the
+                    // context's stream) and its input, and nothing later in the backward pass needs the result
+                    const size_t s = (size_t)(m->side_next++) % m->side.size();
+                    wc = m->side[s];
+                    wc->math = ctx->math;
+                    wc->deterministic = ctx->deterministic;
+                    wc->workspace_frozen = ctx->workspace_frozen;
+                    cudaError_t e = cudaEventRecord(m->side_fork[s], ctx->stream);
+                    if (e == cudaSuccess) e = cudaStreamWaitEvent(m->side_stream[s], m->side_fork[s], 0);
+                    if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
+                    m->side_used[s] = 1;
+                }
+                const int rc_w = cb_conv_wgrad(wc, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                               o.stride, o.pad, o.pad, 1);
+                if (rc_w != CB_OK) { m->err = cb_last_error(wc); return rc_w; }
                 if (!to_input)
                     CBT_TRY(cb_conv_dgrad_ex(ctx, m->P + o.w_off, y.d, x.d, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
                                              o.stride, o.pad, o.pad, o.in0_grad_accumulate ? 1 : 0, 0, 0));
                 break;
+            }
         }
         if (o.in0_grad_accumulate && !native_acc && !to_input)
             CBT_TRY(cb_tensor_op(ctx, CB_OP_ADD, x.d, m->scratch, 0.f, x.size()));
@@ -826,6 +923,13 @@ int cbt_backward(cbt_model* m) {
             int rc = dp_release_buckets(m, i);
             if (rc != CB_OK) return rc;
         }
+    }
+    // join: everything queued on the context's stream after this call sees every weight gradient
+    for (size_t s = 0; s < m->side.size(); ++s) {
+        if (!m->side_used[s]) continue;
+        cudaError_t e = cudaEventRecord(m->side_join[s], m->side_stream[s]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, m->side_join[s], 0);
+        if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
     }
     if (m->comm) {
         // the gradients are summed over the ranks by the time anything later on the context's stream reads them

@@ -107,6 +107,9 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // nothing above touches global memory: the kernel before this one may still be running until here
+    griddep_wait();
+    griddep_launch();
     const uint32_t tmem_base = ws.tmem_base;
     if (threadIdx.x == 0) CB_TRACE_EVENT(p.trace, 2);
 
@@ -274,6 +277,8 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
     // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
     // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
     __shared__ float red[8][33];
+    griddep_wait();
+    griddep_launch();
     const long long total = (long long)rows_tot * NQ;
     const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
     const int grp = threadIdx.y;
@@ -404,14 +409,14 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
-    umma_wgrad_kernel<<<grid, 192 + 32 * kShiftWarps, smem, ctx->stream>>>(tmX, tmdY, p);
-    e = cudaGetLastError();
+    e = launch_dep(ctx, umma_wgrad_kernel, dim3((unsigned)grid), dim3(192 + 32 * kShiftWarps), smem, tmX, tmdY, p);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
     const long long total = (long long)mtiles * 128 * NQ;
     int rgrid = (int)((total + 31) / 32);
-    wgrad_reduce_kernel<<<rgrid, dim3(32, 8), 0, ctx->stream>>>(p.partial, dW, grid, mtiles * 128, rowsA, NQ, Cp, Cin, OC, OCp, FH, FW,
-                                                         accumulate ? 1 : 0, s2, IC_src);
-    e = cudaGetLastError();
+    e = launch_dep(ctx, wgrad_reduce_kernel, dim3((unsigned)rgrid), dim3(32, 8), 0, (const float*)p.partial, dW, grid, mtiles * 128,
+                   rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
     ctx->launches += 2;
     ctx->last_kernel = "umma_tf32";

@@ -38,6 +38,8 @@ TRAIN_SIGNATURES = {
     "cbt_dp_unique_id": (_i, [C.c_char_p]),
     "cbt_dp_init": (_i, [C.c_void_p, C.c_char_p, _i, _i, _i]),
     "cbt_dp_world": (_i, [C.c_void_p]),
+    "cbt_set_wgrad_streams": (_i, [C.c_void_p, _i]),
+    "cbt_side_launches": (_ll, [C.c_void_p]),
     "cbt_save_crseq": (_i, [C.c_void_p, C.c_char_p, C.c_uint]),
     "cbt_load_crseq": (_i, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint)]),
 }
@@ -171,6 +173,15 @@ class ResNetTrainer:
         dist.broadcast(t, 0)
         ident = bytes(t.cpu().tolist())
         self._check(self.lib.cbt_dp_init(self.h, ident, world, rank, buckets))
+
+    def set_wgrad_streams(self, n: int):
+        """Run the convolution weight gradients of the backward pass on n streams of their own (0 = inline)."""
+        self._check(self.lib.cbt_set_wgrad_streams(self.h, int(n)))
+
+    @property
+    def launches(self) -> int:
+        """Kernel launches so far: the context's stream plus the weight-gradient streams."""
+        return int(self.ctx.launches) + int(self.lib.cbt_side_launches(self.h))
 
     def set_bn_groups(self, groups: int):
         """BatchNorm statistics per group of batch/groups consecutive samples (what `groups` data-parallel ranks compute)."""

@@ -49,6 +49,14 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels_onehot);
 int cbt_backward(cbt_model* m);
 int cbt_update(cbt_model* m, float lr, float beta, float l2);
 
+/* The convolution weight gradients of cbt_backward run on `n` CUDA streams of the executor's own (0..4; 0: on the
+ * context's stream). Only the update needs them, so they fill the SMs that the chain of data-gradient and BatchNorm
+ * kernels leaves idle; each forks where its layer's output gradient is complete and joins before cbt_backward's work
+ * ends, so callers see no difference in ordering. Default: environment variable CBT_WGRAD_STREAMS, else 2. Not while
+ * the stream is being captured. cbt_side_launches counts the launches made there (cb_launch_count does not). */
+int cbt_set_wgrad_streams(cbt_model* m, int n);
+long long cbt_side_launches(const cbt_model* m);
+
 /* BatchNorm statistics per group of batch / groups consecutive samples instead of over the whole batch (default 1).
  * On one GPU, G groups compute exactly what G data-parallel ranks compute on their shards of the same batch. */
 int cbt_set_bn_groups(cbt_model* m, int groups);

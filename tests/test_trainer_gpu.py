@@ -162,6 +162,39 @@ def test_bn_groups_reproduce_sharded_gradients(torch_cuda):
     ctx.close()
 
 
+def test_wgrad_streams_do_not_change_results(torch_cuda):
+    """The weight gradients run on streams of their own, concurrently with the rest of the backward pass. Gradients after
+    one step and parameters after three (eager and as a replayed CUDA graph) are bit-identical for 0, 1 and 3 streams."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import ResNetTrainer
+    _, _, dimg, dlab = make_batch(torch, 16, 32, 10, "wstreams")
+    results = []
+    for n in (0, 1, 3):
+        ctx = Context(0, math="tf32", sync=False)
+        tr = ResNetTrainer(ctx, batch=16, blocks_per_stage=2, image_hw=32, classes=10)
+        tr.set_wgrad_streams(n)
+        tr.init_params("wstreams")
+        l0 = tr.launches
+        tr.forward(dimg, dlab)
+        tr.backward()
+        ctx.synchronize()
+        launches = tr.launches - l0
+        g1 = tr.grads.clone()
+        tr.update(1e-3)
+        tr.step(dimg, dlab, 1e-3)
+        g = tr.capture_step(dimg, dlab, 1e-3, warmup=0)
+        g.replay()
+        ctx.synchronize()
+        results.append((g1, tr.params.clone(), launches))
+        tr.close()
+        ctx.close()
+    for g1, p, launches in results[1:]:
+        assert torch.equal(g1, results[0][0])
+        assert torch.equal(p, results[0][1])
+        assert launches == results[0][2]
+
+
 def test_resnet56_loss_tracks_fp32_run(torch_cuda):
     """ResNet-56, batch 128 of N(0,1) CIFAR-shaped images, uniform labels, He init, momentum 0.9, lr 0.01/128, 200 steps
     on a repeated batch: the loss of the TF32 and of the 3xTF32 tensor-core run stays within 1 % (of the curve's largest
