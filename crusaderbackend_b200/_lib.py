@@ -38,6 +38,7 @@ SIGNATURES = {
     "cb_launch_count": (_ll, [_ctx]),
     "cb_last_kernel": (C.c_char_p, [_ctx]),
     "cb_gemm": (_i, [_ctx, _i, _i, _i, _i, _i, _f, _i, _f, _i, _f, _i, _i, _ll, _ll, _ll, _i]),
+    "cb_gemm_batch_reduce": (_i, [_ctx, _i, _i, _i, _i, _i, _f, _i, _f, _i, _f, _i, _i, _ll, _ll, _i]),
     "cb_measure_umma_peak": (_i, [_ctx, _i, _i, _i, _i, C.POINTER(_fl)]),
     "cb_conv_fwd": (_i, [_ctx, _f, _f, _f, _f] + [_i] * 12),
     "cb_conv_dgrad": (_i, [_ctx, _f, _f, _f] + [_i] * 11),

@@ -125,6 +125,21 @@ class Context:
         """seblas::sgemmNT: C = A @ B^T, B stored N x K (seblas/operations/cuGEMM.cu:1685)."""
         return self.gemm(A, B, Cout, transB=True)
 
+    def sgemmNTA(self, A, B, Cout):
+        """seblas::sgemmNTA: C += sum over n of A[n] @ B[n]^T, A n x M x K, B n x N x K, C M x N
+        (seblas/operations/cuGEMM.cu:1701); the batch is folded into the contraction, one launch."""
+        if A.dim() != 3 or B.dim() != 3 or Cout.dim() != 2:
+            raise ValueError("sgemmNTA: A and B are 3-D (batch first), C is 2-D")
+        for t in (A, B, Cout):
+            if t.stride(-1) != 1:
+                raise ValueError("operands must be row-major (unit inner stride)")
+        n, M, K = A.shape
+        if B.shape[0] != n or B.shape[2] != K or tuple(Cout.shape) != (M, B.shape[1]):
+            raise ValueError("sgemmNTA: shapes do not agree")
+        self._check(self.lib.cb_gemm_batch_reduce(self.h, 0, 1, M, B.shape[1], K, _ptr(A), A.stride(1), _ptr(B), B.stride(1),
+                                                  _ptr(Cout), Cout.stride(0), n, A.stride(0), B.stride(0), 1))
+        return Cout
+
     # ---- convolution: arguments in the order of seblas::conv / convDerive / convError
     @staticmethod
     def _geo(W, X, stride, pad):

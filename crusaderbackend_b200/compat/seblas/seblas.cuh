@@ -269,9 +269,8 @@ inline Tensor* sgemmNT(Tensor* A, Tensor* B, Tensor* C) {  // B stored N x K
 inline Tensor* sgemmNTA(Tensor* A, Tensor* B, Tensor* C) {  // C += sum over A->dims.n of A[n] * B[n]^T
     assert(A->dims.w == B->dims.w && A->dims.h == C->dims.h && B->dims.h == C->dims.w);
     const int M = A->dims.h, K = A->dims.w, N = B->dims.h;
-    for (uint32 n = 0; n < A->dims.n; ++n)
-        SEBLAS_CB(cb_gemm(context(), 0, 1, M, N, K, A->elements + (size_t)n * M * K, K, B->elements + (size_t)n * N * K, K,
-                          C->elements, N, 1, 0, 0, 0, 1));
+    SEBLAS_CB(cb_gemm_batch_reduce(context(), 0, 1, M, N, K, A->elements, K, B->elements, K, C->elements, N, (int)A->dims.n,
+                                   (long long)M * K, (long long)N * K, 1));
     return C;
 }
 

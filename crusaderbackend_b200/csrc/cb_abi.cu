@@ -311,4 +311,44 @@ int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const floa
     return finish(ctx, "cb_gemm");
 }
 
+// C (+)= sum over `count` operand pairs of op(A[b]) * op(B[b]): the batch is folded into the contraction, one launch on
+// the tensor-core path (the k-blocks walk the pairs); the CUDA-core fp32 path adds the pairs one after the other.
+int cb_gemm_batch_reduce(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
+                         int ldb, float* C, int ldc, int count, long long strideA, long long strideB, int accumulate) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (M < 0 || N < 0 || K < 0 || count < 0) return fail(ctx, CB_EINVAL, "cb_gemm_batch_reduce: negative extent");
+    if (M == 0 || N == 0) return CB_OK;
+    if (!A || !B || !C) return fail(ctx, CB_EINVAL, "cb_gemm_batch_reduce: null operand");
+    if (lda < (transA ? M : K) || ldb < (transB ? K : N) || ldc < N)
+        return fail(ctx, CB_EINVAL, "cb_gemm_batch_reduce: leading dimension smaller than the row length");
+    if (K == 0 || count == 0) {
+        if (!accumulate) {
+            cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, M, ctx->stream);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "cb_gemm_batch_reduce: clear of C");
+        }
+        return finish(ctx, "cb_gemm_batch_reduce");
+    }
+    GemmCall g;
+    g.I = N; g.J = M; g.K = K; g.batch = 1;
+    g.P = B; g.ldp = ldb; g.strideP = strideB; g.p_mn = transB ? 0 : 1;
+    g.Q = A; g.ldq = lda; g.strideQ = strideA; g.q_mn = transA ? 1 : 0;
+    g.C = C; g.ldc = ldc; g.strideC = 0; g.out_mode = 0;
+    g.accumulate = accumulate ? 1 : 0;
+    g.kfold = count;
+    int rc = CB_OK;
+    if (ctx->math != CB_MATH_FP32 && umma_gemm_eligible(g)) {
+        rc = launch_umma_gemm(ctx, g, ctx->math == CB_MATH_3XTF32);
+    } else {
+        g.kfold = 1;
+        for (int b = 0; b < count && rc == CB_OK; ++b) {
+            g.P = B + (long long)b * strideB;
+            g.Q = A + (long long)b * strideA;
+            g.accumulate = (accumulate || b > 0) ? 1 : 0;
+            rc = launch_simt_gemm(ctx, g);
+        }
+    }
+    if (rc != CB_OK) return rc;
+    return finish(ctx, "cb_gemm_batch_reduce");
+}
+
 }  // extern "C"

@@ -100,6 +100,7 @@ struct GemmCall {
     float* C = nullptr; long long ldc = 0, strideC = 0; int out_mode = 0;
     int accumulate = 0;
     Epilogue ep;
+    int kfold = 1;  // > 1 (with batch == 1): C (+)= sum over kfold operand pairs, strideP / strideQ apart, of P Q^T
 };
 // Per-element tail of a convolution, applied in this order while the accumulator is written out:
 // y = conv; y = y * scale + shift (if scale); y += bias[oc] (if bias); y += out (if accumulate); y = max(y, 0) (if relu).

@@ -37,6 +37,7 @@ struct GemmParams {
     int mi, bn;            // P sub-tiles per CTA tile, UMMA N
     int stages;
     int num_kb, splits, kb_per_split;
+    int kb_per_fold;       // > 0: the k-blocks walk `kfold` operand pairs of kb_per_fold blocks each (their products are summed)
     int kc;                // k-blocks per accumulation chunk: the accumulator is drained to C every kc blocks
     int tmem_cols;         // allocated TMEM columns (power of two >= 2*bn)
     int p_batched, q_batched;
@@ -151,9 +152,16 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
             const WorkItem it = decode_work(p, w);
-            const int bp = p.p_batched ? it.b : 0;
-            const int bq = p.q_batched ? it.b : 0;
             for (int kb = it.kb0; kb < it.kb1; ++kb) {
+                // operand pair and k-offset of this block: the batch index of the work item, or, with the batch folded
+                // into K, the pair the block falls in (the tail of every pair is zero-filled by TMA)
+                int pair = it.b, kk = kb;
+                if (p.kb_per_fold) {
+                    pair = kb / p.kb_per_fold;
+                    kk = kb - pair * p.kb_per_fold;
+                }
+                const int bp = p.p_batched ? pair : 0;
+                const int bq = p.q_batched ? pair : 0;
                 ok = warp_wait(smem_u32(&ps.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
                 if (!ok) break;
                 if (lane == 0) {
@@ -163,7 +171,7 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
                     mbar_expect_tx(full, hi_bytes);
                     armed |= 1u << s;
                     armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
-                    const int k0 = kb * kBK;
+                    const int k0 = kk * kBK;
                     if (P_MN) {
                         for (int bx = 0; bx < 4 * p.mi; ++bx)
                             tma_load_3d(sP + bx * 4096u, &tmP, full, it.i0 + 32 * bx, k0, bp);
@@ -551,14 +559,16 @@ bool umma_gemm_eligible(const GemmCall& g) {
     auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!aligned16(g.P) || !aligned16(g.Q)) return false;
     if ((g.ldp & 3) || (g.ldq & 3)) return false;
-    if (g.batch > 1 && ((g.strideP & 3) || (g.strideQ & 3))) return false;
+    if ((g.batch > 1 || g.kfold > 1) && ((g.strideP & 3) || (g.strideQ & 3))) return false;
+    if (g.kfold > 1 && g.batch != 1) return false;
     if (g.I < 1 || g.J < 1 || g.K < 1) return false;
     return true;
 }
 
 int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     // ---- tile configuration
-    const int num_kb = (g.K + kBK - 1) / kBK;
+    const int kfold = g.kfold > 1 ? g.kfold : 1;
+    const int num_kb = kfold * ((g.K + kBK - 1) / kBK);
     const int smem_cap = ctx->max_smem_optin - 2048;  // static barriers + 1 KB alignment slack
     int best_mi = 1, best_bn = 16, best_stages = 2, best_splits = 1;
     double best_cost = 1e300;
@@ -619,8 +629,10 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     int cols = 32;
     while (cols < 2 * gp.bn) cols <<= 1;
     gp.tmem_cols = cols;
-    gp.p_batched = (g.batch > 1 && g.strideP != 0) ? 1 : 0;
-    gp.q_batched = (g.batch > 1 && g.strideQ != 0) ? 1 : 0;
+    gp.kb_per_fold = kfold > 1 ? (g.K + kBK - 1) / kBK : 0;
+    const int pairs = kfold > 1 ? kfold : g.batch;  // extent of the operands' batch dimension
+    gp.p_batched = (pairs > 1 && g.strideP != 0) ? 1 : 0;
+    gp.q_batched = (pairs > 1 && g.strideQ != 0) ? 1 : 0;
     gp.C = g.C; gp.ldc = g.ldc; gp.strideC = g.strideC;
     gp.out_mode = g.out_mode;
     gp.accumulate = g.accumulate;
@@ -631,7 +643,7 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     // ---- tensor maps (innermost dimension first)
     CUtensorMap tp, tq;
     {
-        const uint64_t nb = gp.p_batched ? (uint64_t)g.batch : 1;
+        const uint64_t nb = gp.p_batched ? (uint64_t)pairs : 1;
         const uint64_t bstride = gp.p_batched ? (uint64_t)g.strideP * 4 : (uint64_t)g.ldp * 4 * (g.p_mn ? g.K : g.I);
         uint64_t dims[3], str[2];
         uint32_t box[3];
@@ -643,7 +655,7 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
         if (rc != CB_OK) return rc;
     }
     {
-        const uint64_t nb = gp.q_batched ? (uint64_t)g.batch : 1;
+        const uint64_t nb = gp.q_batched ? (uint64_t)pairs : 1;
         const uint64_t bstride = gp.q_batched ? (uint64_t)g.strideQ * 4 : (uint64_t)g.ldq * 4 * (g.q_mn ? g.K : g.J);
         uint64_t dims[3], str[2];
         uint32_t box[3];

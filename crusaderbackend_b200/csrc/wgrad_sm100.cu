@@ -270,33 +270,34 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
 
 // dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fw*OCp + oc][fh*Cp + c], summed in CTA order.
 // s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
-__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+template <int kReduceGroups>
+__global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
                                                            int OC, int OCp, int FH, int FW, int accumulate, int s2,
                                                            int IC_src) {
-    // block = 32 consecutive accumulator elements x 8 groups of partials; each thread sums its group's partials in
-    // order, the 8 group sums are added in order in shared memory: a fixed summation order (deterministic)
-    __shared__ float red[8][33];
+    // block = 32 consecutive valid accumulator rows of one column x 16 groups of partials; each thread sums its group's
+    // partials in order, the 16 group sums are added in order in shared memory: a fixed summation order (deterministic)
+    __shared__ float red[kReduceGroups][33];
     griddep_wait();
     griddep_launch();
     const long long total = (long long)rows_tot * NQ;
-    const long long i = (long long)blockIdx.x * 32 + threadIdx.x;
+    const int row_blocks = (rowsA + 31) / 32;
+    const int col = (int)blockIdx.x / row_blocks;
+    const int r = ((int)blockIdx.x - col * row_blocks) * 32 + (int)threadIdx.x;
     const int grp = threadIdx.y;
-    const int col = (int)(i / rows_tot);
-    const int r = (int)(i - (long long)col * rows_tot);
-    const bool live = i < total && r < rowsA;
+    const bool live = r < rowsA;
     float s = 0.f;
     if (live) {
-        const float* src = partial + i;  // element i of the [col][row] partial layout
+        const float* src = partial + (long long)col * rows_tot + r;  // element of the [col][row] partial layout
 #pragma unroll 4
-        for (int q = grp; q < nparts; q += 8) s += __ldg(src + q * total);
+        for (int q = grp; q < nparts; q += kReduceGroups) s += __ldg(src + q * total);
     }
     red[grp][threadIdx.x] = s;
     __syncthreads();
     if (grp != 0 || !live) return;
     float sum = 0.f;
 #pragma unroll
-    for (int g = 0; g < 8; ++g) sum += red[g][threadIdx.x];
+    for (int g = 0; g < kReduceGroups; ++g) sum += red[g][threadIdx.x];
     const int fh = r / Cp, c = r - fh * Cp;
     const int fw = col / OCp, oc = col - fw * OCp;
     if (c >= Cin || oc >= OC) return;
@@ -412,9 +413,14 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     e = launch_dep(ctx, umma_wgrad_kernel, dim3((unsigned)grid), dim3(192 + 32 * kShiftWarps), smem, tmX, tmdY, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
-    const long long total = (long long)mtiles * 128 * NQ;
-    int rgrid = (int)((total + 31) / 32);
-    e = launch_dep(ctx, wgrad_reduce_kernel, dim3((unsigned)rgrid), dim3(32, 8), 0, (const float*)p.partial, dW, grid, mtiles * 128,
+    const int rgrid = NQ * ((rowsA + 31) / 32);
+    static const int groups = [] {
+        const char* env = std::getenv("CB_WGRAD_REDUCE_GROUPS");  // development override: 8, 16 or 32
+        const int v = env ? std::atoi(env) : 16;
+        return v == 8 || v == 32 ? v : 16;
+    }();
+    auto* reduce = groups == 8 ? wgrad_reduce_kernel<8> : (groups == 32 ? wgrad_reduce_kernel<32> : wgrad_reduce_kernel<16>);
+    e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, (const float*)p.partial, dW, grid, mtiles * 128,
                    rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");

@@ -75,12 +75,20 @@ const char* cb_version(void);
  *   op(B) is K x N: transB == 0 -> B stored K x N (ldb); transB != 0 -> B stored N x K (ldb).
  *   strideA/B/C are the element distances between consecutive batch matrices (0 = shared operand).
  * Replaces seblas::sgemm (NN, batched over B.n with A shared; seblas/operations/cuGEMM.cu:1649),
- * sgemmTN (:1667), sgemmNT (:1685) and, with accumulate=1 and the batch folded by the caller,
- * sgemmNTA (:1701).
+ * sgemmTN (:1667) and sgemmNT (:1685); sgemmNTA (:1701) is cb_gemm_batch_reduce.
  */
 int cb_gemm(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
             int ldb, float* C, int ldc, int batch, long long strideA, long long strideB, long long strideC,
             int accumulate);
+
+/*
+ * C (+)= sum over b = 0..count-1 of op(A[b]) * op(B[b]): cb_gemm's operand conventions, one M x N result. Replaces
+ * seblas::sgemmNTA (seblas/operations/cuGEMM.cu:1701-1714 with its kernels :1370-1640: C += A[n] * B[n]^T summed over
+ * A->dims.n) with transA = 0, transB = 1, accumulate = 1. On the tensor-core paths the batch is folded into the
+ * contraction: ONE launch whose k-blocks walk the pairs.
+ */
+int cb_gemm_batch_reduce(cb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A, int lda, const float* B,
+                         int ldb, float* C, int ldc, int count, long long strideA, long long strideB, int accumulate);
 
 /* Measured ceiling of the TF32 tensor pipe on this GPU: runs, on every SM, a loop that only issues
  * tcgen05.mma.kind::tf32 (M = 128, N = n, K = 8) on operands resident in shared memory — no global traffic, no

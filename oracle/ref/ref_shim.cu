@@ -42,6 +42,17 @@ int ref_gemm(int form, float* A, float* B, float* C, int M, int N, int K, int ba
     });
 }
 
+// sgemmNTA: C += sum over n of A[n] * B[n]^T (A batch x M x K, B batch x N x K, C M x N)
+int ref_gemm_nta(float* A, float* B, float* C, int M, int N, int K, int batch) {
+    return guarded([&] {
+        Tensor* a = view(A, batch, 1, M, K);
+        Tensor* b = view(B, batch, 1, N, K);
+        Tensor* c = view(C, 1, 1, M, N);
+        sgemmNTA(a, b, c);
+        drop(a); drop(b); drop(c);
+    });
+}
+
 int ref_conv(float* W, float* X, float* Y, float* bias, int N, int IC, int IH, int IW, int OC, int FH, int FW, int sH,
              int sW, int pH, int pW) {
     return guarded([&] {

@@ -27,6 +27,9 @@ CASES = {
     "gemm_nt_f4_m96": dict(op="gemm", form=2, M=96, N=80, K=72, batch=1),
     "gemm_nt_scalar_m150": dict(op="gemm", form=2, M=150, N=37, K=29, batch=1),
     "gemm_nt_f4_m256": dict(op="gemm", form=2, M=256, N=64, K=64, batch=1),  # float4 NT kernel, M > 128
+    # sgemmNTA: C += sum_n A[n] B[n]^T; M <= 128 (its float4 kernel shares the NT kernel's row-block defect)
+    "gemm_nta_f4": dict(op="gemm_nta", M=96, N=80, K=72, batch=3),
+    "gemm_nta_scalar": dict(op="gemm_nta", M=50, N=37, K=29, batch=2),
     "conv_s1_bias": dict(op="conv", N=2, IC=5, IH=9, IW=9, OC=7, F=3, s=1, p=1, bias=True),
     "conv_s2": dict(op="conv", N=2, IC=5, IH=10, IW=10, OC=7, F=3, s=2, p=1, bias=False),
     "conv_1x1": dict(op="conv", N=3, IC=6, IH=8, IW=8, OC=4, F=1, s=1, p=0, bias=False),
@@ -48,6 +51,10 @@ def inputs(name: str, c: dict) -> dict:
         A = orc.uniform_pm1((K, M) if c["form"] == 1 else (M, K), name, "A")
         B = orc.uniform_pm1((N, K) if c["form"] == 2 else (b, K, N), name, "B")
         return dict(A=A, B=B)
+    if c["op"] == "gemm_nta":
+        M, N, K, b = c["M"], c["N"], c["K"], c["batch"]
+        return dict(A=orc.uniform_pm1((b, M, K), name, "A"), B=orc.uniform_pm1((b, N, K), name, "B"),
+                    C0=orc.uniform_pm1((M, N), name, "C0"))
     if c["op"] == "conv":
         OH, OW = orc.conv_out_hw(c["IH"], c["IW"], c["F"], c["F"], c["s"], c["s"], c["p"], c["p"])
         return dict(W=orc.he_normal_filter(c["OC"], c["IC"], c["F"], c["F"], name),
@@ -99,6 +106,10 @@ def main(out_dir: str) -> None:
             A, B = d(x["A"]), d(x["B"])
             Cc = torch.zeros((c["batch"], c["M"], c["N"]), device=dev)
             ok(lib.ref_gemm(c["form"], p(A), p(B), p(Cc), c["M"], c["N"], c["K"], c["batch"]), name)
+            out[name + "/C"] = Cc.cpu().numpy()
+        elif c["op"] == "gemm_nta":
+            A, B, Cc = d(x["A"]), d(x["B"]), d(x["C0"])
+            ok(lib.ref_gemm_nta(p(A), p(B), p(Cc), c["M"], c["N"], c["K"], c["batch"]), name)
             out[name + "/C"] = Cc.cpu().numpy()
         elif c["op"] == "conv":
             W, X, dY, bias = d(x["W"]), d(x["X"]), d(x["dY"]), d(x["bias"])

@@ -239,3 +239,40 @@ def test_golden_reference_gemm_cases(torch_cuda, ctxs, golden):
         else:
             ctxs["3xtf32"].sgemm(A, B, out)
         assert orc.max_err_norm(out.cpu().numpy(), golden[name + "/C"]) <= 2e-5, name
+
+
+@pytest.mark.parametrize("math", ["tf32", "3xtf32", "fp32"])
+@pytest.mark.parametrize("n,M,N,K", [(3, 96, 80, 72), (2, 50, 37, 29), (128, 10, 64, 64), (16, 64, 576, 40), (5, 130, 300, 100)])
+def test_sgemm_nta_batch_folded_into_k(torch_cuda, ctxs, math, n, M, N, K):
+    """seblas::sgemmNTA (seblas/operations/cuGEMM.cu:1701): C += sum over n of A[n] B[n]^T, against the fp64 oracle;
+    on the tensor-core paths the whole batch is ONE launch (the k-blocks walk the samples; K need not be a multiple of
+    the 32-element k-block: the tail of every sample is zero-filled)."""
+    torch = torch_cuda
+    A = orc.uniform_pm1((n, M, K), "nta", n, M, "A")
+    B = orc.uniform_pm1((n, N, K), "nta", n, N, "B")
+    C0 = orc.uniform_pm1((M, N), "nta", n, "C0")
+    want = C0.astype(np.float64)
+    for b in range(n):
+        want = want + orc.gemm_f64(A[b], B[b], False, True)
+    ctx = ctxs[math]
+    dA, dB, dC = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(C0).cuda()
+    l0 = ctx.launches
+    ctx.sgemmNTA(dA, dB, dC)
+    launches = ctx.launches - l0
+    ctx.synchronize()
+    assert orc.max_err_norm(dC.cpu().numpy(), want) <= TOL[math]
+    if math != "fp32" and K % 4 == 0:
+        assert ctx.last_kernel.startswith("umma") and launches <= 2   # the GEMM, plus a clear only for split-K outputs
+
+
+def test_golden_reference_sgemm_nta(torch_cuda, ctxs, golden):
+    """Same seeded inputs as the recorded runs of the reference's sgemmNTA kernels."""
+    from tests.golden.make_golden import CASES, inputs
+    torch = torch_cuda
+    for name, c in CASES.items():
+        if c["op"] != "gemm_nta":
+            continue
+        x = inputs(name, c)
+        A, B, Cc = (torch.from_numpy(x[k]).cuda() for k in ("A", "B", "C0"))
+        ctxs["3xtf32"].sgemmNTA(A, B, Cc)
+        assert orc.max_err_norm(Cc.cpu().numpy(), golden[name + "/C"]) <= 2e-5, name

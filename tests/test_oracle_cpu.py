@@ -142,6 +142,17 @@ def test_golden_gemm(golden, name):
     assert orc.max_err_norm(golden[name + "/C"], _gemm_oracle(c, inputs(name, c))) < F32_TOL
 
 
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "gemm_nta"])
+def test_golden_gemm_nta(golden, name):
+    """seblas::sgemmNTA accumulates the per-sample products A[n] B[n]^T onto C (seblas/operations/cuGEMM.cu:1701)."""
+    c = CASES[name]
+    x = inputs(name, c)
+    want = x["C0"].astype(np.float64)
+    for b in range(c["batch"]):
+        want = want + orc.gemm_f64(x["A"][b], x["B"][b], False, True)
+    assert orc.max_err_norm(golden[name + "/C"], want) < F32_TOL
+
+
 def test_golden_gemm_nt_float4_defect(golden):
     """The reference's float4 NT kernel is only right for its first 128 rows (its main-loop prefetch drops the
     row-block offset, seblas/operations/cuGEMM.cu:1322-1324): rows < 128 pin the oracle, rows >= 128 are known-bad."""
