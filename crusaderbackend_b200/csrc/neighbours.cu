@@ -215,46 +215,74 @@ __device__ __forceinline__ float4 bn_group_sum(float4 v, float4 (*red)[16]) {
     return t;
 }
 
-template <int SPT>
+// Sums, over the G batch groups of a block, of Q float4 quantities per position vector; every thread returns the totals
+// of its position. The G x (Q float4) values go through shared memory once: thread (x, g) with g < 4 Q adds component
+// g & 3 of quantity g >> 2 over the groups in group order (a fixed order: deterministic), and everyone reads the
+// totals back. red: Q * 1024 floats, tot: Q * (1024 / G) floats.
+template <int Q, int G>
+__device__ __forceinline__ void bn_block_sums(float4 (&v)[Q], float* red, float* tot) {
+    constexpr int W = (256 / G) * 4;  // floats per group row: the block's positions
+    static_assert(G >= 4 * Q, "one summing thread per (quantity, component)");
+    const int x = threadIdx.x, g = threadIdx.y;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) *reinterpret_cast<float4*>(red + (q * G + g) * W + x * 4) = v[q];
+    __syncthreads();
+    if (g < 4 * Q) {
+        const float* src = red + (g >> 2) * G * W + x * 4 + (g & 3);
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < G; ++k) t += src[k * W];
+        tot[(g >> 2) * W + x * 4 + (g & 3)] = t;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < Q; ++q) v[q] = *reinterpret_cast<const float4*>(tot + q * W + x * 4);
+}
+
+// Block = 256 / G float4 position vectors x G batch groups (G = 16, 32 or 64: more groups for small maps, so that the
+// grid still covers the GPU); thread (x, g) keeps samples n = g, g + G, ... (SPT of them) in registers.
+template <int SPT, int G>
 __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict__ X, const float* __restrict__ beta,
                                                          const float* __restrict__ gamma, float* __restrict__ mean,
                                                          float* __restrict__ var, float* __restrict__ Y,
                                                          float* __restrict__ xhat, const float* __restrict__ res, int N,
                                                          long long P, int relu) {
+    constexpr int PB = 256 / G;
+    __shared__ __align__(16) float red[1024];
+    __shared__ __align__(16) float tot[PB * 4];
     griddep_wait();
     griddep_launch();
-    __shared__ float4 red[16][16];
-    const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
+    const long long p = ((long long)blockIdx.x * PB + threadIdx.x) * 4;
     const bool live = p < P;
     const int g = threadIdx.y;
     float4 x[SPT];
-    float4 s = f4_zero();
+    float4 s[1] = {f4_zero()};
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        const int n = g + 16 * i;
+        const int n = g + G * i;
         x[i] = (live && n < N) ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
-        s = f4_add(s, x[i]);
+        s[0] = f4_add(s[0], x[i]);
     }
     const float invN = 1.0f / (float)N;
-    float4 m = bn_group_sum(s, red);
-    m = make_float4(m.x * invN, m.y * invN, m.z * invN, m.w * invN);
-    float4 q = f4_zero();
+    bn_block_sums<1, G>(s, red, tot);
+    const float4 m = make_float4(s[0].x * invN, s[0].y * invN, s[0].z * invN, s[0].w * invN);
+    float4 q[1] = {f4_zero()};
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        if (g + 16 * i < N) {
+        if (g + G * i < N) {
             const float a = x[i].x - m.x, b = x[i].y - m.y, c = x[i].z - m.z, d = x[i].w - m.w;
-            q = f4_add(q, make_float4(a * a, b * b, c * c, d * d));
+            q[0] = f4_add(q[0], make_float4(a * a, b * b, c * c, d * d));
         }
     }
-    float4 v = bn_group_sum(q, red);
-    v = make_float4(v.x * invN, v.y * invN, v.z * invN, v.w * invN);
+    bn_block_sums<1, G>(q, red, tot);
+    const float4 v = make_float4(q[0].x * invN, q[0].y * invN, q[0].z * invN, q[0].w * invN);
     if (!live) return;
     const float4 inv = make_float4(1.0f / sqrtf(v.x + 1e-8f), 1.0f / sqrtf(v.y + 1e-8f), 1.0f / sqrtf(v.z + 1e-8f),
                                    1.0f / sqrtf(v.w + 1e-8f));
     const float4 ga = *reinterpret_cast<const float4*>(gamma + p), be = *reinterpret_cast<const float4*>(beta + p);
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        const int n = g + 16 * i;
+        const int n = g + G * i;
         if (n < N) {
             const float4 h = make_float4((x[i].x - m.x) * inv.x, (x[i].y - m.y) * inv.y, (x[i].z - m.z) * inv.z,
                                          (x[i].w - m.w) * inv.w);
@@ -273,23 +301,25 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
 
 // Data gradient (statistics recomputed from X as seblas::batchNormGrad does) and, when dgamma / dbeta are given, the
 // parameter gradients dbeta = sum dy, dgamma = sum dy * xhat of seblas::batchNormParamGrads in the same pass.
-template <int SPT>
+template <int SPT, int G>
 __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
                                                          const float* __restrict__ X, float* __restrict__ dX,
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                          const float* __restrict__ relu_out, float* __restrict__ dres,
                                                          int dres_add, int pg_add, int N, long long P) {
+    constexpr int PB = 256 / G;
+    __shared__ __align__(16) float red[4 * 1024];
+    __shared__ __align__(16) float tot[4 * PB * 4];
     griddep_wait();
     griddep_launch();
-    __shared__ float4 red[16][16];
-    const long long p = ((long long)blockIdx.x * 16 + threadIdx.x) * 4;
+    const long long p = ((long long)blockIdx.x * PB + threadIdx.x) * 4;
     const bool live = p < P;
     const int g = threadIdx.y;
     float4 x[SPT], dy[SPT];
-    float4 s = f4_zero();
+    float4 s[1] = {f4_zero()};
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        const int n = g + 16 * i;
+        const int n = g + G * i;
         const bool on = live && n < N;
         x[i] = on ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
         dy[i] = on ? *reinterpret_cast<const float4*>(dY + (long long)n * P + p) : f4_zero();
@@ -302,28 +332,27 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
             float4* d = reinterpret_cast<float4*>(dres + (long long)n * P + p);
             *d = dres_add ? f4_add(*d, dy[i]) : dy[i];
         }
-        s = f4_add(s, x[i]);
+        s[0] = f4_add(s[0], x[i]);
     }
     const float invN = 1.0f / (float)N;
-    float4 m = bn_group_sum(s, red);
-    m = make_float4(m.x * invN, m.y * invN, m.z * invN, m.w * invN);
+    bn_block_sums<1, G>(s, red, tot);
+    const float4 m = make_float4(s[0].x * invN, s[0].y * invN, s[0].z * invN, s[0].w * invN);
     const float4 ga = live ? *reinterpret_cast<const float4*>(gamma + p) : f4_zero();
-    float4 sq = f4_zero(), sdx = f4_zero(), sd = f4_zero(), sxc = f4_zero();
+    // sums of xc^2, dy * xc (dxhat = dy * gamma is factored out below), dy and xc, in one exchange
+    float4 sums[4] = {f4_zero(), f4_zero(), f4_zero(), f4_zero()};
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        if (g + 16 * i < N) {
+        if (g + G * i < N) {
             const float4 xc = make_float4(x[i].x - m.x, x[i].y - m.y, x[i].z - m.z, x[i].w - m.w);
             x[i] = xc;  // keep the centred value
-            sq = f4_add(sq, make_float4(xc.x * xc.x, xc.y * xc.y, xc.z * xc.z, xc.w * xc.w));
-            sdx = f4_add(sdx, make_float4(dy[i].x * xc.x, dy[i].y * xc.y, dy[i].z * xc.z, dy[i].w * xc.w));
-            sd = f4_add(sd, dy[i]);
-            sxc = f4_add(sxc, xc);
+            sums[0] = f4_add(sums[0], make_float4(xc.x * xc.x, xc.y * xc.y, xc.z * xc.z, xc.w * xc.w));
+            sums[1] = f4_add(sums[1], make_float4(dy[i].x * xc.x, dy[i].y * xc.y, dy[i].z * xc.z, dy[i].w * xc.w));
+            sums[2] = f4_add(sums[2], dy[i]);
+            sums[3] = f4_add(sums[3], xc);
         }
     }
-    sq = bn_group_sum(sq, red);
-    sdx = bn_group_sum(sdx, red);   // sum dy * xc   (dxhat = dy * gamma is factored out below)
-    sd = bn_group_sum(sd, red);     // sum dy
-    sxc = bn_group_sum(sxc, red);
+    bn_block_sums<4, G>(sums, red, tot);
+    const float4 sq = sums[0], sdx = sums[1], sd = sums[2], sxc = sums[3];
     if (!live) return;
     float o_inv[4], o_dvar[4], o_dmean[4];
     const float sqv[4] = {sq.x, sq.y, sq.z, sq.w}, sdxv[4] = {sdx.x, sdx.y, sdx.z, sdx.w}, sdv[4] = {sd.x, sd.y, sd.z, sd.w},
@@ -337,7 +366,7 @@ __global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict
     }
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
-        const int n = g + 16 * i;
+        const int n = g + G * i;
         if (n < N) {
             float4 o;
             o.x = dy[i].x * gav[0] * o_inv[0] + o_dvar[0] * x[i].x * 2.0f * invN + o_dmean[0] * invN;
@@ -383,34 +412,57 @@ __global__ void __launch_bounds__(256) bn_paramgrad_par_kernel(const float* __re
     }
 }
 
-// samples per thread for the batch-parallel kernels: smallest power of two >= ceil(N / 16), 0 when N > 256
-inline int bn_spt(int N) {
-    const int need = (N + 15) / 16;
-    for (int s = 1; s <= 16; s <<= 1)
-        if (s >= need) return s;
-    return 0;
+// Eligibility of the batch-parallel kernels: non-zero when N <= 256 (16 samples per thread at 16 groups).
+inline int bn_spt(int N) { return N <= 256 ? 1 : 0; }
+
+// Batch groups per block: 32 when every group still gets two samples, else 16 (measured on the ResNet-56 step at
+// batch 128 / 64 / 16: 32 groups beat 16 and 64 on every map size once N >= 64); then the samples per thread, the
+// smallest power of two >= ceil(N / groups).
+struct BnShape { int groups, spt; unsigned grid; };
+inline BnShape bn_shape(const cb_ctx* ctx, int N, long long P) {
+    static const int forced = [] {
+        const char* e = std::getenv("CB_BN_GROUPS");  // development override: 16, 32 or 64
+        return e ? std::atoi(e) : 0;
+    }();
+    (void)ctx;
+    int G = N >= 64 ? 32 : 16;
+    if (forced == 16 || forced == 32 || forced == 64) G = forced;
+    const int need = (N + G - 1) / G;
+    int spt = 1;
+    while (spt < need) spt <<= 1;
+    const int pb = 256 / G;
+    return BnShape{G, spt, (unsigned)((P / 4 + pb - 1) / pb)};
 }
 
-template <int SPT>
+#define BN_DISPATCH(shape, KERNEL, ...)                                                                        \
+    do {                                                                                                       \
+        const dim3 blk_((unsigned)(256 / (shape).groups), (unsigned)(shape).groups);                            \
+        switch ((shape).groups * 100 + (shape).spt) {                                                          \
+            case 1601: launch_dep(ctx, KERNEL<1, 16>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 1602: launch_dep(ctx, KERNEL<2, 16>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 1604: launch_dep(ctx, KERNEL<4, 16>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 1608: launch_dep(ctx, KERNEL<8, 16>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 1616: launch_dep(ctx, KERNEL<16, 16>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;       \
+            case 3201: launch_dep(ctx, KERNEL<1, 32>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 3202: launch_dep(ctx, KERNEL<2, 32>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 3204: launch_dep(ctx, KERNEL<4, 32>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 3208: launch_dep(ctx, KERNEL<8, 32>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 6401: launch_dep(ctx, KERNEL<1, 64>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            case 6402: launch_dep(ctx, KERNEL<2, 64>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;        \
+            default: launch_dep(ctx, KERNEL<4, 64>, dim3((shape).grid), blk_, 0, __VA_ARGS__); break;          \
+        }                                                                                                      \
+    } while (0)
+
 void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
                        float* xhat, const float* res, int N, long long P, int relu) {
-    launch_dep(ctx, bn_fwd_par_kernel<SPT>, dim3((unsigned)((P / 4 + 15) / 16)), dim3(16, 16), 0, X, beta, gamma, mean, var, Y, xhat, res,
-               N, P, relu);
+    const BnShape sh = bn_shape(ctx, N, P);
+    BN_DISPATCH(sh, bn_fwd_par_kernel, X, beta, gamma, mean, var, Y, xhat, res, N, P, relu);
 }
-template <int SPT>
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                        float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
-    launch_dep(ctx, bn_bwd_par_kernel<SPT>, dim3((unsigned)((P / 4 + 15) / 16)), dim3(16, 16), 0, dY, gamma, X, dX, dgamma, dbeta,
-               relu_out, dres, dres_add, pg_add, N, P);
+    const BnShape sh = bn_shape(ctx, N, P);
+    BN_DISPATCH(sh, bn_bwd_par_kernel, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P);
 }
-#define BN_SPT_SWITCH(spt, CALL)            \
-    switch (spt) {                          \
-        case 1: CALL(1); break;             \
-        case 2: CALL(2); break;             \
-        case 4: CALL(4); break;             \
-        case 8: CALL(8); break;             \
-        default: CALL(16); break;           \
-    }
 
 // ------------------------------------------------------------------ elementwise
 enum { OP_RELU, OP_RELU_GRAD, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_ADDS, OP_SUBS, OP_MULS, OP_DIVS, OP_FILL,
@@ -761,9 +813,7 @@ int cb_bn_fwd(cb_ctx* ctx, const float* X, const float* beta, const float* gamma
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(Y) && (!xhat || aligned16(xhat));
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(beta) && aligned16(gamma) && (!mean || aligned16(mean)) && (!var || aligned16(var))) {
-#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, mean, var, Y, xhat, nullptr, N, P, 0)
-        BN_SPT_SWITCH(spt, CB_CALL)
-#undef CB_CALL
+        launch_bn_fwd_par(ctx, X, beta, gamma, mean, var, Y, xhat, nullptr, N, P, 0);
         return done(ctx, "cb_bn_fwd");
     }
     if (vec) bn_fwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(X, beta, gamma, mean, var, Y, xhat, N, P);
@@ -779,9 +829,7 @@ int cb_bn_bwd(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, 
     const bool vec = (P % 4 == 0) && aligned16(X) && aligned16(dY) && aligned16(dX);
     const int spt = bn_spt(N);
     if (vec && spt > 0 && aligned16(gamma)) {
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, nullptr, 0, 0, N, P)
-        BN_SPT_SWITCH(spt, CB_CALL)
-#undef CB_CALL
+        launch_bn_bwd_par(ctx, dY, gamma, X, dX, nullptr, nullptr, nullptr, nullptr, 0, 0, N, P);
         return done(ctx, "cb_bn_bwd");
     }
     if (vec) bn_bwd_kernel<4><<<grid_for(ctx, P / 4, 128), 128, 0, ctx->stream>>>(dY, gamma, X, dX, N, P);
@@ -814,9 +862,7 @@ static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, c
     const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
                     aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out)) && (!dres || aligned16(dres));
     if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_bwd_par<S>(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P)
-    BN_SPT_SWITCH(spt, CB_CALL)
-#undef CB_CALL
+    launch_bn_bwd_par(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P);
     return done(ctx, "cb_bn_bwd_fused");
 }
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
@@ -861,9 +907,7 @@ static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, cons
     const int spt = bn_spt(N);
     if (!((P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(Y) && aligned16(beta) && aligned16(gamma) && (!R || aligned16(R))))
         return fail(ctx, CB_EUNSUPPORTED, "cb_bn_fwd_relu: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-#define CB_CALL(S) launch_bn_fwd_par<S>(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, R, N, P, 1)
-    BN_SPT_SWITCH(spt, CB_CALL)
-#undef CB_CALL
+    launch_bn_fwd_par(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, R, N, P, 1);
     return done(ctx, "cb_bn_fwd_relu");
 }
 int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {

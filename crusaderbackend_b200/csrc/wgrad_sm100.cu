@@ -415,11 +415,11 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
     const int rgrid = NQ * ((rowsA + 31) / 32);
     static const int groups = [] {
-        const char* env = std::getenv("CB_WGRAD_REDUCE_GROUPS");  // development override: 8, 16 or 32
-        const int v = env ? std::atoi(env) : 16;
-        return v == 8 || v == 32 ? v : 16;
+        const char* env = std::getenv("CB_WGRAD_REDUCE_GROUPS");  // development override: 2, 4 or 8
+        const int v = env ? std::atoi(env) : 8;
+        return v == 2 || v == 4 ? v : 8;
     }();
-    auto* reduce = groups == 8 ? wgrad_reduce_kernel<8> : (groups == 32 ? wgrad_reduce_kernel<32> : wgrad_reduce_kernel<16>);
+    auto* reduce = groups == 2 ? wgrad_reduce_kernel<2> : (groups == 4 ? wgrad_reduce_kernel<4> : wgrad_reduce_kernel<8>);
     e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, (const float*)p.partial, dW, grid, mtiles * 128,
                    rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src);
     if (e == cudaSuccess) e = cudaGetLastError();
