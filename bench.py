@@ -460,6 +460,79 @@ def bench_reference(args):
     }), flush=True)
 
 
+# ------------------------------------------------------------------------------------------ single-kernel cases
+def run_case(args):
+    """`--case NAME`: a few launches of ONE kernel on a small, larger-than-L2-irrelevant case, for profiler captures of
+    that kernel (prints a one-line summary, not the benchmark line). NAME is conv_fwd | conv_dgrad | conv_wgrad
+    (with --shape N,IC,H,OC,F,stride), bn_fwd | bn_bwd (--shape N,C,H), momentum, head, gemm (--shape M,N,K,form)."""
+    import torch
+    from crusaderbackend_b200.api import Context
+    torch.cuda.set_device(0)
+    ctx = Context(0, math="tf32", sync=False)
+    name = args.case
+    shp = args.shape.split(",") if args.shape else []
+    reps = max(1, args.steps)
+    if name.startswith("conv_"):
+        N, IC, H, OC, F, st = (int(v) for v in (shp or ["128", "16", "32", "16", "3", "1"]))
+        p = 1 if F == 3 else 0
+        OH = (H - F + 2 * p) // st + 1
+        X = torch.randn(N, IC, H, H, device="cuda")
+        W = torch.randn(OC, IC, F, F, device="cuda") * (2.0 / (IC * F * F)) ** 0.5
+        Y = torch.empty(N, OC, OH, OH, device="cuda")
+        dY = torch.randn(N, OC, OH, OH, device="cuda")
+        dX = torch.empty_like(X)
+        dW = torch.zeros_like(W)
+        ctx.lib.cb_conv_cache_filters(ctx.h, 1)
+        fn = {"conv_fwd": lambda: ctx.conv(W, X, Y, st, st, p, p), "conv_dgrad": lambda: ctx.convDerive(W, dY, dX, st, st, p, p),
+              "conv_wgrad": lambda: ctx.convError(dY, X, dW, st, st, p, p)}[name]
+    elif name in ("bn_fwd", "bn_bwd"):
+        N, Cc, H = (int(v) for v in (shp or ["128", "16", "32"]))
+        P = Cc * H * H
+        X = torch.randn(N, P, device="cuda")
+        Y = torch.empty_like(X)
+        R = torch.randn(N, P, device="cuda")
+        dY = torch.randn(N, P, device="cuda")
+        dX, dR = torch.empty_like(X), torch.empty_like(X)
+        g, b = torch.ones(P, device="cuda"), torch.zeros(P, device="cuda")
+        dg, db = torch.empty(P, device="cuda"), torch.empty(P, device="cuda")
+        pt = lambda t: C.c_void_p(t.data_ptr())
+        if name == "bn_fwd":
+            fn = lambda: ctx._check(ctx.lib.cb_bn_fwd_add_relu(ctx.h, pt(X), pt(b), pt(g), pt(R), pt(Y), N, P))
+        else:
+            ctx._check(ctx.lib.cb_bn_fwd_add_relu(ctx.h, pt(X), pt(b), pt(g), pt(R), pt(Y), N, P))
+            fn = lambda: ctx._check(ctx.lib.cb_bn_bwd_fused_res(ctx.h, pt(dY), pt(g), pt(X), pt(dX), pt(dg), pt(db), pt(Y), pt(dR), 0, N, P))
+    elif name == "gemm":
+        M, N, K, form = (shp or ["4096", "4096", "4096", "NN"])
+        M, N, K = int(M), int(N), int(K)
+        tA, tB = FORMS[form]
+        A = torch.randn((K, M) if tA else (M, K), device="cuda")
+        B = torch.randn((N, K) if tB else (K, N), device="cuda")
+        Cc = torch.empty(M, N, device="cuda")
+        fn = lambda: ctx.gemm(A, B, Cc, transA=tA, transB=tB)
+    elif name in ("momentum", "head"):
+        from crusaderbackend_b200.train import ResNetTrainer
+        tr = ResNetTrainer(ctx, batch=128, blocks_per_stage=9, image_hw=32, classes=10)
+        tr.init_params("bench")
+        img = torch.randn(128, 3, 32, 32, device="cuda")
+        lab = torch.zeros(128, 10, device="cuda")
+        lab[:, 0] = 1
+        fn = lambda: tr.step(img, lab, 1e-4)
+        reps = 1
+    else:
+        raise SystemExit(f"unknown case {name}")
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"case": name, "shape": args.shape, "launch_us_with_host_gaps": round(e0.elapsed_time(e1) / reps * 1e3, 1),
+                      "kernel": ctx.last_kernel}), flush=True)
+
+
 # ------------------------------------------------------------------------------------------ our arm
 def bench_ours(args):
     import torch
@@ -552,7 +625,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and reference-CUDA legs (profiling runs)")
     ap.add_argument("--quick", action="store_true", help="headline and convolution table only (profiling runs)")
+    ap.add_argument("--case", default=None, help="run a few launches of one kernel instead of the benchmark (profiler captures)")
+    ap.add_argument("--shape", default=None, help="comma-separated extents of --case")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -1,6 +1,8 @@
 // C-ABI entry points: context management, error reporting and the GEMM dispatcher.
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <mutex>
 #include <cstring>
 #include <new>
 
@@ -152,6 +154,26 @@ int encode_tmap(cb_ctx* ctx, CUtensorMap* out, const void* base, int rank, const
 }  // namespace cb
 
 using namespace cb;
+
+namespace cb {
+cudaError_t raise_dynamic_smem_once(const void* kernel, int device, int smem_optin, int* max_dynamic) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> done;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = done.find({kernel, device});
+    if (it == done.end()) {
+        cudaFuncAttributes fa;
+        cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+        if (e != cudaSuccess) return e;
+        const int bound = smem_optin - (int)fa.sharedSizeBytes;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bound);
+        if (e != cudaSuccess) return e;
+        it = done.emplace(std::make_pair(kernel, device), bound).first;
+    }
+    if (max_dynamic) *max_dynamic = it->second;
+    return cudaSuccess;
+}
+}  // namespace cb
 
 extern "C" {
 

@@ -68,6 +68,15 @@ cudaError_t launch_dep(cb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return launch_dep_on(ctx->stream, ctx->pdl != 0, kernel, grid, block, smem, std::forward<Args>(args)...);
 }
 
+// Raises cudaFuncAttributeMaxDynamicSharedMemorySize of `kernel` to the most this device allows (opt-in limit minus
+// the kernel's static shared memory), once per (kernel, device) instead of on every launch; *max_dynamic receives that
+// bound. Thread-safe.
+cudaError_t raise_dynamic_smem_once(const void* kernel, int device, int smem_optin, int* max_dynamic);
+template <typename... KArgs>
+cudaError_t raise_dynamic_smem_once(void (*kernel)(KArgs...), int device, int smem_optin, int* max_dynamic) {
+    return raise_dynamic_smem_once(reinterpret_cast<const void*>(kernel), device, smem_optin, max_dynamic);
+}
+
 // CB_OK when ctx is non-null and its device is the current one.
 int enter(cb_ctx* ctx);
 // Grows one of the context's scratch blocks to at least `bytes`; growth waits for the whole device before the old

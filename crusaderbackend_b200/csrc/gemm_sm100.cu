@@ -41,6 +41,7 @@ struct GemmParams {
     int kc;                // k-blocks per accumulation chunk: the accumulator is drained to C every kc blocks
     int tmem_cols;         // allocated TMEM columns (power of two >= 2*bn)
     int p_batched, q_batched;
+    int p_wide, q_wide;    // MN-major operand whose extent is a multiple of 32: all 32-wide slices of a tile in ONE TMA box
     float* C;
     long long ldc, strideC;
     int out_mode, accumulate, atomic_out;
@@ -56,6 +57,7 @@ struct __align__(8) PipeSmem {
     uint64_t xf[kMaxStages];
     uint64_t tfull[2];
     uint64_t tempty[2];
+    uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -144,11 +146,11 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
     const uint32_t acc_stride = (uint32_t)p.tmem_cols >> 1;  // column offset of accumulator 1
 
     const int total_work = p.batch * p.tiles_i * p.tiles_j * p.splits;
+    uint32_t armed = 0, armed_parity = 0;  // producer lane: stages armed at least once / parity of their last arming
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         uint32_t s = 0, ph = 0;
-        uint32_t armed = 0, armed_parity = 0;  // per-stage: armed at least once / parity of the last arming
         bool ok = true;
         for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
             const WorkItem it = decode_work(p, w);
@@ -173,30 +175,29 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
                     armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
                     const int k0 = kk * kBK;
                     if (P_MN) {
-                        for (int bx = 0; bx < 4 * p.mi; ++bx)
-                            tma_load_3d(sP + bx * 4096u, &tmP, full, it.i0 + 32 * bx, k0, bp);
+                        if (p.p_wide) {
+                            tma_load_4d(sP, &tmP, full, 0, k0, it.i0 >> 5, bp);
+                        } else {
+                            for (int bx = 0; bx < 4 * p.mi; ++bx)
+                                tma_load_3d(sP + bx * 4096u, &tmP, full, it.i0 + 32 * bx, k0, bp);
+                        }
                     } else {
                         for (int m = 0; m < p.mi; ++m)
                             tma_load_3d(sP + m * kPTileBytes, &tmP, full, k0, it.i0 + 128 * m, bp);
                     }
                     if (Q_MN) {
-                        for (int bx = 0; bx < (p.bn >> 5); ++bx)
-                            tma_load_3d(sQ + bx * 4096u, &tmQ, full, it.j0 + 32 * bx, k0, bq);
+                        if (p.q_wide) {
+                            tma_load_4d(sQ, &tmQ, full, 0, k0, it.j0 >> 5, bq);
+                        } else {
+                            for (int bx = 0; bx < (p.bn >> 5); ++bx)
+                                tma_load_3d(sQ + bx * 4096u, &tmQ, full, it.j0 + 32 * bx, k0, bq);
+                        }
                     } else {
                         tma_load_3d(sQ, &tmQ, full, k0, it.j0, bq);
                     }
                 }
                 __syncwarp();
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
-            }
-        }
-        if (!ok && lane == 0) {
-            // an abort leaves copies in flight: give every armed stage a bounded chance to land
-            for (int st = 0; st < p.stages; ++st) {
-                if (!((armed >> st) & 1u)) continue;
-                const uint32_t par = (armed_parity >> st) & 1u;
-                for (int spin = 0; spin < 20000; ++spin)
-                    if (mbar_try_wait(smem_u32(&ps.full[st]), par)) break;
             }
         }
     } else if (warp == 1) {
@@ -388,6 +389,20 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    if (ps.abort_flag) {
+        // A bounded wait gave up somewhere in this CTA: copies armed before that may still be in flight towards its
+        // shared memory and issued MMAs may still run on its accumulators; both get a bounded chance to finish before
+        // the shared memory and TMEM are released.
+        if (warp == 0 && lane == 0) {
+            for (int st = 0; st < p.stages; ++st)
+                if ((armed >> st) & 1u) mbar_drain(smem_u32(&ps.full[st]), (armed_parity >> st) & 1u, p.status);
+        }
+        if (warp == 1 && lane == 0) {
+            tc_commit(smem_u32(&ps.drain));
+            mbar_drain(smem_u32(&ps.drain), 0, p.status);
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
@@ -536,19 +551,20 @@ int zero_output(cb_ctx* ctx, const GemmCall& g) {
 }
 
 template <bool P_MN, bool Q_MN>
-cudaError_t launch_variant(bool x3, dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& tp,
-                           const CUtensorMap& tq, const GemmParams& gp) {
+cudaError_t launch_variant(cb_ctx* ctx, bool x3, dim3 grid, size_t smem, const CUtensorMap& tp, const CUtensorMap& tq,
+                           const GemmParams& gp) {
+    int bound = 0;
     cudaError_t e;
     if (x3) {
-        e = cudaFuncSetAttribute(umma_gemm_kernel<P_MN, Q_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem);
+        e = raise_dynamic_smem_once(umma_gemm_kernel<P_MN, Q_MN, true>, ctx->device, ctx->max_smem_optin, &bound);
         if (e != cudaSuccess) return e;
-        umma_gemm_kernel<P_MN, Q_MN, true><<<grid, 64 + 32 * kEpiWarps + 128, smem, st>>>(tp, tq, gp);
+        if ((int)smem > bound) return cudaErrorInvalidValue;
+        umma_gemm_kernel<P_MN, Q_MN, true><<<grid, 64 + 32 * kEpiWarps + 128, smem, ctx->stream>>>(tp, tq, gp);
     } else {
-        e = cudaFuncSetAttribute(umma_gemm_kernel<P_MN, Q_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem);
+        e = raise_dynamic_smem_once(umma_gemm_kernel<P_MN, Q_MN, false>, ctx->device, ctx->max_smem_optin, &bound);
         if (e != cudaSuccess) return e;
-        umma_gemm_kernel<P_MN, Q_MN, false><<<grid, 64 + 32 * kEpiWarps, smem, st>>>(tp, tq, gp);
+        if ((int)smem > bound) return cudaErrorInvalidValue;
+        umma_gemm_kernel<P_MN, Q_MN, false><<<grid, 64 + 32 * kEpiWarps, smem, ctx->stream>>>(tp, tq, gp);
     }
     return cudaGetLastError();
 }
@@ -595,7 +611,9 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
             if (!ctx->deterministic && g.ep.relu == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8 &&
                 (long long)g.I * g.J * g.batch <= 65536) {
                 splits = (int)(ctx->sm_count / tiles);
-                if (splits > num_kb / 4) splits = num_kb / 4;
+                // at least four k-blocks per split, one for outputs so small that the atomic adds cost nothing
+                const int min_kb = (long long)g.I * g.J * g.batch <= 4096 ? 1 : 4;
+                if (splits > num_kb / min_kb) splits = num_kb / min_kb;
                 if (splits < 1) splits = 1;
             }
             const long long work = tiles * splits;
@@ -645,25 +663,44 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     {
         const uint64_t nb = gp.p_batched ? (uint64_t)pairs : 1;
         const uint64_t bstride = gp.p_batched ? (uint64_t)g.strideP * 4 : (uint64_t)g.ldp * 4 * (g.p_mn ? g.K : g.I);
-        uint64_t dims[3], str[2];
-        uint32_t box[3];
-        if (g.p_mn) { dims[0] = g.I; dims[1] = g.K; box[0] = 32; box[1] = kBK; }
-        else        { dims[0] = g.K; dims[1] = g.I; box[0] = kBK; box[1] = 128; }
-        dims[2] = nb; box[2] = 1;
-        str[0] = (uint64_t)g.ldp * 4; str[1] = bstride;
-        int rc = encode_tmap(ctx, &tp, g.P, 3, dims, str, box, nullptr, g.p_mn ? 129 : 128);
+        int rc;
+        gp.p_wide = (g.p_mn && (g.I & 31) == 0) ? 1 : 0;
+        if (gp.p_wide) {
+            // view the i extent as (32, I / 32): one box [slices of the tile][32 k][32 i] is the tile's MN-major layout
+            uint64_t dims[4] = {32, (uint64_t)g.K, (uint64_t)g.I / 32, nb};
+            uint64_t str[3] = {(uint64_t)g.ldp * 4, 128, bstride};
+            uint32_t box[4] = {32, (uint32_t)kBK, (uint32_t)(4 * gp.mi), 1};
+            rc = encode_tmap(ctx, &tp, g.P, 4, dims, str, box, nullptr, 129);
+        } else {
+            uint64_t dims[3], str[2];
+            uint32_t box[3];
+            if (g.p_mn) { dims[0] = g.I; dims[1] = g.K; box[0] = 32; box[1] = kBK; }
+            else        { dims[0] = g.K; dims[1] = g.I; box[0] = kBK; box[1] = 128; }
+            dims[2] = nb; box[2] = 1;
+            str[0] = (uint64_t)g.ldp * 4; str[1] = bstride;
+            rc = encode_tmap(ctx, &tp, g.P, 3, dims, str, box, nullptr, g.p_mn ? 129 : 128);
+        }
         if (rc != CB_OK) return rc;
     }
     {
         const uint64_t nb = gp.q_batched ? (uint64_t)pairs : 1;
         const uint64_t bstride = gp.q_batched ? (uint64_t)g.strideQ * 4 : (uint64_t)g.ldq * 4 * (g.q_mn ? g.K : g.J);
-        uint64_t dims[3], str[2];
-        uint32_t box[3];
-        if (g.q_mn) { dims[0] = g.J; dims[1] = g.K; box[0] = 32; box[1] = kBK; }
-        else        { dims[0] = g.K; dims[1] = g.J; box[0] = kBK; box[1] = (uint32_t)gp.bn; }
-        dims[2] = nb; box[2] = 1;
-        str[0] = (uint64_t)g.ldq * 4; str[1] = bstride;
-        int rc = encode_tmap(ctx, &tq, g.Q, 3, dims, str, box, nullptr, g.q_mn ? 129 : 128);
+        int rc;
+        gp.q_wide = (g.q_mn && (g.J & 31) == 0) ? 1 : 0;
+        if (gp.q_wide) {
+            uint64_t dims[4] = {32, (uint64_t)g.K, (uint64_t)g.J / 32, nb};
+            uint64_t str[3] = {(uint64_t)g.ldq * 4, 128, bstride};
+            uint32_t box[4] = {32, (uint32_t)kBK, (uint32_t)(gp.bn >> 5), 1};
+            rc = encode_tmap(ctx, &tq, g.Q, 4, dims, str, box, nullptr, 129);
+        } else {
+            uint64_t dims[3], str[2];
+            uint32_t box[3];
+            if (g.q_mn) { dims[0] = g.J; dims[1] = g.K; box[0] = 32; box[1] = kBK; }
+            else        { dims[0] = g.K; dims[1] = g.J; box[0] = kBK; box[1] = (uint32_t)gp.bn; }
+            dims[2] = nb; box[2] = 1;
+            str[0] = (uint64_t)g.ldq * 4; str[1] = bstride;
+            rc = encode_tmap(ctx, &tq, g.Q, 3, dims, str, box, nullptr, g.q_mn ? 129 : 128);
+        }
         if (rc != CB_OK) return rc;
     }
 
@@ -677,10 +714,10 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
     const int hi = gp.mi * kPTileBytes + gp.bn * kBK * 4;
     const size_t smem = (size_t)gp.stages * (x3 ? 2 * hi : hi) + 1024;
     cudaError_t e;
-    if (g.p_mn && g.q_mn)       e = launch_variant<true, true>(x3, dim3(grid), smem, ctx->stream, tp, tq, gp);
-    else if (g.p_mn && !g.q_mn) e = launch_variant<true, false>(x3, dim3(grid), smem, ctx->stream, tp, tq, gp);
-    else if (!g.p_mn && g.q_mn) e = launch_variant<false, true>(x3, dim3(grid), smem, ctx->stream, tp, tq, gp);
-    else                        e = launch_variant<false, false>(x3, dim3(grid), smem, ctx->stream, tp, tq, gp);
+    if (g.p_mn && g.q_mn)       e = launch_variant<true, true>(ctx, x3, dim3(grid), smem, tp, tq, gp);
+    else if (g.p_mn && !g.q_mn) e = launch_variant<true, false>(ctx, x3, dim3(grid), smem, tp, tq, gp);
+    else if (!g.p_mn && g.q_mn) e = launch_variant<false, true>(ctx, x3, dim3(grid), smem, tp, tq, gp);
+    else                        e = launch_variant<false, false>(ctx, x3, dim3(grid), smem, tp, tq, gp);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_gemm_kernel launch");
     ctx->launches += 1;
     ctx->last_kernel = x3 ? "umma_3xtf32" : "umma_tf32";

@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
 // Data gradient (statistics recomputed from X as seblas::batchNormGrad does) and, when dgamma / dbeta are given, the
 // parameter gradients dbeta = sum dy, dgamma = sum dy * xhat of seblas::batchNormParamGrads in the same pass.
 template <int SPT, int G>
-__global__ void __launch_bounds__(256) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
+__global__ void __launch_bounds__(256, SPT <= 4 ? 4 : 1) bn_bwd_par_kernel(const float* __restrict__ dY, const float* __restrict__ gamma,
                                                          const float* __restrict__ X, float* __restrict__ dX,
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                          const float* __restrict__ relu_out, float* __restrict__ dres,
@@ -712,26 +712,42 @@ __global__ void __launch_bounds__(256) head_fwd_kernel(const float* __restrict__
                                                        float* __restrict__ loss_n, int C, int HW, int M) {
     griddep_wait();
     griddep_launch();
-    extern __shared__ float sh[];  // pooled[C]
+    extern __shared__ float sh[];  // pooled[C], then logits[32]
+    float* shl = sh + C;
     const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* Xn = X + (long long)n * C * HW;
-    for (int c = warp; c < C; c += 8) {
-        float s = 0.f;
-        for (int i = lane; i < HW; i += 32) s += Xn[(long long)c * HW + i];
-        s = warp_sum(s);
-        if (lane == 0) {
-            sh[c] = s / (float)HW;
-            pooled[(long long)n * C + c] = sh[c];
+    // pooling: a warp takes four channels at a time so that their loads are in flight together; each channel is summed
+    // lane-strided, then across the lanes
+    for (int c0 = warp * 4; c0 < C; c0 += 32) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = lane; i < HW; i += 32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j < C) s[j] += Xn[(long long)(c0 + j) * HW + i];
         }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float t = warp_sum(s[j]);
+            if (lane == 0 && c0 + j < C) {
+                sh[c0 + j] = t / (float)HW;
+                pooled[(long long)n * C + c0 + j] = sh[c0 + j];
+            }
+        }
+    }
+    __syncthreads();
+    // logits: one warp per class, lanes stride the channels (coalesced weight rows), summed across the lanes
+    for (int m = warp; m < M; m += 8) {
+        float a = 0.f;
+        for (int c = lane; c < C; c += 32) a = fmaf(W[(long long)m * C + c], sh[c], a);
+        a = warp_sum(a);
+        if (lane == 0) shl[m] = a + (b ? b[m] : 0.f);
     }
     __syncthreads();
     if (warp != 0) return;
     float logit = -1e15f;
     if (lane < M) {
-        float a = b ? b[lane] : 0.f;
-        for (int c = 0; c < C; ++c) a = fmaf(W[(long long)lane * C + c], sh[c], a);
-        logit = a;
-        logits[(long long)n * M + lane] = a;
+        logit = shl[lane];
+        logits[(long long)n * M + lane] = logit;
     }
     const float mx = warp_max(logit);
     const float e = lane < M ? expf(logit - mx) : 0.f;
@@ -749,8 +765,8 @@ __global__ void __launch_bounds__(256) head_fwd_kernel(const float* __restrict__
 }
 
 // Backward. CTA n < N: dX[n][c][:] = (sum_m W[m][c] dlogits[n][m]) / HW (dense-layer data gradient and the pooling
-// gradient). CTA N: dW[m][c] += sum_n dlogits[n][m] pooled[n][c], db[m] += sum_n dlogits[n][m], and the batch's summed
-// loss, every sum in sample order (deterministic).
+// gradient). The next ceil(M C / 256) CTAs: dW[m][c] += sum_n dlogits[n][m] pooled[n][c], one output per thread. The
+// last CTA: db[m] += sum_n dlogits[n][m] and the batch's summed loss. Every sum runs in sample order (deterministic).
 __global__ void __launch_bounds__(256) head_bwd_kernel(const float* __restrict__ dlogits, const float* __restrict__ pooled,
                                                        const float* __restrict__ W, float* __restrict__ dX,
                                                        float* __restrict__ dW, float* __restrict__ db,
@@ -771,21 +787,52 @@ __global__ void __launch_bounds__(256) head_bwd_kernel(const float* __restrict__
         for (int i = threadIdx.x; i < C * HW; i += blockDim.x) out[i] = sh[i / HW];
         return;
     }
-    for (int i = threadIdx.x; i < M * C; i += blockDim.x) {
+    const int w_ctas = (M * C + 255) / 256;
+    if (n < N + w_ctas) {
+        const int i = (n - N) * 256 + (int)threadIdx.x;
+        if (i >= M * C) return;
         const int m = i / C, c = i - m * C;
         float a = 0.f;
-        for (int k = 0; k < N; ++k) a = fmaf(dlogits[(long long)k * M + m], pooled[(long long)k * C + c], a);
-        dW[i] += a;
-    }
-    if (db)
-        for (int m = threadIdx.x; m < M; m += blockDim.x) {
-            float a = 0.f;
-            for (int k = 0; k < N; ++k) a += dlogits[(long long)k * M + m];
-            db[m] += a;
+        int k = 0;
+        for (; k + 8 <= N; k += 8) {  // eight samples' loads in flight, added in sample order
+            float d[8], q[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                d[u] = dlogits[(long long)(k + u) * M + m];
+                q[u] = pooled[(long long)(k + u) * C + c];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a = fmaf(d[u], q[u], a);
         }
-    if (threadIdx.x == 0 && loss_sum) {
+        for (; k < N; ++k) a = fmaf(dlogits[(long long)k * M + m], pooled[(long long)k * C + c], a);
+        dW[i] += a;
+        return;
+    }
+    if (db && (int)threadIdx.x < M) {
+        const int m = threadIdx.x;
         float a = 0.f;
-        for (int k = 0; k < N; ++k) a += loss_n[k];
+        int k = 0;
+        for (; k + 8 <= N; k += 8) {
+            float d[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) d[u] = dlogits[(long long)(k + u) * M + m];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a += d[u];
+        }
+        for (; k < N; ++k) a += dlogits[(long long)k * M + m];
+        db[m] += a;
+    }
+    if (threadIdx.x == 32 && loss_sum) {
+        float a = 0.f;
+        int k = 0;
+        for (; k + 16 <= N; k += 16) {
+            float d[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) d[u] = loss_n[k + u];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) a += d[u];
+        }
+        for (; k < N; ++k) a += loss_n[k];
         *loss_sum = a;
     }
 }
@@ -1039,7 +1086,7 @@ int cb_head_fwd(cb_ctx* ctx, const float* X, const float* W, const float* b, con
     if (N == 0) return CB_OK;
     if (!X || !W || !labels || !pooled || !logits || !probs || !dlogits || !loss_per_sample)
         return fail(ctx, CB_EINVAL, "cb_head_fwd: null operand");
-    launch_dep(ctx, head_fwd_kernel, dim3((unsigned)N), dim3(256), (size_t)C * sizeof(float), X, W, b, labels, pooled, logits, probs,
+    launch_dep(ctx, head_fwd_kernel, dim3((unsigned)N), dim3(256), (size_t)(C + 32) * sizeof(float), X, W, b, labels, pooled, logits, probs,
                dlogits, loss_per_sample, C, HW, M);
     return done(ctx, "cb_head_fwd");
 }
@@ -1051,7 +1098,7 @@ int cb_head_bwd(cb_ctx* ctx, const float* dlogits, const float* pooled, const fl
     if (C > 8192) return fail(ctx, CB_EUNSUPPORTED, "cb_head_bwd: at most 8192 channels");
     if (N == 0) return CB_OK;
     if (!dlogits || !pooled || !W || !dX || !dW || (loss_sum && !loss_per_sample)) return fail(ctx, CB_EINVAL, "cb_head_bwd: null operand");
-    launch_dep(ctx, head_bwd_kernel, dim3((unsigned)(N + 1)), dim3(256), (size_t)C * sizeof(float), dlogits, pooled, W, dX, dW, db,
+    launch_dep(ctx, head_bwd_kernel, dim3((unsigned)(N + (M * C + 255) / 256 + 1)), dim3(256), (size_t)C * sizeof(float), dlogits, pooled, W, dX, dW, db,
                loss_per_sample, loss_sum, N, C, HW, M);
     return done(ctx, "cb_head_bwd");
 }

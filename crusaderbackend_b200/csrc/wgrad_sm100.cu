@@ -40,6 +40,7 @@ struct __align__(8) WgradSmem {
     uint64_t empty[kConvMaxStages];
     uint64_t xf[kConvMaxStages];
     uint64_t tfull;
+    uint64_t drain;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             mbar_init(smem_u32(&ws.xf[s]), 32 * kShiftWarps);
         }
         mbar_init(smem_u32(&ws.tfull), 1);
+        mbar_init(smem_u32(&ws.drain), 1);
         mbar_fence_init();
         tma_prefetch_desc(&tmX);
         tma_prefetch_desc(&tmdY);
@@ -113,6 +115,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     const uint32_t tmem_base = ws.tmem_base;
     if (threadIdx.x == 0) CB_TRACE_EVENT(p.trace, 2);
 
+    uint32_t armed = 0, armed_parity = 0;  // producer lane: stages armed at least once / parity of their last arming
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         uint32_t s = 0, ph = 0;
@@ -123,6 +126,8 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             if (lane == 0) {
                 const uint32_t full = smem_u32(&ws.full[s]);
                 mbar_expect_tx(full, (uint32_t)p.lps * (p.a_bytes + set_bytes));
+                armed |= 1u << s;
+                armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
                 for (int l = 0; l < p.lps; ++l) {
                     const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
                     // lines past the end use an image index >= N: their boxes are zero-filled and add nothing
@@ -258,6 +263,20 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     if (threadIdx.x == 64) CB_TRACE_EVENT(p.trace, 10);
     tc_fence_before();
     __syncthreads();
+    if (ws.abort_flag) {
+        // A bounded wait gave up somewhere in this CTA: copies armed before that may still be in flight towards its
+        // shared memory and issued MMAs may still run on its accumulator; both get a bounded chance to finish before
+        // the shared memory and TMEM are released.
+        if (warp == 0 && lane == 0) {
+            for (int st = 0; st < p.stages; ++st)
+                if ((armed >> st) & 1u) mbar_drain(smem_u32(&ws.full[st]), (armed_parity >> st) & 1u, p.status);
+        }
+        if (warp == 1 && lane == 0) {
+            tc_commit(smem_u32(&ws.drain));
+            mbar_drain(smem_u32(&ws.drain), 0, p.status);
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
@@ -408,8 +427,10 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         if (rc != CB_OK) return rc;
     }
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int smem_bound = 0;
+    cudaError_t e = raise_dynamic_smem_once(umma_wgrad_kernel, ctx->device, ctx->max_smem_optin, &smem_bound);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
+    if ((int)smem > smem_bound) return CB_EUNSUPPORTED;
     e = launch_dep(ctx, umma_wgrad_kernel, dim3((unsigned)grid), dim3(192 + 32 * kShiftWarps), smem, tmX, tmdY, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
