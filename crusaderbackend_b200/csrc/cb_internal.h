@@ -35,6 +35,7 @@ struct cb_ctx {
     long long filter_version = 0;  // bumped by every call that may have changed a filter's values
     void* filter_cache = nullptr;  // the cache itself (conv_sm100.cu)
     int pdl = 1;                   // launch kernels that call griddep_wait with programmatic stream serialization
+    int wgrad_grid_cap = 0;        // > 0: most CTAs a weight-gradient kernel uses (contexts that run beside another stream)
 };
 
 namespace cb {

@@ -514,6 +514,10 @@ int cbt_set_wgrad_streams(cbt_model* m, int n) {
         }
         m->side_own_status.push_back(c->d_status);
         c->d_status = m->ctx->d_status;
+        // half the SMs per weight-gradient kernel: it shares the GPU with the data-gradient chain and with the other
+        // weight-gradient streams, and fewer CTAs mean fewer partial sums to write and add (measured on the
+        // ResNet-56 step: 74 CTAs beat 148, 49 and 37 at batch 128, and tie at batch 16)
+        c->wgrad_grid_cap = m->ctx->sm_count / 2;
         m->side.push_back(c); m->side_stream.push_back(st); m->side_fork.push_back(ef); m->side_join.push_back(ej);
     }
     m->side_used.assign((size_t)n, 0);

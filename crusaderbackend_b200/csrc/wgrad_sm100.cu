@@ -404,6 +404,12 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     int grid = p.groups / min_groups;
     if (grid < 1) grid = 1;
     if (grid > ctx->sm_count) grid = ctx->sm_count;
+    static const int max_grid = [] {
+        const char* e = std::getenv("CB_WGRAD_MAXGRID");  // development override
+        return e ? std::atoi(e) : 0;
+    }();
+    if (max_grid > 0 && grid > max_grid) grid = max_grid;
+    else if (max_grid == 0 && ctx->wgrad_grid_cap > 0 && grid > ctx->wgrad_grid_cap) grid = ctx->wgrad_grid_cap;
     const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
     int rc = ensure_workspace(ctx, part_bytes);
     if (rc != CB_OK) return rc;
