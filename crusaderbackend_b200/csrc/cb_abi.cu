@@ -85,6 +85,16 @@ int ensure_workspace(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->w
 int ensure_workspace2(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->workspace2, &ctx->workspace2_bytes, bytes, 0); }
 int ensure_workspace3(cb_ctx* ctx, size_t bytes) { return grow_block(ctx, &ctx->workspace3, &ctx->workspace3_bytes, bytes, 0); }
 
+int ensure_wgrad_acc(cb_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->wgrad_acc_bytes) return CB_OK;
+    int rc = grow_block(ctx, &ctx->wgrad_acc, &ctx->wgrad_acc_bytes, bytes, bytes);
+    if (rc != CB_OK) return rc;
+    // kept all zero from here on: every call that adds into it also clears what it read
+    cudaError_t e = cudaMemset(ctx->wgrad_acc, 0, ctx->wgrad_acc_bytes);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "weight-gradient accumulator clear");
+    return CB_OK;
+}
+
 // Entry check of every context call: the context must exist and its device must be the current one (launches go to the
 // current device; scratch and tensor maps belong to the context's).
 int enter(cb_ctx* ctx) {
@@ -215,6 +225,7 @@ int cb_destroy(cb_ctx* ctx) {
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->workspace2) cudaFree(ctx->workspace2);
     if (ctx->workspace3) cudaFree(ctx->workspace3);
+    if (ctx->wgrad_acc) cudaFree(ctx->wgrad_acc);
     if (ctx->d_status) cudaFree(ctx->d_status);
     filter_cache_destroy(ctx);
     delete ctx;

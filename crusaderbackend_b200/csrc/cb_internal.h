@@ -35,6 +35,8 @@ struct cb_ctx {
     long long filter_version = 0;  // bumped by every call that may have changed a filter's values
     void* filter_cache = nullptr;  // the cache itself (conv_sm100.cu)
     int pdl = 1;                   // launch kernels that call griddep_wait with programmatic stream serialization
+    void* wgrad_acc = nullptr;     // weight-gradient accumulator [column][row], all zero between calls (wgrad_sm100.cu)
+    size_t wgrad_acc_bytes = 0;
     int wgrad_grid_cap = 0;        // > 0: most CTAs a weight-gradient kernel uses (contexts that run beside another stream)
 };
 
@@ -85,6 +87,8 @@ int enter(cb_ctx* ctx);
 int ensure_workspace(cb_ctx* ctx, size_t bytes);
 int ensure_workspace2(cb_ctx* ctx, size_t bytes);
 int ensure_workspace3(cb_ctx* ctx, size_t bytes);
+// The zero-filled accumulator of the weight-gradient kernels, at least `bytes` large (same growth rules).
+int ensure_wgrad_acc(cb_ctx* ctx, size_t bytes);
 
 // Encodes a tiled fp32 tensor map. dims/box are innermost-first; strides_bytes has rank-1 entries
 // (the innermost stride is 4 bytes). swizzle_bytes in {0, 32, 64, 128}, or 129 for

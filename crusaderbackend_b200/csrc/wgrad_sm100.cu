@@ -30,7 +30,8 @@ struct WgradParams {
     int groups;                      // ceil(total_lines / lps)
     int stages, tmem_cols;
     uint32_t line_bytes, stage_bytes, a_bytes;  // one line slot of a stage / lps of them / the A part of a line slot
-    float* partial;                  // [gridDim.x][NQ][mtiles * 128]
+    float* partial;                  // [gridDim.x][NQ][mtiles * 128]; with `atomic`: ONE such tile that every CTA adds into
+    int atomic;
     int* status;
     long long* trace;
 };
@@ -221,15 +222,20 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                 const int r = m * 128 + 32 * quarter + lane;
                 if (m * 128 + 32 * quarter >= p.rowsA) continue;  // warp-uniform: no valid row in this quarter
                 // partial[cta][col][row]: for one column the warp's 32 rows are 128 contiguous bytes
-                float* dst = p.partial + (long long)blockIdx.x * p.NQ * rows_tot + r;
+                float* dst = p.partial + (p.atomic ? 0LL : (long long)blockIdx.x * p.NQ * rows_tot) + r;
                 const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
                 for (int c = 0; c < p.NQ; c += 16) {
                     uint32_t v[16];
                     tmem_ld16(t_row + (uint32_t)c, v);
                     tmem_ld_wait();
                     if (r < p.rowsA) {
+                        if (p.atomic) {
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) dst[(long long)(c + e) * rows_tot] = __uint_as_float(v[e]);
+                            for (int e = 0; e < 16; ++e) atomicAdd(dst + (long long)(c + e) * rows_tot, __uint_as_float(v[e]));
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) dst[(long long)(c + e) * rows_tot] = __uint_as_float(v[e]);
+                        }
                     }
                 }
             }
@@ -290,10 +296,10 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
 // dW[oc][c][fh][fw] (+)= sum over CTAs of partial[cta][fw*OCp + oc][fh*Cp + c], summed in CTA order.
 // s2 != 0: the rows are (tap of the 2x2 phase convolution, phase*IC + c) and map back to the 3x3 stride-2 filter.
 template <int kReduceGroups>
-__global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+__global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float* __restrict__ partial, float* __restrict__ dW,
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
                                                            int OC, int OCp, int FH, int FW, int accumulate, int s2,
-                                                           int IC_src) {
+                                                           int IC_src, int clear) {
     // block = 32 consecutive valid accumulator rows of one column x 16 groups of partials; each thread sums its group's
     // partials in order, the 16 group sums are added in order in shared memory: a fixed summation order (deterministic)
     __shared__ float red[kReduceGroups][33];
@@ -307,9 +313,16 @@ __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(const 
     const bool live = r < rowsA;
     float s = 0.f;
     if (live) {
-        const float* src = partial + (long long)col * rows_tot + r;  // element of the [col][row] partial layout
+        float* src = partial + (long long)col * rows_tot + r;  // element of the [col][row] partial layout
+        if (clear) {  // the one accumulator tile the CTAs added into: read it and leave it zero for the next call
+            if (grp == 0) {
+                s = *src;
+                *src = 0.f;
+            }
+        } else {
 #pragma unroll 4
-        for (int q = grp; q < nparts; q += kReduceGroups) s += __ldg(src + q * total);
+            for (int q = grp; q < nparts; q += kReduceGroups) s += __ldg(src + q * total);
+        }
     }
     red[grp][threadIdx.x] = s;
     __syncthreads();
@@ -410,10 +423,23 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     }();
     if (max_grid > 0 && grid > max_grid) grid = max_grid;
     else if (max_grid == 0 && ctx->wgrad_grid_cap > 0 && grid > ctx->wgrad_grid_cap) grid = ctx->wgrad_grid_cap;
-    const size_t part_bytes = (size_t)grid * mtiles * 128 * NQ * sizeof(float);
-    int rc = ensure_workspace(ctx, part_bytes);
-    if (rc != CB_OK) return rc;
-    p.partial = static_cast<float*>(ctx->workspace);
+    // Partial sums: one tile per CTA added in a fixed order by the second kernel (deterministic contexts), or one
+    // zero-filled tile that every CTA adds into with atomics and the second kernel moves into dW and clears again.
+    static const int allow_atomic = [] {
+        const char* e = std::getenv("CB_WGRAD_ATOMIC");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    p.atomic = (!ctx->deterministic && allow_atomic) ? 1 : 0;
+    int rc;
+    if (p.atomic) {
+        rc = ensure_wgrad_acc(ctx, (size_t)mtiles * 128 * NQ * sizeof(float));
+        if (rc != CB_OK) return rc;
+        p.partial = static_cast<float*>(ctx->wgrad_acc);
+    } else {
+        rc = ensure_workspace(ctx, (size_t)grid * mtiles * 128 * NQ * sizeof(float));
+        if (rc != CB_OK) return rc;
+        p.partial = static_cast<float*>(ctx->workspace);
+    }
 
     CUtensorMap tmX, tmdY;
     {
@@ -447,8 +473,12 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         return v == 2 || v == 4 ? v : 8;
     }();
     auto* reduce = groups == 2 ? wgrad_reduce_kernel<2> : (groups == 4 ? wgrad_reduce_kernel<4> : wgrad_reduce_kernel<8>);
-    e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, (const float*)p.partial, dW, grid, mtiles * 128,
-                   rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src);
+    if (p.atomic)
+        e = launch_dep(ctx, wgrad_reduce_kernel<1>, dim3((unsigned)rgrid), dim3(32, 1), 0, p.partial, dW, 1, mtiles * 128, rowsA, NQ, Cp,
+                       Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1);
+    else
+        e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, p.partial, dW, grid, mtiles * 128,
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
     ctx->launches += 2;
