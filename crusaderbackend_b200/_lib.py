@@ -58,6 +58,10 @@ SIGNATURES = {
     "cb_bn_paramgrad": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_bwd_fused": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_fwd_relu": (_i, [_ctx, _f, _f, _f, _f, _i, _ll]),
+    "cb_bn_fwd_relu_ex": (_i, [_ctx, _f, _f, _f, _f, _i, _ll, _ll]),
+    "cb_bn_bwd_fused_ex": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _i, _ll, _ll, _ll, _i]),
+    "cb_avgpool_ex": (_i, [_ctx, _f, _f, _i, _i, _i, _i, _i, _i, _ll]),
+    "cb_avgpool_back_ex": (_i, [_ctx, _f, _f, _i, _i, _i, _i, _i, _i, _ll]),
     "cb_bn_fwd_add_relu": (_i, [_ctx, _f, _f, _f, _f, _f, _i, _ll]),
     "cb_bn_bwd_fused_res": (_i, [_ctx, _f, _f, _f, _f, _f, _f, _f, _f, _i, _i, _ll]),
     "cb_add_relu": (_i, [_ctx, _f, _f, _f, _ll]),

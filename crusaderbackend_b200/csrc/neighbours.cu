@@ -246,7 +246,8 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
                                                          const float* __restrict__ gamma, float* __restrict__ mean,
                                                          float* __restrict__ var, float* __restrict__ Y,
                                                          float* __restrict__ xhat, const float* __restrict__ res, int N,
-                                                         long long P, int relu) {
+                                                         long long P, int relu, long long xs) {
+    // xs: floats between consecutive samples of X (P when dense; larger for a channel-prefix view of a wider tensor)
     constexpr int PB = 256 / G;
     __shared__ __align__(16) float red[1024];
     __shared__ __align__(16) float tot[PB * 4];
@@ -260,7 +261,7 @@ __global__ void __launch_bounds__(256) bn_fwd_par_kernel(const float* __restrict
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
         const int n = g + G * i;
-        x[i] = (live && n < N) ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
+        x[i] = (live && n < N) ? *reinterpret_cast<const float4*>(X + (long long)n * xs + p) : f4_zero();
         s[0] = f4_add(s[0], x[i]);
     }
     const float invN = 1.0f / (float)N;
@@ -306,7 +307,9 @@ __global__ void __launch_bounds__(256, SPT <= 4 ? 4 : 1) bn_bwd_par_kernel(const
                                                          const float* __restrict__ X, float* __restrict__ dX,
                                                          float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                          const float* __restrict__ relu_out, float* __restrict__ dres,
-                                                         int dres_add, int pg_add, int N, long long P) {
+                                                         int dres_add, int pg_add, int N, long long P, long long xs,
+                                                         long long dxs, int dx_add) {
+    // xs / dxs: floats between consecutive samples of X / dX (P when dense); dx_add: dX += instead of dX =
     constexpr int PB = 256 / G;
     __shared__ __align__(16) float red[4 * 1024];
     __shared__ __align__(16) float tot[4 * PB * 4];
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(256, SPT <= 4 ? 4 : 1) bn_bwd_par_kernel(const
     for (int i = 0; i < SPT; ++i) {
         const int n = g + G * i;
         const bool on = live && n < N;
-        x[i] = on ? *reinterpret_cast<const float4*>(X + (long long)n * P + p) : f4_zero();
+        x[i] = on ? *reinterpret_cast<const float4*>(X + (long long)n * xs + p) : f4_zero();
         dy[i] = on ? *reinterpret_cast<const float4*>(dY + (long long)n * P + p) : f4_zero();
         if (relu_out && on) {  // the ReLU that followed this layer in the forward pass: dy passes where its output is > 0
             const float4 r = *reinterpret_cast<const float4*>(relu_out + (long long)n * P + p);
@@ -373,7 +376,8 @@ __global__ void __launch_bounds__(256, SPT <= 4 ? 4 : 1) bn_bwd_par_kernel(const
             o.y = dy[i].y * gav[1] * o_inv[1] + o_dvar[1] * x[i].y * 2.0f * invN + o_dmean[1] * invN;
             o.z = dy[i].z * gav[2] * o_inv[2] + o_dvar[2] * x[i].z * 2.0f * invN + o_dmean[2] * invN;
             o.w = dy[i].w * gav[3] * o_inv[3] + o_dvar[3] * x[i].w * 2.0f * invN + o_dmean[3] * invN;
-            *reinterpret_cast<float4*>(dX + (long long)n * P + p) = o;
+            float4* dst = reinterpret_cast<float4*>(dX + (long long)n * dxs + p);
+            *dst = dx_add ? f4_add(*dst, o) : o;
         }
     }
     if (g == 0 && dgamma && dbeta) {
@@ -454,14 +458,18 @@ inline BnShape bn_shape(const cb_ctx* ctx, int N, long long P) {
     } while (0)
 
 void launch_bn_fwd_par(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* mean, float* var, float* Y,
-                       float* xhat, const float* res, int N, long long P, int relu) {
+                       float* xhat, const float* res, int N, long long P, int relu, long long xs = 0) {
     const BnShape sh = bn_shape(ctx, N, P);
-    BN_DISPATCH(sh, bn_fwd_par_kernel, X, beta, gamma, mean, var, Y, xhat, res, N, P, relu);
+    if (xs == 0) xs = P;
+    BN_DISPATCH(sh, bn_fwd_par_kernel, X, beta, gamma, mean, var, Y, xhat, res, N, P, relu, xs);
 }
 void launch_bn_bwd_par(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                       float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
+                       float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P,
+                       long long xs = 0, long long dxs = 0, int dx_add = 0) {
     const BnShape sh = bn_shape(ctx, N, P);
-    BN_DISPATCH(sh, bn_bwd_par_kernel, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P);
+    if (xs == 0) xs = P;
+    if (dxs == 0) dxs = P;
+    BN_DISPATCH(sh, bn_bwd_par_kernel, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P, xs, dxs, dx_add);
 }
 
 // ------------------------------------------------------------------ elementwise
@@ -526,8 +534,9 @@ int launch_eltwise(cb_ctx* ctx, const float* a, float* b, float* out, float s, l
 
 // ------------------------------------------------------------------ pooling
 // Non-overlapping rH x rW windows; one thread per output element, consecutive threads -> consecutive ow.
+// C / ys: channels per sample and floats between consecutive samples of the pooled tensor (ys == 0: dense)
 __global__ void avgpool_kernel(const float* __restrict__ X, float* __restrict__ Y, long long total, int H, int W,
-                               int rH, int rW) {
+                               int rH, int rW, int C, long long ys) {
     const int OH = H / rH, OW = W / rW;
     const float inv = 1.0f / (float)(rH * rW);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -540,12 +549,17 @@ __global__ void avgpool_kernel(const float* __restrict__ X, float* __restrict__ 
         float s = 0.f;
         for (int a = 0; a < rH; ++a)
             for (int b = 0; b < rW; ++b) s += src[a * W + b];
-        Y[i] = s * inv;
+        long long o = i;
+        if (ys) {
+            const long long n = c / C;
+            o = n * ys + ((c - n * C) * OH + oh) * (long long)OW + ow;
+        }
+        Y[o] = s * inv;
     }
 }
 // One thread per INPUT element: every dX element of a covered window gets dY / (rH*rW), the rest zero.
 __global__ void avgpool_back_kernel(float* __restrict__ dX, const float* __restrict__ dY, long long total, int H,
-                                    int W, int rH, int rW) {
+                                    int W, int rH, int rW, int C, long long ys) {
     const int OH = H / rH, OW = W / rW;
     const float inv = 1.0f / (float)(rH * rW);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -555,7 +569,12 @@ __global__ void avgpool_back_kernel(float* __restrict__ dX, const float* __restr
         const int h = (int)(t % H);
         const long long c = t / H;
         const int oh = h / rH, ow = w / rW;
-        dX[i] = (oh < OH && ow < OW) ? dY[(c * OH + oh) * OW + ow] * inv : 0.f;
+        long long o = (c * OH + oh) * OW + ow;
+        if (ys) {
+            const long long n = c / C;
+            o = n * ys + ((c - n * C) * OH + oh) * (long long)OW + ow;
+        }
+        dX[i] = (oh < OH && ow < OW) ? dY[o] * inv : 0.f;
     }
 }
 // Global average pool: one warp per (n,c) plane.
@@ -900,7 +919,8 @@ int cb_bn_paramgrad(cb_ctx* ctx, const float* dY, const float* xhat, float* dgam
 }
 
 static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
-                             float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P) {
+                             float* dbeta, const float* relu_out, float* dres, int dres_add, int pg_add, int N, long long P,
+                             long long xs = 0, long long dxs = 0, int dx_add = 0) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: negative extent");
     if (N == 0 || P == 0) return CB_OK;
@@ -909,8 +929,16 @@ static int bn_bwd_fused_impl(cb_ctx* ctx, const float* dY, const float* gamma, c
     const bool ok = (P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(dY) && aligned16(dX) && aligned16(gamma) &&
                     aligned16(dgamma) && aligned16(dbeta) && (!relu_out || aligned16(relu_out)) && (!dres || aligned16(dres));
     if (!ok) return fail(ctx, CB_EUNSUPPORTED, "cb_bn_bwd_fused: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-    launch_bn_bwd_par(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P);
+    if ((xs && (xs < P || (xs & 3))) || (dxs && (dxs < P || (dxs & 3))))
+        return fail(ctx, CB_EINVAL, "cb_bn_bwd_fused: a batch stride must be at least P and a multiple of 4 floats");
+    launch_bn_bwd_par(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, dres, dres_add, pg_add, N, P, xs, dxs, dx_add);
     return done(ctx, "cb_bn_bwd_fused");
+}
+int cb_bn_bwd_fused_ex(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                       float* dbeta, const float* relu_out, int N, long long P, long long x_batch_stride,
+                       long long dx_batch_stride, int accumulate_dx) {
+    return bn_bwd_fused_impl(ctx, dY, gamma, X, dX, dgamma, dbeta, relu_out, nullptr, 0, 0, N, P, x_batch_stride, dx_batch_stride,
+                             accumulate_dx ? 1 : 0);
 }
 int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
                     float* dbeta, const float* relu_out, int N, long long P) {
@@ -925,7 +953,7 @@ int cb_bn_bwd_fused_res(cb_ctx* ctx, const float* dY, const float* gamma, const 
 
 extern "C" {
 static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
-                            long long P);
+                            long long P, long long xs = 0);
 }
 
 namespace cb {
@@ -946,7 +974,7 @@ int bn_fwd_group(cb_ctx* ctx, const float* X, const float* beta, const float* ga
 extern "C" {
 
 static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, const float* R, float* Y, int N,
-                            long long P) {
+                            long long P, long long xs) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     if (N < 0 || P < 0) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: negative extent");
     if (N == 0 || P == 0) return CB_OK;
@@ -954,8 +982,13 @@ static int bn_fwd_relu_impl(cb_ctx* ctx, const float* X, const float* beta, cons
     const int spt = bn_spt(N);
     if (!((P % 4 == 0) && spt > 0 && aligned16(X) && aligned16(Y) && aligned16(beta) && aligned16(gamma) && (!R || aligned16(R))))
         return fail(ctx, CB_EUNSUPPORTED, "cb_bn_fwd_relu: needs N <= 256, P % 4 == 0 and 16-byte aligned tensors");
-    launch_bn_fwd_par(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, R, N, P, 1);
+    if (xs && (xs < P || (xs & 3))) return fail(ctx, CB_EINVAL, "cb_bn_fwd_relu: the batch stride must be at least P and a multiple of 4 floats");
+    launch_bn_fwd_par(ctx, X, beta, gamma, nullptr, nullptr, Y, nullptr, R, N, P, 1, xs);
     return done(ctx, "cb_bn_fwd_relu");
+}
+int cb_bn_fwd_relu_ex(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P,
+                      long long x_batch_stride) {
+    return bn_fwd_relu_impl(ctx, X, beta, gamma, nullptr, Y, N, P, x_batch_stride);
 }
 int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P) {
     return bn_fwd_relu_impl(ctx, X, beta, gamma, nullptr, Y, N, P);
@@ -1024,8 +1057,33 @@ int cb_avgpool(cb_ctx* ctx, const float* X, float* Y, long long NC, int H, int W
     const long long total = NC * (H / rH) * (W / rW);
     if (total == 0) return CB_OK;
     if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_avgpool: null operand");
-    avgpool_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(X, Y, total, H, W, rH, rW);
+    avgpool_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(X, Y, total, H, W, rH, rW, 1, 0);
     return done(ctx, "cb_avgpool");
+}
+
+int cb_avgpool_ex(cb_ctx* ctx, const float* X, float* Y, int N, int C, int H, int W, int rH, int rW, long long y_batch_stride) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (N < 0 || C < 1 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool_ex: bad extent");
+    const long long total = (long long)N * C * (H / rH) * (W / rW);
+    if (total == 0) return CB_OK;
+    if (!X || !Y) return fail(ctx, CB_EINVAL, "cb_avgpool_ex: null operand");
+    if (y_batch_stride && y_batch_stride < (long long)C * (H / rH) * (W / rW))
+        return fail(ctx, CB_EINVAL, "cb_avgpool_ex: batch stride smaller than one pooled sample");
+    avgpool_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(X, Y, total, H, W, rH, rW, C, y_batch_stride);
+    return done(ctx, "cb_avgpool_ex");
+}
+
+int cb_avgpool_back_ex(cb_ctx* ctx, float* dX, const float* dY, int N, int C, int H, int W, int rH, int rW,
+                       long long dy_batch_stride) {
+    if (int rc_enter = enter(ctx)) return rc_enter;
+    if (N < 0 || C < 1 || H < 0 || W < 0 || rH < 1 || rW < 1) return fail(ctx, CB_EINVAL, "cb_avgpool_back_ex: bad extent");
+    const long long total = (long long)N * C * H * W;
+    if (total == 0) return CB_OK;
+    if (!dX || !dY) return fail(ctx, CB_EINVAL, "cb_avgpool_back_ex: null operand");
+    if (dy_batch_stride && dy_batch_stride < (long long)C * (H / rH) * (W / rW))
+        return fail(ctx, CB_EINVAL, "cb_avgpool_back_ex: batch stride smaller than one pooled sample");
+    avgpool_back_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(dX, dY, total, H, W, rH, rW, C, dy_batch_stride);
+    return done(ctx, "cb_avgpool_back_ex");
 }
 
 int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H, int W, int rH, int rW) {
@@ -1034,7 +1092,7 @@ int cb_avgpool_back(cb_ctx* ctx, float* dX, const float* dY, long long NC, int H
     const long long total = NC * H * W;
     if (total == 0) return CB_OK;
     if (!dX || !dY) return fail(ctx, CB_EINVAL, "cb_avgpool_back: null operand");
-    avgpool_back_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(dX, dY, total, H, W, rH, rW);
+    avgpool_back_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(dX, dY, total, H, W, rH, rW, 1, 0);
     return done(ctx, "cb_avgpool_back");
 }
 

@@ -31,7 +31,12 @@ struct TensorBuf {
     int n = 0, c = 0, h = 0, w = 0;
     float* a = nullptr;   // value
     float* d = nullptr;   // gradient (allocated lazily for tensors that need one)
+    // A view is a channel range [c_off, c_off + c) of a wider tensor `view_of` (a DenseNet block buffer): it shares that
+    // tensor's memory, so its samples are the parent's sample size apart.
+    int view_of = -1, c_off = 0;
+    long long bstride = 0;  // floats between consecutive samples; 0 = dense (c * h * w)
     long long size() const { return (long long)n * c * h * w; }
+    long long sample() const { return (long long)c * h * w; }
 };
 
 struct Op {
@@ -161,13 +166,24 @@ long long add_param(cbt_model* m, long long size, int is_weight, int kind, int d
     return e.offset;
 }
 
-int add_conv(cbt_model* m, int in, int oc, int f, int stride, int pad) {
+// channels [c_off, c_off + c) of tensor `parent` as a tensor of its own (no memory of its own)
+int new_view(cbt_model* m, int parent, int c_off, int c) {
+    const TensorBuf p = m->t[parent];
+    const int id = new_tensor(m, p.n, c, p.h, p.w);
+    m->t[id].view_of = parent;
+    m->t[id].c_off = c_off;
+    m->t[id].bstride = p.sample();
+    return id;
+}
+
+// out >= 0: the result goes into that (view) tensor instead of a new one
+int add_conv(cbt_model* m, int in, int oc, int f, int stride, int pad, int out = -1) {
     const TensorBuf& x = m->t[in];
     const int oh = (x.h - f + 2 * pad) / stride + 1, ow = (x.w - f + 2 * pad) / stride + 1;
     Op o{};
     o.kind = OP_CONV; o.in0 = in; o.oc = oc; o.f = f; o.stride = stride; o.pad = pad;
     o.w_off = add_param(m, (long long)oc * x.c * f * f, 1, 0, oc, x.c, f, f);
-    o.out = new_tensor(m, x.n, oc, oh, ow);
+    o.out = out >= 0 ? out : new_tensor(m, x.n, oc, oh, ow);
     m->ops.push_back(o);
     return o.out;
 }
@@ -249,11 +265,11 @@ int add_concat(cbt_model* m, int a, int b) {
     return o.out;
 }
 
-int add_avgpool2(cbt_model* m, int in) {
+int add_avgpool2(cbt_model* m, int in, int out = -1) {
     const TensorBuf x = m->t[in];
     Op o{};
     o.kind = OP_AVGPOOL; o.in0 = in;
-    o.out = new_tensor(m, x.n, x.c, x.h / 2, x.w / 2);
+    o.out = out >= 0 ? out : new_tensor(m, x.n, x.c, x.h / 2, x.w / 2);
     m->ops.push_back(o);
     return o.out;
 }
@@ -319,28 +335,37 @@ int finalize_model(cbt_model* m, int x, int classes) {
     m->param_count = (m->param_count + 3) & ~3LL;
     // in backward order the LAST forward consumer of a tensor writes its gradient first; every earlier consumer must
     // accumulate onto it
+    // (views count as their parent: the gradient memory is shared, and the consumer of the widest view comes last in
+    // the forward pass, so the first write in backward order covers every channel the later ones add to)
+    auto root = [&](int id) { return m->t[id].view_of >= 0 ? m->t[id].view_of : id; };
     std::vector<int> seen(m->t.size(), 0);
     for (int i = (int)m->ops.size() - 1; i >= 0; --i) {
         Op& o = m->ops[i];
         if (o.in0 >= 0) {
-            o.in0_grad_accumulate = seen[o.in0] > 0;
-            seen[o.in0]++;
+            o.in0_grad_accumulate = seen[root(o.in0)] > 0;
+            seen[root(o.in0)]++;
         }
         if (o.in1 >= 0) {
-            o.in1_grad_accumulate = seen[o.in1] > 0;
-            seen[o.in1]++;
+            o.in1_grad_accumulate = seen[root(o.in1)] > 0;
+            seen[root(o.in1)]++;
         }
     }
     long long biggest = 0;
     for (size_t i = 0; i < m->t.size(); ++i) {
         TensorBuf& b = m->t[i];
         int rc = CB_OK;
-        if ((int)i != m->input) {  // the network input is read straight from the caller's batch buffer
+        if ((int)i != m->input && b.view_of < 0) {  // the network input is read straight from the caller's batch buffer
             rc = dev_alloc(m, &b.a, b.size());
             if (rc == CB_OK) rc = dev_alloc(m, &b.d, b.size());
         }
         if (rc != CB_OK) return rc;
         if (b.size() > biggest) biggest = b.size();
+    }
+    for (TensorBuf& b : m->t) {
+        if (b.view_of < 0) continue;
+        const TensorBuf& par = m->t[(size_t)b.view_of];
+        b.a = par.a + (long long)b.c_off * b.h * b.w;
+        b.d = par.d + (long long)b.c_off * b.h * b.w;
     }
     m->scratch_elems = biggest;
     int rc = dev_alloc(m, &m->scratch, biggest);
@@ -471,16 +496,27 @@ int cbt_densenet_create(cbt_model** out, cb_ctx* ctx, int batch, int growth, int
     cb_conv_cache_filters(ctx, 1);
     int x = new_tensor(m, batch, 3, image_hw, image_hw);
     m->input = x;
-    x = add_conv(m, x, 2 * growth, 3, 1, 1);
+    // Every dense block is ONE buffer of all the channels it will ever hold; each layer reads the channel prefix that
+    // exists so far (a view) and its 3x3 convolution writes the next `growth` channels in place, so the concatenation
+    // [x ; y] the reference performs with a copy per layer (ChannelConcatenater over seblas::concat,
+    // seblas/operations/cuConcat.cu:9-60) costs nothing here. The producer of a block's first channels (the stem, or
+    // the pooling of the transition before it) writes into the buffer directly as well.
+    int ch = 2 * growth, hw = image_hw;
+    int block_buf = new_tensor(m, batch, ch + layers * growth, hw, hw);
+    x = add_conv(m, x, ch, 3, 1, 1, new_view(m, block_buf, 0, ch));
     for (int block = 0; block < 3; ++block) {
         for (int l = 0; l < layers; ++l) {
             int y = add_conv(m, add_bn_relu(m, x), 4 * growth, 1, 1, 0);
-            y = add_conv(m, add_bn_relu(m, y), growth, 3, 1, 1);
-            x = add_concat(m, x, y);
+            add_conv(m, add_bn_relu(m, y), growth, 3, 1, 1, new_view(m, block_buf, ch, growth));
+            ch += growth;
+            x = new_view(m, block_buf, 0, ch);  // for the last layer: the whole buffer
         }
         if (block < 2) {
-            const int ch = m->t[x].c;
-            x = add_avgpool2(m, add_conv(m, add_bn_relu(m, x), ch / 2, 1, 1, 0));
+            const int t = add_conv(m, add_bn_relu(m, x), ch / 2, 1, 1, 0);
+            ch /= 2;
+            hw /= 2;
+            block_buf = new_tensor(m, batch, ch + layers * growth, hw, hw);
+            x = add_avgpool2(m, t, new_view(m, block_buf, 0, ch));
         }
     }
     x = add_bn_relu(m, x);
@@ -716,6 +752,14 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
         TensorBuf& y = m->t[o.out];
         switch (o.kind) {
             case OP_CONV:
+                if (x.bstride || y.bstride) {
+                    cb_epilogue ep{};
+                    ep.x_batch_stride = x.bstride;
+                    ep.y_batch_stride = y.bstride;
+                    CBT_TRY(cb_conv_fwd_ex(ctx, m->P + o.w_off, x.a, y.a, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride, o.stride,
+                                           o.pad, o.pad, &ep));
+                    break;
+                }
                 CBT_TRY(cb_conv_fwd(ctx, m->P + o.w_off, x.a, y.a, nullptr, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
                                     o.stride, o.pad, o.pad, 0));
                 break;
@@ -741,8 +785,13 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                     break;
                 }
                 if (o.relu) {
-                    CBT_TRY(cb_bn_fwd_relu(ctx, x.a, m->P + o.b_off, m->P + o.w_off, y.a, x.n, (long long)x.c * x.h * x.w));
+                    CBT_TRY(cb_bn_fwd_relu_ex(ctx, x.a, m->P + o.b_off, m->P + o.w_off, y.a, x.n, (long long)x.c * x.h * x.w,
+                                              x.bstride));
                     break;
+                }
+                if (x.bstride) {
+                    m->err = "a BatchNorm without ReLU cannot read a view";
+                    return CB_EUNSUPPORTED;
                 }
                 CBT_TRY(cb_bn_fwd(ctx, x.a, m->P + o.b_off, m->P + o.w_off, nullptr, nullptr, y.a,
                                   o.xhat >= 0 ? m->t[o.xhat].a : nullptr, x.n, (long long)x.c * x.h * x.w));
@@ -766,7 +815,7 @@ int cbt_forward(cbt_model* m, const float* images, const float* labels) {
                 CBT_TRY(cb_concat_channels(ctx, 2, src, ch, y.a, x.n, x.h * x.w));
                 break;
             }
-            case OP_AVGPOOL: CBT_TRY(cb_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h, x.w, 2, 2)); break;
+            case OP_AVGPOOL: CBT_TRY(cb_avgpool_ex(ctx, x.a, y.a, x.n, x.c, x.h, x.w, 2, 2, y.bstride)); break;
             case OP_GAP: CBT_TRY(cb_global_avgpool(ctx, x.a, y.a, (long long)x.n * x.c, x.h * x.w)); break;
             case OP_LINEAR:
                 CBT_TRY(cb_linear_fwd(ctx, x.a, m->P + o.w_off, m->P + o.b_off, y.a, x.n, x.c * x.h * x.w, o.oc));
@@ -826,7 +875,12 @@ int cbt_backward(cbt_model* m) {
         const bool to_input = o.in0 == m->input;  // the network input needs no gradient
         // Ops whose kernel can add onto an existing gradient write x.d directly; the others go through the scratch
         // buffer followed by x.d += scratch when an earlier consumer already wrote x.d.
-        const bool native_acc = o.kind == OP_CONV || o.kind == OP_ADD;
+        const bool bn_native = o.kind == OP_BN && o.xhat < 0 && o.in1 < 0 && m->bn_groups == 1;
+        const bool native_acc = o.kind == OP_CONV || o.kind == OP_ADD || bn_native;
+        if (x.bstride && !(o.kind == OP_CONV || bn_native)) {
+            m->err = "only convolutions and fused BatchNorm-ReLU layers can read a view";
+            return CB_EUNSUPPORTED;
+        }
         float* dx = (o.in0_grad_accumulate && !native_acc) ? m->scratch : x.d;
         switch (o.kind) {
             case OP_SOFTMAX_CE: break;  // the forward already wrote softmax - labels into the logits' gradient
@@ -850,7 +904,7 @@ int cbt_backward(cbt_model* m) {
                 if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
                 break;
             }
-            case OP_AVGPOOL: CBT_TRY(cb_avgpool_back(ctx, dx, y.d, (long long)x.n * x.c, x.h, x.w, 2, 2)); break;
+            case OP_AVGPOOL: CBT_TRY(cb_avgpool_back_ex(ctx, dx, y.d, x.n, x.c, x.h, x.w, 2, 2, y.bstride)); break;
             case OP_GAP: CBT_TRY(cb_global_avgpool_back(ctx, dx, y.d, (long long)x.n * x.c, x.h * x.w)); break;
             case OP_RELU: CBT_TRY(cb_relu_grad(ctx, x.a, y.d, dx, x.size())); break;
             case OP_ADD: {
@@ -879,6 +933,10 @@ int cbt_backward(cbt_model* m) {
                 float* dbeta = m->G + (m->bn_grad_swap ? o.w_off : o.b_off);
                 const long long P = (long long)x.c * x.h * x.w;
                 if (m->bn_groups > 1) {
+                    if (x.bstride) {
+                        m->err = "BatchNorm groups are not combined with views";
+                        return CB_EUNSUPPORTED;
+                    }
                     const int ng = x.n / m->bn_groups;
                     for (int g = 0; g < m->bn_groups; ++g) {
                         const long long off = (long long)g * ng * P;
@@ -890,7 +948,9 @@ int cbt_backward(cbt_model* m) {
                     CBT_TRY(cb_bn_bwd_fused_res(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, y.a, m->t[o.in1].d,
                                                 o.in1_grad_accumulate ? 1 : 0, x.n, P));
                 } else if (o.xhat < 0) {
-                    CBT_TRY(cb_bn_bwd_fused(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, o.relu ? y.a : nullptr, x.n, P));
+                    // (dx is x.d here: this form adds onto an existing gradient itself, also through a view's stride)
+                    CBT_TRY(cb_bn_bwd_fused_ex(ctx, y.d, m->P + o.w_off, x.a, dx, dgamma, dbeta, o.relu ? y.a : nullptr, x.n, P,
+                                               x.bstride, x.bstride, o.in0_grad_accumulate ? 1 : 0));
                 } else {
                     CBT_TRY(cb_bn_paramgrad(ctx, y.d, m->t[o.xhat].a, dgamma, dbeta, x.n, P));
                     CBT_TRY(cb_bn_bwd(ctx, y.d, m->P + o.w_off, x.a, dx, x.n, P));
@@ -912,12 +972,12 @@ int cbt_backward(cbt_model* m) {
                     if (e != cudaSuccess) { m->err = cudaGetErrorString(e); return CB_ECUDA; }
                     m->side_used[s] = 1;
                 }
-                const int rc_w = cb_conv_wgrad(wc, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
-                                               o.stride, o.pad, o.pad, 1);
+                const int rc_w = cb_conv_wgrad_ex(wc, y.d, x.a, m->G + o.w_off, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
+                                                  o.stride, o.pad, o.pad, 1, y.bstride, x.bstride);
                 if (rc_w != CB_OK) { m->err = cb_last_error(wc); return rc_w; }
                 if (!to_input)
                     CBT_TRY(cb_conv_dgrad_ex(ctx, m->P + o.w_off, y.d, x.d, x.n, x.c, x.h, x.w, o.oc, o.f, o.f, o.stride,
-                                             o.stride, o.pad, o.pad, o.in0_grad_accumulate ? 1 : 0, 0, 0));
+                                             o.stride, o.pad, o.pad, o.in0_grad_accumulate ? 1 : 0, y.bstride, x.bstride));
                 break;
             }
         }

@@ -204,6 +204,24 @@ int cb_bn_bwd_fused(cb_ctx* ctx, const float* dY, const float* gamma, const floa
 /* Y = relu(batchNorm(X)) in one pass (the BatchNorm -> ReLU pair of the operand graph, seann/operands/seblas/BatchNorm.cu:14
  * followed by activate/ReLU.cu:8); same limits as cb_bn_bwd_fused. */
 int cb_bn_fwd_relu(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P);
+/*
+ * Batch-strided forms for tensors that are a channel prefix of a wider NCHW tensor (a DenseNet block buffer that later
+ * layers append their feature maps to, so that concatenation costs no copy; the reference's concat copies,
+ * seblas/operations/cuConcat.cu:9-60): the N samples of X (and of dX) are x_batch_stride (dx_batch_stride) floats
+ * apart instead of P; 0 = dense. cb_bn_fwd_relu_ex reads X strided and writes a dense Y. cb_bn_bwd_fused_ex reads X
+ * strided, writes dX strided, and with accumulate_dx adds onto what dX already holds (the gradient of the shared
+ * buffer collects contributions from every layer that read it). cb_avgpool_ex / cb_avgpool_back_ex: the pooled tensor
+ * (Y resp. dY) is the strided one. Strides are at least one sample and multiples of 4 floats.
+ */
+int cb_bn_fwd_relu_ex(cb_ctx* ctx, const float* X, const float* beta, const float* gamma, float* Y, int N, long long P,
+                      long long x_batch_stride);
+int cb_bn_bwd_fused_ex(cb_ctx* ctx, const float* dY, const float* gamma, const float* X, float* dX, float* dgamma,
+                       float* dbeta, const float* relu_out, int N, long long P, long long x_batch_stride,
+                       long long dx_batch_stride, int accumulate_dx);
+int cb_avgpool_ex(cb_ctx* ctx, const float* X, float* Y, int N, int C, int H, int W, int rH, int rW, long long y_batch_stride);
+int cb_avgpool_back_ex(cb_ctx* ctx, float* dX, const float* dY, int N, int C, int H, int W, int rH, int rW,
+                       long long dy_batch_stride);
+
 /* Y = relu(batchNorm(X) + R): the BatchNorm that ends a residual block, the shortcut add
  * (seann/operands/controlling/ShortcutEndpoint.cu:57-74) and the ReLU after it (archive/Resnet56:14-15) in one pass; and
  * the matching backward pass: dY is masked by relu_out > 0, the masked gradient is written (or, with accumulate_dR,

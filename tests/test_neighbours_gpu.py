@@ -237,3 +237,50 @@ def test_momentum_single_and_multi(torch_cuda, ctxs, golden):
         assert orc.max_err_norm(dw[i].cpu().numpy(), rw) <= 1e-6
         assert orc.max_err_norm(dm[i].cpu().numpy(), rm) <= 1e-6
         assert not dg[i].any()
+
+
+def test_strided_batchnorm_and_pooling_match_dense_forms(torch_cuda, ctxs):
+    """The batch-strided entry points (a channel prefix of a wider NCHW buffer, as a DenseNet block is laid out) give
+    bit for bit what the dense entry points give on a contiguous copy of the same values; the backward form also adds
+    onto an existing gradient."""
+    import ctypes as C
+    torch = torch_cuda
+    ctx = ctxs["fp32"]
+    lib = ctx.lib
+    N, Ct, Cv, H = 48, 20, 12, 8
+    P, HW = Cv * H * H, H * H
+    wide = torch.from_numpy(orc.normal((N, Ct, H, H), "sbn", "X")).cuda()
+    view = wide[:, :Cv]                       # strided: samples Ct*HW apart
+    dense = view.contiguous()
+    gamma = torch.from_numpy(orc.uniform_pm1((P,), "sbn", "g") + 1.5).cuda()
+    beta = torch.from_numpy(orc.uniform_pm1((P,), "sbn", "b")).cuda()
+    p = lambda t: C.c_void_p(t.data_ptr())
+    y1, y2 = torch.empty(N, P, device="cuda"), torch.empty(N, P, device="cuda")
+    ctx._check(lib.cb_bn_fwd_relu_ex(ctx.h, p(view), p(beta), p(gamma), p(y1), N, P, Ct * HW))
+    ctx._check(lib.cb_bn_fwd_relu(ctx.h, p(dense), p(beta), p(gamma), p(y2), N, P))
+    ctx.synchronize()
+    assert torch.equal(y1, y2)
+    dy = torch.from_numpy(orc.normal((N, P), "sbn", "dY")).cuda()
+    g0 = torch.from_numpy(orc.normal((N, Ct, H, H), "sbn", "G0")).cuda()
+    dwide = g0.clone()
+    dg1, db1, dg2, db2 = (torch.empty(P, device="cuda") for _ in range(4))
+    dx2 = torch.empty(N, P, device="cuda")
+    ctx._check(lib.cb_bn_bwd_fused_ex(ctx.h, p(dy), p(gamma), p(view), p(dwide), p(dg1), p(db1), p(y1), N, P, Ct * HW, Ct * HW, 1))
+    ctx._check(lib.cb_bn_bwd_fused(ctx.h, p(dy), p(gamma), p(dense), p(dx2), p(dg2), p(db2), p(y2), N, P))
+    ctx.synchronize()
+    assert torch.equal(dg1, dg2) and torch.equal(db1, db2)
+    assert torch.equal(dwide[:, :Cv], g0[:, :Cv] + dx2.view(N, Cv, H, H))
+    assert torch.equal(dwide[:, Cv:], g0[:, Cv:])          # the channels beyond the view are untouched
+    # pooling into / out of a channel prefix of a wider pooled buffer
+    X = torch.from_numpy(orc.normal((N, Cv, H, H), "sbn", "PX")).cuda()
+    pooled_wide = torch.zeros(N, Ct, H // 2, H // 2, device="cuda")
+    pooled = torch.empty(N, Cv, H // 2, H // 2, device="cuda")
+    ctx._check(lib.cb_avgpool_ex(ctx.h, p(X), p(pooled_wide), N, Cv, H, H, 2, 2, Ct * HW // 4))
+    ctx._check(lib.cb_avgpool(ctx.h, p(X), p(pooled), N * Cv, H, H, 2, 2))
+    ctx.synchronize()
+    assert torch.equal(pooled_wide[:, :Cv], pooled) and not pooled_wide[:, Cv:].any()
+    dX1, dX2 = torch.empty_like(X), torch.empty_like(X)
+    ctx._check(lib.cb_avgpool_back_ex(ctx.h, p(dX1), p(pooled_wide), N, Cv, H, H, 2, 2, Ct * HW // 4))
+    ctx._check(lib.cb_avgpool_back(ctx.h, p(dX2), p(pooled), N * Cv, H, H, 2, 2))
+    ctx.synchronize()
+    assert torch.equal(dX1, dX2)
