@@ -544,6 +544,103 @@ __global__ void upsample2_zero_kernel(const float* __restrict__ dXsub, float* __
     }
 }
 
+// Vector forms of the four re-layout kernels for 16-byte aligned tensors with W % 4 == 0: one thread moves four
+// consecutive pixels of an input row (a 16-byte access on the full-resolution side, two 8-byte accesses on the
+// half-resolution side), so every access is coalesced.
+__global__ void space_to_depth2_vec_kernel(const float* __restrict__ X, float* __restrict__ Xs, int C, int H, int W,
+                                           long long items) {
+    griddep_wait();
+    griddep_launch();
+    const int H2 = H / 2, W2 = W / 2, WQ = W / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(i % WQ);
+        long long r = i / WQ;
+        const int y = (int)(r % H);
+        r /= H;
+        const int c = (int)(r % C);
+        const long long n = r / C;
+        const float4 v = *reinterpret_cast<const float4*>(X + ((n * C + c) * H + y) * W + 4 * q);
+        const int row = y & 1;
+        float* d0 = Xs + (((n * 4 + 2 * row) * C + c) * H2 + (y >> 1)) * W2 + 2 * q;  // phase (row, 0)
+        float* d1 = d0 + (long long)C * H2 * W2;                                       // phase (row, 1)
+        *reinterpret_cast<float2*>(d0) = make_float2(v.x, v.z);
+        *reinterpret_cast<float2*>(d1) = make_float2(v.y, v.w);
+    }
+}
+__global__ void depth_to_space2_vec_kernel(const float* __restrict__ dXs, float* __restrict__ dX, int N, int C, int H, int W,
+                                           int per_group, long long items, int accumulate) {
+    griddep_wait();
+    griddep_launch();
+    const int H2 = H / 2, W2 = W / 2, WQ = W / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(i % WQ);
+        long long r = i / WQ;
+        const int y = (int)(r % H);
+        r /= H;
+        const int c = (int)(r % C);
+        const long long n = r / C;
+        float2 ph[2];
+#pragma unroll
+        for (int col = 0; col < 2; ++col) {
+            const int og = ((y & 1) * 2 + col) * C + c;
+            const int g = og / per_group, o = og - g * per_group;
+            ph[col] = *reinterpret_cast<const float2*>(dXs + ((((long long)g * N + n) * per_group + o) * H2 + (y >> 1)) * W2 + 2 * q);
+        }
+        float4* dst = reinterpret_cast<float4*>(dX + ((n * C + c) * H + y) * W + 4 * q);
+        float4 v = make_float4(ph[0].x, ph[1].x, ph[0].y, ph[1].y);
+        if (accumulate) {
+            const float4 old = *dst;
+            v = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+        }
+        *dst = v;
+    }
+}
+__global__ void subsample2_vec_kernel(const float* __restrict__ X, float* __restrict__ Xsub, long long NC, int H, int W,
+                                      long long items) {
+    griddep_wait();
+    griddep_launch();
+    const int H2 = H / 2, W2 = W / 2, WQ = W / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(i % WQ);
+        const long long r = i / WQ;
+        const int ii = (int)(r % H2);
+        const long long nc = r / H2;
+        const float4 v = *reinterpret_cast<const float4*>(X + (nc * H + 2 * ii) * W + 4 * q);
+        *reinterpret_cast<float2*>(Xsub + (nc * H2 + ii) * W2 + 2 * q) = make_float2(v.x, v.z);
+    }
+}
+__global__ void upsample2_zero_vec_kernel(const float* __restrict__ dXsub, float* __restrict__ dX, int H, int W,
+                                          long long items, int accumulate) {
+    griddep_wait();
+    griddep_launch();
+    const int H2 = H / 2, W2 = W / 2, WQ = W / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(i % WQ);
+        const long long r = i / WQ;
+        const int y = (int)(r % H);
+        const long long nc = r / H;
+        float4* dst = reinterpret_cast<float4*>(dX + (nc * H + y) * W + 4 * q);
+        if (y & 1) {
+            if (!accumulate) *dst = make_float4(0.f, 0.f, 0.f, 0.f);
+            continue;
+        }
+        const float2 a = *reinterpret_cast<const float2*>(dXsub + (nc * H2 + (y >> 1)) * W2 + 2 * q);
+        if (accumulate) {
+            const float4 old = *dst;
+            *dst = make_float4(old.x + a.x, old.y, old.z + a.y, old.w);
+        } else {
+            *dst = make_float4(a.x, 0.f, a.y, 0.f);
+        }
+    }
+}
+static bool vec_ok(const void* a, const void* b, int W) {
+    return (W & 3) == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
+}
+
 int relayout_grid(const cb_ctx* ctx, long long n) {
     long long g = (n + 255) / 256;
     const long long cap = (long long)ctx->sm_count * 16;
@@ -795,7 +892,9 @@ int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const fl
 
 int launch_space_to_depth2(cb_ctx* ctx, const float* X, float* Xs, int N, int C, int H, int W) {
     const long long n_el = (long long)N * C * H * W;
-    cudaError_t e = launch_dep(ctx, space_to_depth2_kernel, dim3((unsigned)relayout_grid(ctx, n_el)), dim3(256), 0, X, Xs, C, H, W, n_el);
+    cudaError_t e = vec_ok(X, Xs, W)
+                        ? launch_dep(ctx, space_to_depth2_vec_kernel, dim3((unsigned)relayout_grid(ctx, n_el / 4)), dim3(256), 0, X, Xs, C, H, W, n_el / 4)
+                        : launch_dep(ctx, space_to_depth2_kernel, dim3((unsigned)relayout_grid(ctx, n_el)), dim3(256), 0, X, Xs, C, H, W, n_el);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "space_to_depth2_kernel launch");
     ctx->launches += 1;
@@ -803,7 +902,10 @@ int launch_space_to_depth2(cb_ctx* ctx, const float* X, float* Xs, int N, int C,
 }
 int launch_subsample2(cb_ctx* ctx, const float* X, float* Xsub, long long NC, int H, int W) {
     const long long n_sub = NC * (H / 2) * (W / 2);
-    cudaError_t e = launch_dep(ctx, subsample2_kernel, dim3((unsigned)relayout_grid(ctx, n_sub)), dim3(256), 0, X, Xsub, NC, H, W, n_sub);
+    const long long n_items = NC * (H / 2) * (W / 4);
+    cudaError_t e = vec_ok(X, Xsub, W)
+                        ? launch_dep(ctx, subsample2_vec_kernel, dim3((unsigned)relayout_grid(ctx, n_items)), dim3(256), 0, X, Xsub, NC, H, W, n_items)
+                        : launch_dep(ctx, subsample2_kernel, dim3((unsigned)relayout_grid(ctx, n_sub)), dim3(256), 0, X, Xsub, NC, H, W, n_sub);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "subsample2_kernel launch");
     ctx->launches += 1;
@@ -982,8 +1084,12 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const C
             rc = conv_on_packed(ctx, env, q, ps, W, X /* = dY */, sub, plain, N, H2, W2, 1, 1, 0, 0, 0, 0);
             const long long n_full = (long long)N * IC * IH * IW;
             if (rc == CB_OK) {
-                launch_dep(ctx, upsample2_zero_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0, (const float*)sub,
-                           Y /* = dX */, IH, IW, n_full, ep.accumulate ? 1 : 0);
+                if (vec_ok(sub, Y, IW))
+                    launch_dep(ctx, upsample2_zero_vec_kernel, dim3((unsigned)relayout_grid(ctx, n_full / 4)), dim3(256), 0,
+                               (const float*)sub, Y /* = dX */, IH, IW, n_full / 4, ep.accumulate ? 1 : 0);
+                else
+                    launch_dep(ctx, upsample2_zero_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0, (const float*)sub,
+                               Y /* = dX */, IH, IW, n_full, ep.accumulate ? 1 : 0);
                 ctx->launches += 1;
             }
         }
@@ -1028,8 +1134,11 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const C
         if (rc != CB_OK) return rc;
     }
     const long long n_full = (long long)N * IC * IH * IW;
-    cudaError_t e = launch_dep(ctx, depth_to_space2_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0,
-                               (const float*)dXs, Y /* = dX */, N, IC, IH, IW, per_group, n_full, ep.accumulate ? 1 : 0);
+    cudaError_t e = vec_ok(dXs, Y, IW)
+                        ? launch_dep(ctx, depth_to_space2_vec_kernel, dim3((unsigned)relayout_grid(ctx, n_full / 4)), dim3(256), 0,
+                                     (const float*)dXs, Y /* = dX */, N, IC, IH, IW, per_group, n_full / 4, ep.accumulate ? 1 : 0)
+                        : launch_dep(ctx, depth_to_space2_kernel, dim3((unsigned)relayout_grid(ctx, n_full)), dim3(256), 0,
+                                     (const float*)dXs, Y /* = dX */, N, IC, IH, IW, per_group, n_full, ep.accumulate ? 1 : 0);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "depth_to_space2_kernel launch");
     ctx->launches += 1;
