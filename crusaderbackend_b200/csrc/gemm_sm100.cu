@@ -19,6 +19,8 @@
 // (exact), rounded to TF32. D = P_hi*Q_lo + P_lo*Q_hi + P_hi*Q_hi; the dropped lo*lo term is < 2^-20 |p q|.
 #include <utility>
 
+#include <cstdlib>
+
 #include "cb_internal.h"
 #include "cb_ptx.cuh"
 
@@ -606,10 +608,14 @@ int launch_umma_gemm(cb_ctx* ctx, const GemmCall& g, bool x3) {
             const long long tiles = (long long)g.batch * ((g.I + 128 * mi - 1) / (128 * mi)) *
                                     ((g.J + bn_eff - 1) / bn_eff);
             int splits = 1;
-            // split K across CTAs (atomic adds into C) only for small outputs: atomics on a large C cost more
-            // than the idle SMs they would fill
+            // split K across CTAs (atomic adds into C) only for outputs up to split_limit elements: atomics on a large C
+            // cost more than the idle SMs they would fill
+            static const long long split_limit = [] {
+                const char* e = std::getenv("CB_GEMM_SPLIT_LIMIT");  // development override
+                return e ? std::atoll(e) : 300000LL;
+            }();
             if (!ctx->deterministic && g.ep.relu == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 8 &&
-                (long long)g.I * g.J * g.batch <= 65536) {
+                (long long)g.I * g.J * g.batch <= split_limit) {
                 splits = (int)(ctx->sm_count / tiles);
                 // at least four k-blocks per split, one for outputs so small that the atomic adds cost nothing
                 const int min_kb = (long long)g.I * g.J * g.batch <= 4096 ? 1 : 4;
