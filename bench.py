@@ -585,7 +585,9 @@ def bench_ours(args):
                                                 "ms_per_step": round(weak["ms_per_step"], 4),
                                                 "global_batch": weak["global_batch"],
                                                 "replicas_identical": weak["replicas_identical"]}
-    if world == 1:
+    if rank == 0:
+        # per-kernel sections on rank 0 (the other ranks wait at the closing barrier); everything beyond the roofline
+        # of the dominant kernel only on single-GPU runs
         from crusaderbackend_b200.api import Context
         ctx = Context(local, math="tf32", sync=False)
         umma_peak = ctx.measure_umma_peak(256, False, False, 20000)
@@ -601,7 +603,7 @@ def bench_ours(args):
                                "how": "cb_measure_umma_peak: resident-operand tcgen05.mma.kind::tf32 loop, M=128 N=256 K=8, every SM",
                                "bf16_tflops_measured_cublas": peaks["bf16_tflops"], "nominal_tf32_tflops": 1100.0}
         line["conv"] = conv
-        if not args.quick:
+        if not args.quick and world == 1:
             line["gemm"] = gemm_section(torch, local, umma_peak)
             try:
                 line["densenet_bc100"] = densenet_section(torch, local)
