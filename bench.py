@@ -69,7 +69,8 @@ def profiled_traffic(key: str):
 
 
 class ClockSampler(threading.Thread):
-    """Samples nvidia-smi clocks and throttle reasons of one GPU back to back (one nvidia-smi query each, ~50 ms) while the timed region runs."""
+    """Samples SM clock and clock-event reasons of one GPU while the timed region runs: NVML queries in this process every
+    5 ms, or one nvidia-smi query (~50 ms) after the other when NVML cannot be loaded. Read-only."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -80,7 +81,32 @@ class ClockSampler(threading.Thread):
         self.samples = []
         self.stop_flag = threading.Event()
 
+    def _nvml_loop(self) -> bool:
+        """In-process NVML reads (read-only queries), one sample every 5 ms; False when NVML is not usable."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            reasons_fn(h)
+        except Exception:
+            return False
+        bits = (0x8, 0x40, 0x20, 0x4)   # hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        while not self.stop_flag.is_set():
+            try:
+                mask = int(reasons_fn(h))
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                self.samples.append([str(mhz), str(max_mhz)] + ["Active" if mask & b else "Not Active" for b in bits])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.005)
+        return True
+
     def run(self):
+        if self._nvml_loop():
+            return
         while not self.stop_flag.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
