@@ -300,36 +300,39 @@ __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float*
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
                                                            int OC, int OCp, int FH, int FW, int accumulate, int s2,
                                                            int IC_src, int clear) {
-    // block = 32 consecutive valid accumulator rows of one column x 16 groups of partials; each thread sums its group's
-    // partials in order, the 16 group sums are added in order in shared memory: a fixed summation order (deterministic)
+    // Per-CTA partials (clear == 0): block = 32 consecutive valid accumulator rows of one column x kReduceGroups groups
+    // of partials; each thread sums its group's partials in order, the group sums are added in order in shared memory:
+    // a fixed summation order (deterministic). One shared accumulator tile (clear != 0): every thread row of the block
+    // takes its own 32 rows, reads the sum and leaves zero behind for the next call.
     __shared__ float red[kReduceGroups][33];
     griddep_wait();
     griddep_launch();
     const long long total = (long long)rows_tot * NQ;
     const int row_blocks = (rowsA + 31) / 32;
-    const int col = (int)blockIdx.x / row_blocks;
-    const int r = ((int)blockIdx.x - col * row_blocks) * 32 + (int)threadIdx.x;
     const int grp = threadIdx.y;
-    const bool live = r < rowsA;
-    float s = 0.f;
-    if (live) {
-        float* src = partial + (long long)col * rows_tot + r;  // element of the [col][row] partial layout
-        if (clear) {  // the one accumulator tile the CTAs added into: read it and leave it zero for the next call
-            if (grp == 0) {
-                s = *src;
-                *src = 0.f;
-            }
-        } else {
+    const int unit = clear ? (int)blockIdx.x * kReduceGroups + grp : (int)blockIdx.x;
+    const int col = unit / row_blocks;
+    const int r = (unit - col * row_blocks) * 32 + (int)threadIdx.x;
+    const bool live = col < NQ && r < rowsA;
+    float sum = 0.f;
+    if (clear) {
+        if (!live) return;
+        float* src = partial + (long long)col * rows_tot + r;  // element of the [col][row] tile layout
+        sum = *src;
+        *src = 0.f;
+    } else {
+        float s = 0.f;
+        if (live) {
+            const float* src = partial + (long long)col * rows_tot + r;
 #pragma unroll 4
             for (int q = grp; q < nparts; q += kReduceGroups) s += __ldg(src + q * total);
         }
-    }
-    red[grp][threadIdx.x] = s;
-    __syncthreads();
-    if (grp != 0 || !live) return;
-    float sum = 0.f;
+        red[grp][threadIdx.x] = s;
+        __syncthreads();
+        if (grp != 0 || !live) return;
 #pragma unroll
-    for (int g = 0; g < kReduceGroups; ++g) sum += red[g][threadIdx.x];
+        for (int g = 0; g < kReduceGroups; ++g) sum += red[g][threadIdx.x];
+    }
     const int fh = r / Cp, c = r - fh * Cp;
     const int fw = col / OCp, oc = col - fw * OCp;
     if (c >= Cin || oc >= OC) return;
@@ -474,8 +477,8 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     }();
     auto* reduce = groups == 2 ? wgrad_reduce_kernel<2> : (groups == 4 ? wgrad_reduce_kernel<4> : wgrad_reduce_kernel<8>);
     if (p.atomic)
-        e = launch_dep(ctx, wgrad_reduce_kernel<1>, dim3((unsigned)rgrid), dim3(32, 1), 0, p.partial, dW, 1, mtiles * 128, rowsA, NQ, Cp,
-                       Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1);
+        e = launch_dep(ctx, wgrad_reduce_kernel<8>, dim3((unsigned)((rgrid + 7) / 8)), dim3(32, 8), 0, p.partial, dW, 1, mtiles * 128,
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1);
     else
         e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, p.partial, dW, grid, mtiles * 128,
                        rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0);
