@@ -3,7 +3,7 @@
 # together with oracle/ref/ref_shim.cu, into oracle/_ref/libseblas_ref.so (git-ignored). No reference source is
 # copied: the one unportable header (seio/logging/LogUtils.cuh -> <windows.h>) is skipped by predefining its
 # include guard and force-including oracle/ref/log_stub.h.
-# Usage: oracle/build_ref.sh [reference_root]   (default /root/reference)
+# Usage: oracle/build_ref.sh [reference_root]   (default: where the reference tree is mounted, see REF below)
 set -e
 REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"

@@ -10,7 +10,7 @@
 # whose FILES are symbolic links to the reference's sources — nothing is copied — and whose seblas/, seio/logging,
 # seio/data and seann/operands/cudnn entries point at compat/. The only reference files left out are
 # seann/operands/cudnn/cuConv2D.{cu,cuh} (the cuDNN-backed operand this library replaces under the same name).
-# Usage: oracle/build_relink.sh [reference_root]   (default /root/reference)
+# Usage: oracle/build_relink.sh [reference_root]   (default: where the reference tree is mounted, see REF below)
 set -e
 REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
