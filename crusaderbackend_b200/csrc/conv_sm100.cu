@@ -708,11 +708,18 @@ int plan_conv(ConvPlan& q, int smem_optin, int sm_count, const float* X, int N, 
     int best = 0;
     ConvPlan bestq{};
     bool forced_hit = false;
-    for (int ns = 1; ns <= (forced_nsplit() == 4 ? 4 : 2) && !forced_hit; ns <<= 1) {
-        if (q.OCp % (16 * ns)) break;
+    for (int ns = 1; ns <= 4 && !forced_hit; ns <<= 1) {
+        // a four-way split only when forced or when nothing narrower fits the 256 accumulator columns (very wide outputs)
+        if (ns == 4 && forced_nsplit() != 4 && best != 0) break;
+        // a split that needs extra padding channels only when no narrower split fits at all
+        if (q.OCp % (16 * ns) != 0 && best != 0) break;
         ConvPlan c = q;
         c.nsplit = ns;
-        c.OCs = q.OCp / ns;
+        // the packed filter is padded to a whole number of 16-channel groups per CTA; channels past Cout are zero rows
+        // and their outputs are dropped by the store
+        c.OCp = (q.Cout + 16 * ns - 1) / (16 * ns) * (16 * ns);
+        c.w_total_bytes = (size_t)FH * q.CG * FW * c.OCp * kRowBytes;
+        c.OCs = c.OCp / ns;
         c.NQ = FW * c.OCs;
         if (c.NQ > 256) continue;
         c.w_bytes = (size_t)FH * c.CG * c.NQ * kRowBytes;

@@ -428,8 +428,12 @@ inline BnShape bn_shape(const cb_ctx* ctx, int N, long long P) {
         const char* e = std::getenv("CB_BN_GROUPS");  // development override: 16, 32 or 64
         return e ? std::atoi(e) : 0;
     }();
-    (void)ctx;
     int G = N >= 64 ? 32 : 16;
+    static const int small64 = [] {
+        const char* e = std::getenv("CB_BN_SMALL64");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    if (small64 && G == 32 && N >= 128 && (P / 4 + 7) / 8 < ctx->sm_count) G = 64;  // maps too small to fill the GPU at 32
     if (forced == 16 || forced == 32 || forced == 64) G = forced;
     const int need = (N + G - 1) / G;
     int spt = 1;

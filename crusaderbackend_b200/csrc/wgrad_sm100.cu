@@ -299,7 +299,7 @@ template <int kReduceGroups>
 __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float* __restrict__ partial, float* __restrict__ dW,
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
                                                            int OC, int OCp, int FH, int FW, int accumulate, int s2,
-                                                           int IC_src, int clear) {
+                                                           int IC_src, int clear, int IC_total, int c_off, int oc_off) {
     // Per-CTA partials (clear == 0): block = 32 consecutive valid accumulator rows of one column x kReduceGroups groups
     // of partials; each thread sums its group's partials in order, the group sums are added in order in shared memory:
     // a fixed summation order (deterministic). One shared accumulator tile (clear != 0): every thread row of the block
@@ -338,7 +338,8 @@ __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float*
     if (c >= Cin || oc >= OC) return;
     float* dst;
     if (!s2) {
-        dst = dW + (((long long)oc * Cin + c) * FH + fh) * FW + fw;
+        // this launch may cover a block (oc_off.., c_off..) of a wider filter with IC_total input channels
+        dst = dW + (((long long)(oc_off + oc) * IC_total + c_off + c) * FH + fh) * FW + fw;
     } else {
         const int phase = c / IC_src, cc = c - phase * IC_src;
         const int sh = s2_tap(phase >> 1, fh), sw = s2_tap(phase & 1, fw);
@@ -370,7 +371,9 @@ int forced_min_groups() {
 // dW (+)= contraction over the pixels of N x Cin x IH x IW planes `X` and N x OC x IH x IW planes `dY` with taps
 // (FH, FW, pH, pW) in the same-size convention of the forward kernel. s2 / IC_src: see wgrad_reduce_kernel.
 static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int Cin, int IH, int IW, int OC, int FH,
-                      int FW, int pH, int pW, int accumulate, int s2, int IC_src, long long dy_batch, long long x_batch) {
+                      int FW, int pH, int pW, int accumulate, int s2, int IC_src, long long dy_batch, long long x_batch,
+                      int IC_total = 0, int c_off = 0, int oc_off = 0) {
+    if (IC_total == 0) IC_total = Cin;
     if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
     if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
     if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;
@@ -478,10 +481,10 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     auto* reduce = groups == 2 ? wgrad_reduce_kernel<2> : (groups == 4 ? wgrad_reduce_kernel<4> : wgrad_reduce_kernel<8>);
     if (p.atomic)
         e = launch_dep(ctx, wgrad_reduce_kernel<8>, dim3((unsigned)((rgrid + 7) / 8)), dim3(32, 8), 0, p.partial, dW, 1, mtiles * 128,
-                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1);
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1, IC_total, c_off, oc_off);
     else
         e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, p.partial, dW, grid, mtiles * 128,
-                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0);
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0, IC_total, c_off, oc_off);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
     ctx->launches += 2;
@@ -494,7 +497,34 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
     if (sH == 1 && sW == 1) {
         if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
         if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
-        return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC, dy_batch, x_batch);
+        // Filters wider than one launch covers (256 input channels, 128 output channels, 512 accumulator columns) are
+        // cut into blocks of input x output channels: each block is its own launch pair on channel slices of X and dY
+        // (same batch strides) that writes its block of dW.
+        const int OCp_all = (OC + 15) / 16 * 16;
+        int oc_max = (256 / FW) & ~15;
+        if (oc_max > 128) oc_max = 128;
+        const int oc_blocks = (OCp_all + oc_max - 1) / oc_max;
+        const int oc_step = ((OC + oc_blocks - 1) / oc_blocks + 15) & ~15;
+        const int nq = FW * (oc_blocks > 1 ? oc_step : OCp_all);
+        int c_max = ((512 / nq) * 128 / FH) & ~7;
+        if (c_max > 256) c_max = 256;
+        if (c_max < 8) return CB_EUNSUPPORTED;
+        const int c_blocks = (IC + c_max - 1) / c_max;
+        const int c_step = ((IC + c_blocks - 1) / c_blocks + 7) & ~7;
+        if (oc_blocks == 1 && c_blocks == 1)
+            return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC, dy_batch, x_batch);
+        const long long plane = (long long)IH * IW;
+        const long long xb = x_batch ? x_batch : (long long)IC * plane, yb = dy_batch ? dy_batch : (long long)OC * plane;
+        for (int o0 = 0; o0 < OC; o0 += oc_step) {
+            const int on = OC - o0 < oc_step ? OC - o0 : oc_step;
+            for (int c0 = 0; c0 < IC; c0 += c_step) {
+                const int cn = IC - c0 < c_step ? IC - c0 : c_step;
+                const int rc = wgrad_core(ctx, dY + o0 * plane, X + c0 * plane, dW, N, cn, IH, IW, on, FH, FW, pH, pW, accumulate, 0, cn,
+                                          yb, xb, IC, c0, o0);
+                if (rc != CB_OK) return rc;
+            }
+        }
+        return CB_OK;
     }
     if (sH != 2 || sW != 2 || FH != FW || pH != pW || (IH & 1) || (IW & 1)) return CB_EUNSUPPORTED;
     if (!((FH == 3 && pH == 1) || (FH == 1 && pH == 0))) return CB_EUNSUPPORTED;

@@ -96,6 +96,23 @@ def test_resnet56_layer_shapes(torch_cuda, ctxs, layer, math):
     check_three_passes(torch_cuda, ctxs[math], math, c)
 
 
+DENSENET_LAYERS = [  # (IC, H, OC, F): the widest 1x1 bottleneck / transition convolutions and a 3x3 growth layer of BC-100
+    (300, 16, 150, 1), (264, 16, 48, 1), (342, 8, 48, 1), (200, 16, 40, 3), (48, 8, 12, 3),
+]
+
+
+@pytest.mark.parametrize("math", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("layer", DENSENET_LAYERS)
+def test_densenet_layer_shapes_stay_on_the_tensor_cores(torch_cuda, ctxs, layer, math):
+    """Filters wider than one launch covers (more than 256 input or 128 output channels in the weight gradient, more
+    than 256 accumulator columns in the data gradient) are cut into channel blocks resp. split over more CTAs; all three
+    passes must come from the tensor-core kernels and match the oracle."""
+    IC, H, OC, F = layer
+    c = conv_case(("dn", layer), 4, IC, H, H, OC, F, 1, 1 if F == 3 else 0)
+    kern = check_three_passes(torch_cuda, ctxs[math], math, c, dW0=orc.normal((OC, IC, F, F), "dn", "dW0", IC))
+    assert all(k.startswith("umma") for k in kern), kern
+
+
 @pytest.mark.parametrize("math", MATHS)
 @pytest.mark.parametrize("geo", [(2, 3, 7, 9, 5, 3, 1, 1), (1, 4, 11, 11, 6, 5, 1, 2), (3, 8, 12, 12, 8, 3, 2, 1),
                                  (2, 5, 6, 6, 4, 1, 1, 0), (2, 12, 8, 8, 24, 3, 1, 1), (4, 48, 16, 16, 12, 3, 1, 1)])
