@@ -272,7 +272,9 @@ int cb_synchronize(cb_ctx* ctx) {
 }
 
 #ifdef CB_TRACE
-// Development builds only: the next tensor-core convolution kernels write 16 time stamps per CTA into `buf`.
+// Development builds only: the next tensor-core convolution kernels write 16 time stamps per CTA into `buf`, and the
+// forward / data-gradient kernel four more words per CTA (issuer wait and issue sums) behind the first 1024 x 16:
+// `buf` holds at least 1024 * 20 words.
 int cb_debug_set_trace(cb_ctx* ctx, long long* buf) {
     if (!ctx) return CB_EINVAL;
     ctx->trace = buf;

@@ -310,18 +310,34 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
         uint32_t s = 0, ph = 0, lt = 0;
         bool ok = conv_warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
         if (lane == 0) CB_TRACE_EVENT(p.trace, 4);
+#ifdef CB_TRACE
+        long long t_tempty = 0, t_full = 0, t_issue = 0;
+#endif
         for (int tile = tile0; tile < p.tiles && ok; tile += tile_step, ++lt) {
             const uint32_t a = lt & 1u;
+#ifdef CB_TRACE
+            const long long c_t0 = clock64();
+#endif
             ok = conv_warp_wait(smem_u32(&cs.tempty[a]), ((lt >> 1) & 1u) ^ 1u, lane, abort_flag, p.status,
                                 CBK_TIMEOUT_TMEM_EMPTY);
             if (!ok) break;
             tc_fence_after();
+#ifdef CB_TRACE
+            t_tempty += clock64() - c_t0;
+#endif
             const uint32_t d_tmem = tmem_base + a * acc_stride;
             int ti = 0;
             for (int cb = 0; cb < p.NCB; ++cb) {
+#ifdef CB_TRACE
+                const long long c_f0 = clock64();
+#endif
                 ok = conv_warp_wait(smem_u32(&cs.full[s]), ph, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
                 if (!ok) break;
                 tc_fence_after();
+#ifdef CB_TRACE
+                const long long c_f1 = clock64();
+                t_full += c_f1 - c_f0;
+#endif
                 if (lane == 0 && lt == 0 && cb == 0) CB_TRACE_EVENT(p.trace, 5);
                 if (lane == 0) {
                     const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
@@ -337,9 +353,22 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
                     ti += per_stage;
                 }
                 __syncwarp();
+#ifdef CB_TRACE
+                t_issue += clock64() - c_f1;
+#endif
                 if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
             }
         }
+#ifdef CB_TRACE
+        if (lane == 0 && p.trace) {
+            // behind the 1024 x 16 event slots: per-CTA sums of the issuer's waits and issue time
+            long long* sums = p.trace + 1024 * 16 + (long long)blockIdx.x * 4;
+            sums[0] = t_tempty;
+            sums[1] = t_full;
+            sums[2] = t_issue;
+            sums[3] = (long long)p.stages * 10000 + p.KS * 1000 + p.NCB * 100 + p.nsplit;
+        }
+#endif
     } else {
         // ------------------------------------------------------------ epilogue (warps 2 ..)
         // One scheduler cannot hide the shuffle and store latencies of a single warp, so every TMEM lane quarter is
