@@ -232,6 +232,17 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
+// Whole warp, converged: the lane umma_tf32_elect elects (the same one every time for the full mask) arrives once on
+// `bar` when every tcgen05.mma it issued earlier retired.
+__device__ __forceinline__ void tc_commit_elect(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n" ::"r"(bar)
+        : "memory");
+}
 // One thread. D[tmem] (+)= A[smem desc] * B[smem desc], kind::tf32, fp32 accumulate.
 __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
@@ -243,6 +254,33 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t desc_a, uint
         "}\n" ::"r"(d_tmem),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// Whole warp, converged, every lane with the same arguments: one elected lane issues the UMMA. Keeping the issuing loop
+// warp-uniform lets the compiler hold the descriptors in uniform registers; in a one-lane branch a descriptor that
+// changes from one UMMA to the next costs ~110 cycles of issue each (measured with the UMMA-only loop of peak_sm100.cu).
+__device__ __forceinline__ void umma_tf32_elect(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// kElect: called by the whole converged warp (elected lane issues); otherwise by the one issuing thread.
+template <bool kElect>
+__device__ __forceinline__ void umma_tf32_sel(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    if (kElect) umma_tf32_elect(d_tmem, desc_a, desc_b, idesc, accumulate);
+    else umma_tf32(d_tmem, desc_a, desc_b, idesc, accumulate);
+}
+template <bool kElect>
+__device__ __forceinline__ void tc_commit_sel(uint32_t bar) {
+    if (kElect) tc_commit_elect(bar);
+    else tc_commit(bar);
 }
 // Whole-warp: 32 lanes x 16 consecutive fp32 columns starting at taddr (lane field = warp's quarter).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {

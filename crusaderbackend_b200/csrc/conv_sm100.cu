@@ -63,8 +63,10 @@ struct ConvParams {
     float* Out;
     long long out_batch;      // elements between consecutive images of the output
     ConvEpilogue ep;
+    int issue_uniform;  // the MMA warp issues as a whole with an elected lane (wide accumulators) instead of from lane 0
     int* status;
     long long* trace;
+    int dbg;       // development probes of the trace build
 };
 
 struct __align__(8) ConvSmem {
@@ -184,7 +186,6 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
                      const __grid_constant__ CUtensorMap tmOut, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ ConvSmem cs;
-    __shared__ uint2 mma_tab[kMaxTileUmmas];  // per UMMA of a tile: descriptor offsets of its P and Q operands
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     volatile int* abort_flag = &cs.abort_flag;
@@ -285,28 +286,20 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ UMMA issuer
-        // One thread feeds the tensor core, and the instructions it spends per tcgen05.mma bound the kernel (a 128 x 48
-        // x 8 UMMA is ~25 cycles of tensor pipe): the operand descriptor offsets of every UMMA of a tile are tabulated
-        // once by the whole warp, so that issuing one costs a shared-memory load and two 64-bit adds.
+        // One thread feeds the tensor core, and what it spends per tcgen05.mma bounds the kernel (a 128 x 48 x 8 UMMA is
+        // ~50 cycles of tensor pipe). The operand descriptors are advanced by plain integer arithmetic on values that
+        // come from kernel parameters and loop counters only: a descriptor offset fetched from a shared-memory table
+        // costs ~113 cycles per UMMA whatever its size (measured with the UMMA-only loop of peak_sm100.cu: 52 -> 113
+        // cycles at N = 64, 103 -> 124 at N = 192), one computed with divisions ~150 instructions.
         const uint32_t idesc = umma_idesc_tf32(128, (uint32_t)p.NQ, 1u, 0u);
         // P: 4 lines x [8 channels][128 B], MN-major: block_bytes between lines (LBO), 512 B per 4 channel rows (SBO)
         const uint64_t descP0 = umma_smem_desc(0, p.block_bytes, 512u, UMMA_SW_128B_BASE32B);
         // Q: packed filter rows [(fw, oc)][32 channels], K-major 128-byte rows
         const uint64_t descQ0 = umma_smem_desc(w_base, 16u, 1024u, UMMA_SW_128B);
-        const int per_stage = p.FH * p.KS;
-        {
-            const uint32_t blk_units = p.block_bytes >> 4;               // descriptor address units (16 B) per line block
-            const uint32_t fh_blocks = p.shared_rows ? 1u : 4u;          // blocks between consecutive filter rows
-            const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
-            for (int i = lane; i < p.NCB * per_stage; i += 32) {
-                const int cb = i / per_stage, rem = i - cb * per_stage;
-                const int fh = rem / p.KS, kk = rem - fh * p.KS;
-                const uint32_t ks = (uint32_t)(cb * p.KS + kk);  // global K step: channels [8 ks, 8 ks + 8)
-                mma_tab[i] = make_uint2((uint32_t)fh * fh_blocks * blk_units + (uint32_t)kk * 64u,
-                                        ((uint32_t)(fh * p.CG) + (ks >> 2)) * q_group_units + (ks & 3u) * 2u);
-            }
-            __syncwarp();
-        }
+        const uint32_t blk_units = p.block_bytes >> 4;                     // descriptor address units (16 B) per line block
+        const uint32_t fh_units = (p.shared_rows ? 1u : 4u) * blk_units;  // between consecutive filter rows of P
+        const uint32_t q_group_units = (uint32_t)p.NQ * (kRowBytes >> 4);  // one (filter row, 32-channel group) of Q
+        const uint32_t q_fh_units = (uint32_t)p.CG * q_group_units;        // between consecutive filter rows of Q
         uint32_t s = 0, ph = 0, lt = 0;
         bool ok = conv_warp_wait(smem_u32(&cs.wbar), 0, lane, abort_flag, p.status, CBK_TIMEOUT_FULL);
         if (lane == 0) CB_TRACE_EVENT(p.trace, 4);
@@ -339,19 +332,39 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
                 t_full += c_f1 - c_f0;
 #endif
                 if (lane == 0 && lt == 0 && cb == 0) CB_TRACE_EVENT(p.trace, 5);
-                if (lane == 0) {
-                    const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
-#pragma unroll 2
-                    for (int j = 0; j < per_stage; ++j, ++ti) {
-                        const uint2 off = mma_tab[ti];
-                        umma_tf32(d_tmem, pbase + off.x, descQ0 + off.y, idesc, ti != 0 ? 1u : 0u);
+                const uint64_t pbase = descP0 + (uint64_t)(((st_base + s * p.stage_bytes) >> 4) & 0x3FFFu);
+                const uint32_t ks0 = (uint32_t)(cb * p.KS);  // first K step of the stage: channels [8 ks0, ..)
+                if (p.issue_uniform) {
+                    // Wide accumulators (long MMA phases): the whole warp runs the loop with the same values and one
+                    // elected lane issues, so that the descriptors stay in uniform registers — from a one-lane branch a
+                    // descriptor that changes between UMMAs costs ~110 cycles of issue, more than a 128 x 192 x 8 UMMA
+                    // takes (measured with the UMMA-only loop of peak_sm100.cu). Narrow accumulators measured slower
+                    // this way and keep the one-lane form.
+                    for (int fh = 0; fh < p.FH; ++fh) {
+                        const uint64_t prow = pbase + (uint64_t)((uint32_t)fh * fh_units);
+                        const uint64_t qrow = descQ0 + (uint64_t)((uint32_t)fh * q_fh_units);
+                        for (int kk = 0; kk < p.KS; ++kk, ++ti) {
+                            const uint32_t ks = ks0 + (uint32_t)kk;
+                            umma_tf32_elect(d_tmem, prow + (uint64_t)((uint32_t)kk * 64u),
+                                            qrow + (uint64_t)((ks >> 2) * q_group_units + (ks & 3u) * 2u), idesc, ti != 0 ? 1u : 0u);
+                        }
+                    }
+                    tc_commit_elect(smem_u32(&cs.empty[s]));
+                    if (cb == p.NCB - 1) tc_commit_elect(smem_u32(&cs.tfull[a]));
+                } else if (lane == 0) {
+                    for (int fh = 0; fh < p.FH; ++fh) {
+                        const uint64_t prow = pbase + (uint64_t)((uint32_t)fh * fh_units);
+                        const uint64_t qrow = descQ0 + (uint64_t)((uint32_t)fh * q_fh_units);
+                        for (int kk = 0; kk < p.KS; ++kk, ++ti) {
+                            const uint32_t ks = ks0 + (uint32_t)kk;
+                            umma_tf32(d_tmem, prow + (uint64_t)((uint32_t)kk * 64u),
+                                      qrow + (uint64_t)((ks >> 2) * q_group_units + (ks & 3u) * 2u), idesc, ti != 0 ? 1u : 0u);
+                        }
                     }
                     tc_commit(smem_u32(&cs.empty[s]));
                     if (cb == p.NCB - 1) tc_commit(smem_u32(&cs.tfull[a]));
-                    if (lt == 0 && cb == p.NCB - 1) CB_TRACE_EVENT(p.trace, 6);
-                } else {
-                    ti += per_stage;
                 }
+                if (lane == 0 && lt == 0 && cb == p.NCB - 1) CB_TRACE_EVENT(p.trace, 6);
                 __syncwarp();
 #ifdef CB_TRACE
                 t_issue += clock64() - c_f1;
@@ -398,6 +411,13 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
             float* img = p.Out + (long long)n * p.out_batch;
             const int pix = h0 * p.W + lane;
             const uint32_t t_row = tmem_base + a * acc_stride + ((uint32_t)(32 * quarter) << 16);
+#ifdef CB_TRACE
+            if (p.dbg & 1) {  // development probe: leave the accumulator unread (how fast is the MMA phase alone?)
+                tc_fence_before();
+                mbar_arrive(smem_u32(&cs.tempty[a]));
+                continue;
+            }
+#endif
             for (int c = slot * 8; c < p.OCs; c += 8 * (kEpiWarps / 4), buf ^= 1u)
                 conv_epilogue_chunk<TAPS>(p, &tmOut, t_row, c, oc0, img, plane, pix, n, valid, has_left, has_right,
                                     my_stage + buf * 1024u, lane, threadIdx.x == 64 && lt == 0 && c == 0);
@@ -421,9 +441,10 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
             for (int st = 0; st < p.stages; ++st)
                 if ((armed >> st) & 1u) mbar_drain(smem_u32(&cs.full[st]), (armed_parity >> st) & 1u, p.status);
         }
-        if (warp == 1 && lane == 0) {
-            tc_commit(smem_u32(&cs.drain));
-            mbar_drain(smem_u32(&cs.drain), 0, p.status);
+        if (warp == 1) {  // the commit comes from the lane that issued the MMAs
+            if (p.issue_uniform) tc_commit_elect(smem_u32(&cs.drain));
+            else if (lane == 0) tc_commit(smem_u32(&cs.drain));
+            if (lane == 0) mbar_drain(smem_u32(&cs.drain), 0, p.status);
         }
         __syncthreads();
     }
@@ -839,7 +860,20 @@ int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const fl
     p.out_batch = out_batch ? out_batch : (long long)q.Cout * (long long)plane;
     p.ep = ep;
     p.status = env.status;
+    {
+        static const int forced = [] {
+            const char* e = std::getenv("CB_CONV_ISSUE");  // development override: 0 one lane, 1 whole warp
+            return e ? std::atoi(e) : -1;
+        }();
+        p.issue_uniform = forced >= 0 ? forced : (q.NQ >= 160 ? 1 : 0);
+    }
     p.trace = err_ctx ? err_ctx->trace : nullptr;
+#ifdef CB_TRACE
+    {
+        const char* e = std::getenv("CB_DBG");
+        p.dbg = e ? std::atoi(e) : 0;
+    }
+#endif
     const uint64_t in_stride = (uint64_t)(in_batch ? in_batch : (long long)q.Cin * (long long)plane) * 4;
     if (in_stride & 15u) return fail(err_ctx, CB_EUNSUPPORTED, "convolution: the input batch stride must be a multiple of 4 floats");
 

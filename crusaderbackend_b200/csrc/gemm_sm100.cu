@@ -241,7 +241,13 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
                     if (!ok) break;
                     tc_fence_after();
                 }
-                if (lane == 0) {
+                // TF32: the whole warp runs this block with the same values and one elected lane issues — in a one-lane
+                // branch a descriptor that changes from UMMA to UMMA costs ~110 cycles of issue each (measured with the
+                // UMMA-only loop of peak_sm100.cu), most of a 128 x 256 x 8 UMMA's 137 cycles. 3xTF32 keeps the one-lane
+                // form: with back-to-back UMMAs the tensor core's operand fetches starve the split warps' shared-memory
+                // traffic and the whole pipeline ran 20-35 % slower.
+                constexpr bool kElect = !X3;
+                if (kElect || lane == 0) {
                     const uint64_t dQ = descQ0 + (uint64_t)(((sP + p_bytes) >> 4) & 0x3FFFu);
                     const uint32_t first = chunk_first ? 0u : 1u;
                     for (int m = 0; m < p.mi; ++m) {
@@ -251,20 +257,20 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
 #pragma unroll
                             for (int kk = 0; kk < kBK / 8; ++kk) {
                                 const uint64_t a = dP + kk * kStepP, b = dQ + kk * kStepQ;
-                                umma_tf32(d_tmem, a, b + lo_units, idesc, kk == 0 ? first : 1u);
-                                umma_tf32(d_tmem, a + lo_units, b, idesc, 1u);
-                                umma_tf32(d_tmem, a, b, idesc, 1u);
+                                umma_tf32_sel<kElect>(d_tmem, a, b + lo_units, idesc, kk == 0 ? first : 1u);
+                                umma_tf32_sel<kElect>(d_tmem, a + lo_units, b, idesc, 1u);
+                                umma_tf32_sel<kElect>(d_tmem, a, b, idesc, 1u);
                             }
                         } else {
-                            umma_tf32(d_tmem, dP, dQ, idesc, first);
-                            umma_tf32(d_tmem, dP + kStepP, dQ + kStepQ, idesc, 1u);
-                            umma_tf32(d_tmem, dP + 2 * kStepP, dQ + 2 * kStepQ, idesc, 1u);
-                            umma_tf32(d_tmem, dP + 3 * kStepP, dQ + 3 * kStepQ, idesc, 1u);
+                            umma_tf32_sel<kElect>(d_tmem, dP, dQ, idesc, first);
+                            umma_tf32_sel<kElect>(d_tmem, dP + kStepP, dQ + kStepQ, idesc, 1u);
+                            umma_tf32_sel<kElect>(d_tmem, dP + 2 * kStepP, dQ + 2 * kStepQ, idesc, 1u);
+                            umma_tf32_sel<kElect>(d_tmem, dP + 3 * kStepP, dQ + 3 * kStepQ, idesc, 1u);
                         }
                     }
-                    tc_commit(smem_u32(&ps.empty[s]));  // stage reusable once these MMAs retire
+                    tc_commit_sel<kElect>(smem_u32(&ps.empty[s]));  // stage reusable once these MMAs retire
                     if (chunk_last)
-                        for (int m = 0; m < p.mi; ++m) tc_commit(smem_u32(&ps.tfull[(sub + m) & 1u]));
+                        for (int m = 0; m < p.mi; ++m) tc_commit_sel<kElect>(smem_u32(&ps.tfull[(sub + m) & 1u]));
                 }
                 __syncwarp();
                 if (chunk_last) sub += (uint32_t)p.mi;
@@ -399,9 +405,10 @@ __global__ void __launch_bounds__(X3 ? 64 + 32 * kEpiWarps + 128 : 64 + 32 * kEp
             for (int st = 0; st < p.stages; ++st)
                 if ((armed >> st) & 1u) mbar_drain(smem_u32(&ps.full[st]), (armed_parity >> st) & 1u, p.status);
         }
-        if (warp == 1 && lane == 0) {
-            tc_commit(smem_u32(&ps.drain));
-            mbar_drain(smem_u32(&ps.drain), 0, p.status);
+        if (warp == 1) {  // the commit comes from the lane that issued the MMAs
+            if (!X3) tc_commit_elect(smem_u32(&ps.drain));
+            else if (lane == 0) tc_commit(smem_u32(&ps.drain));
+            if (lane == 0) mbar_drain(smem_u32(&ps.drain), 0, p.status);
         }
         __syncthreads();
     }

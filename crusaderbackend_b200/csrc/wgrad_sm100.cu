@@ -32,6 +32,7 @@ struct WgradParams {
     uint32_t line_bytes, stage_bytes, a_bytes;  // one line slot of a stage / lps of them / the A part of a line slot
     float* partial;                  // [gridDim.x][NQ][mtiles * 128]; with `atomic`: ONE such tile that every CTA adds into
     int atomic;
+    int issue_uniform;               // the MMA warp issues as a whole with an elected lane instead of from lane 0
     int* status;
     long long* trace;
 };
@@ -173,7 +174,28 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             t_xf += c2 - c1;
 #endif
             if (lane == 0 && first_line) CB_TRACE_EVENT(p.trace, 5);
-            if (lane == 0) {
+            if (p.issue_uniform) {
+                // the whole warp runs the loop with the same values, one elected lane issues: descriptors that change
+                // from UMMA to UMMA cost ~110 cycles of issue each from a one-lane branch (see umma_tf32_elect)
+                for (int l = 0; l < p.lps; ++l) {
+                    const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
+                    const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
+                    const uint64_t dB0 = desc0 + (uint64_t)(((stg + p.a_bytes) >> 4) & 0x3FFFu);
+                    const uint32_t first = (first_line && l == 0) ? 0u : 1u;
+                    for (int m = 0; m < p.mtiles; ++m) {
+                        const uint64_t dA = dA0 + (uint64_t)(m * (16384 >> 4));
+                        const uint32_t d = tmem_base + (uint32_t)m * p.NQ;
+                        umma_tf32_elect(d, dA, dB0, idesc, first);
+                        umma_tf32_elect(d, dA + 2, dB0 + 2, idesc, 1u);
+                        umma_tf32_elect(d, dA + 4, dB0 + 4, idesc, 1u);
+                        umma_tf32_elect(d, dA + 6, dB0 + 6, idesc, 1u);
+                    }
+                }
+                tc_commit_elect(smem_u32(&ws.empty[s]));
+                if (g + (int)gridDim.x >= p.groups) tc_commit_elect(smem_u32(&ws.tfull));
+                if (lane == 0 && first_line) CB_TRACE_EVENT(p.trace, 6);
+                if (lane == 0 && g + (int)gridDim.x >= p.groups) CB_TRACE_EVENT(p.trace, 7);
+            } else if (lane == 0) {
                 for (int l = 0; l < p.lps; ++l) {
                     const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
                     const uint64_t dA0 = desc0 + (uint64_t)((stg >> 4) & 0x3FFFu);
@@ -277,9 +299,10 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             for (int st = 0; st < p.stages; ++st)
                 if ((armed >> st) & 1u) mbar_drain(smem_u32(&ws.full[st]), (armed_parity >> st) & 1u, p.status);
         }
-        if (warp == 1 && lane == 0) {
-            tc_commit(smem_u32(&ws.drain));
-            mbar_drain(smem_u32(&ws.drain), 0, p.status);
+        if (warp == 1) {  // the commit comes from the lane that issued the MMAs
+            if (p.issue_uniform) tc_commit_elect(smem_u32(&ws.drain));
+            else if (lane == 0) tc_commit(smem_u32(&ws.drain));
+            if (lane == 0) mbar_drain(smem_u32(&ws.drain), 0, p.status);
         }
         __syncthreads();
     }
@@ -436,6 +459,13 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         return e ? std::atoi(e) : 1;
     }();
     p.atomic = (!ctx->deterministic && allow_atomic) ? 1 : 0;
+    static const int issue_mode = [] {
+        // development override: 0 one lane (default: with back-to-back UMMAs the tensor core's operand fetches starve
+        // the shift warps' shared-memory traffic and every layer shape measured 5-20 % slower), 1 whole warp
+        const char* e = std::getenv("CB_WGRAD_ISSUE");
+        return e ? std::atoi(e) : 0;
+    }();
+    p.issue_uniform = issue_mode;
     int rc;
     if (p.atomic) {
         rc = ensure_wgrad_acc(ctx, (size_t)mtiles * 128 * NQ * sizeof(float));
