@@ -362,6 +362,35 @@ def gemm_section(torch, local, peak_tflops):
     return out
 
 
+def resnet56_3xtf32_section(torch, local):
+    """The ResNet-56 step of the headline in 3xTF32 mode (fp32-class accuracy), batch 128, one CUDA-graph replay per step."""
+    from crusaderbackend_b200.api import Context
+    from crusaderbackend_b200.train import ResNetTrainer
+    from crusaderbackend_b200 import seeds
+    ctx = Context(local, math="3xtf32", sync=False)
+    tr = ResNetTrainer(ctx, batch=GLOBAL_BATCH, blocks_per_stage=9, image_hw=32, classes=10)
+    tr.init_params("bench")
+    img = torch.from_numpy(seeds.normal((GLOBAL_BATCH, 3, 32, 32), "bench", "img")).cuda()
+    lab = torch.zeros(GLOBAL_BATCH, 10, device="cuda")
+    lab[torch.arange(GLOBAL_BATCH), torch.from_numpy(seeds.rng_for("bench", "lab").integers(0, 10, GLOBAL_BATCH)).cuda()] = 1
+    g = tr.capture_step(img, lab, 0.01 / GLOBAL_BATCH, warmup=2)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    tr.close()
+    ctx.close()
+    return {"ms_per_step": round(ms, 3), "images_per_s": round(GLOBAL_BATCH / ms * 1e3, 1),
+            "note": "3xTF32: convolutions of up to 32 channels (and 64 channels on 8x8 maps) in one tensor-core pass over "
+                    "[x; x_lo; x] x [w; w; w_lo], the others as three passes"}
+
+
 def densenet_section(torch, local):
     """Config 5: DenseNet-BC-100 (k = 12), batch 64, forward + backward + Momentum as one CUDA graph."""
     from crusaderbackend_b200.api import Context
@@ -631,6 +660,10 @@ def bench_ours(args):
         line["conv"] = conv
         if not args.quick and world == 1:
             line["gemm"] = gemm_section(torch, local, umma_peak)
+            try:
+                line["resnet56_3xtf32"] = resnet56_3xtf32_section(torch, local)
+            except Exception as exc:
+                line["resnet56_3xtf32"] = {"error": str(exc)[:300]}
             try:
                 line["densenet_bc100"] = densenet_section(torch, local)
             except Exception as exc:

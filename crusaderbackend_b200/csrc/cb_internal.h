@@ -131,6 +131,9 @@ struct ConvEpilogue {
 int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
                   int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, bool dgrad_of, long long in_batch,
                   long long out_batch);
+// 3xTF32 forward / data gradient in one tensor-core pass (stride 1; conv_sm100.cu), else CB_EUNSUPPORTED.
+int umma_conv_fwd_x3(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
+                     int IW, int OC, int FH, int FW, int pH, int pW, bool dgrad_of, long long in_batch, long long out_batch);
 int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
                     int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch);
 // Packed-filter cache of a context (conv_sm100.cu).

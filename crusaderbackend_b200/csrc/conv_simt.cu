@@ -2,6 +2,8 @@
 // These serve CB_MATH_FP32 and every geometry the tensor-core implicit-GEMM kernels do not cover; they compute
 // exact fp32 FMAs. Index maps follow seblas/operations/cuConv.cu:105-115 (forward) and the adjoint of it for the
 // two gradients (the reference's weight-gradient map at :570-571 is wrong for stride > 1 and is not reproduced).
+#include <cstdlib>
+
 #include "cb_internal.h"
 
 namespace cb {
@@ -229,6 +231,15 @@ int grid_el(const cb_ctx* ctx, long long n) {
 static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out, const ConvEpilogue& ep, int N, int IC,
                        int IH, int IW, int OC, int FH, int FW, int sH, int sW, int pH, int pW, bool dgrad_of,
                        long long in_per, long long out_per, long long out_plane, long long in_batch, long long out_batch) {
+    static const int one_pass = [] {
+        const char* e = std::getenv("CB_CONV_X3_ONEPASS");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    if (one_pass && sH == 1 && sW == 1) {
+        // one pass of the tensor-core kernel over three channel groups, when the tripled filter fits
+        const int rc1 = umma_conv_fwd_x3(ctx, W, In, Out, ep, N, IC, IH, IW, OC, FH, FW, pH, pW, dgrad_of, in_batch, out_batch);
+        if (rc1 != CB_EUNSUPPORTED) return rc1;
+    }
     const long long w_elems = (long long)OC * IC * FH * FW;
     const long long in_elems = in_per * N, out_elems = out_per * N;
     auto up = [](long long n) { return (n + 63) & ~63LL; };

@@ -63,6 +63,7 @@ struct ConvParams {
     float* Out;
     long long out_batch;      // elements between consecutive images of the output
     ConvEpilogue ep;
+    int c_wrap;         // > 0: input channels from c_wrap on are read again from channel (c - c_wrap) (3xTF32 form)
     int issue_uniform;  // the MMA warp issues as a whole with an elected lane (wide accumulators) instead of from lane 0
     int* status;
     long long* trace;
@@ -80,7 +81,7 @@ struct __align__(8) ConvSmem {
     int abort_flag;
 };
 
-enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3 };
+enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3, PACK_FWD_X3 = 4, PACK_DGRAD_X3 = 5 };
 constexpr int kMaxTileUmmas = 256;  // UMMAs of one tile (filter rows x 8-channel steps) the issuer's table holds
 
 // Horizontal tap sets the kernel is instantiated for: the taps' column offsets fw - pW.
@@ -259,7 +260,8 @@ __global__ void __launch_bounds__(64 + 32 * kEpiWarps, kEpiWarps <= 8 ? 2 : 1)
                     mbar_expect_tx(full, p.stage_bytes);
                     armed |= 1u << s;
                     armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
-                    const int c0 = cb * p.KS * kCB;
+                    int c0 = cb * p.KS * kCB;
+                    if (p.c_wrap && c0 >= p.c_wrap) c0 -= p.c_wrap;  // third channel group of the 3xTF32 form: x_hi again
                     if (p.shared_rows) {
                         // W == 32: the tile is 4 consecutive rows of one image; ONE box (32 px, 8*KS channels, FH+3
                         // rows) lands as [row][channel][128 B]; rows above / below the image are zero-filled
@@ -485,6 +487,21 @@ __device__ __forceinline__ float pack_value(const PackJob& j, long long i) {
     const int ch = cg * 32 + c;
     const float* W = j.W;
     const int OC = j.OC, IC = j.IC, FHs = j.FHs, FWs = j.FWs;
+    if (j.mode == PACK_FWD_X3 || j.mode == PACK_DGRAD_X3) {
+        // 3xTF32 in one pass: the convolution runs over three groups of input channels [x ; x_lo ; x] against
+        // [w ; w ; w_lo] (the tensor core reads the hi part of whatever it is given), all into one accumulator
+        const int cin = j.mode == PACK_FWD_X3 ? IC : OC;   // input channels of the convolution the kernel runs
+        const int cout = j.mode == PACK_FWD_X3 ? OC : IC;
+        if (o >= cout || ch >= 3 * cin) return 0.f;
+        const int grp = ch / cin, cc = ch - grp * cin;
+        const float w = j.mode == PACK_FWD_X3 ? W[(((long long)o * IC + cc) * FHs + fh) * FWs + fw]
+                                               : W[(((long long)cc * IC + o) * FHs + (FHs - 1 - fh)) * FWs + (FWs - 1 - fw)];
+        if (grp < 2) return w;
+        const float hi = __uint_as_float(__float_as_uint(w) & 0xFFFFE000u);
+        uint32_t r;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(w - hi));
+        return __uint_as_float(r);
+    }
     if (j.mode == PACK_FWD) {
         if (o < OC && ch < IC) return W[(((long long)o * IC + ch) * FHs + fh) * FWs + fw];
     } else if (j.mode == PACK_DGRAD) {
@@ -691,6 +708,32 @@ static bool vec_ok(const void* a, const void* b, int W) {
     return (W & 3) == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
 }
 
+// 3xTF32 in one pass: X2[n][c] = X[n][c] and X2[n][C + c] = lo part of X[n][c] (x = hi + lo with hi the 19 bits the
+// tensor core reads, lo = rna_tf32(x - hi)), four pixels per thread; X may be batch-strided, X2 is dense.
+__global__ void tf32_split2_kernel(const float* __restrict__ X, float* __restrict__ X2, long long per4, long long x_batch,
+                                   long long items) {
+    griddep_wait();
+    griddep_launch();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items; i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / per4, r = i - n * per4;
+        const float4 v = *reinterpret_cast<const float4*>(X + n * x_batch + 4 * r);
+        float4 lo;
+        const float in[4] = {v.x, v.y, v.z, v.w};
+        float out[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float hi = __uint_as_float(__float_as_uint(in[e]) & 0xFFFFE000u);
+            uint32_t q;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(q) : "f"(in[e] - hi));
+            out[e] = __uint_as_float(q);
+        }
+        lo = make_float4(out[0], out[1], out[2], out[3]);
+        float* dst = X2 + n * 8 * per4 + 4 * r;   // a sample of X2 holds 2 * per elements = 8 * per4 floats
+        *reinterpret_cast<float4*>(dst) = v;
+        *reinterpret_cast<float4*>(dst + 4 * per4) = lo;
+    }
+}
+
 int relayout_grid(const cb_ctx* ctx, long long n) {
     long long g = (n + 255) / 256;
     const long long cap = (long long)ctx->sm_count * 16;
@@ -709,6 +752,8 @@ struct ConvEnv {
 struct ConvPlan {
     int Cin, Cout, OCp, OCs, nsplit, NQ, CG, L, KS, shared_rows, nblocks, stages;
     int ew;      // epilogue warps of the kernel instantiation: 8 or 16
+    int c_wrap = 0;  // set by the caller before planning: input-channel wrap of the 3xTF32 form (0 = none)
+    int ks_max = 4;  // set by the caller before planning: most K steps a stage may carry
     int per_sm;  // CTAs the plan expects to share an SM (2 for narrow outputs with a small filter, else 1)
     size_t w_bytes;       // one CTA's slice of the packed filter
     size_t w_total_bytes; // the whole packed filter
@@ -786,6 +831,7 @@ int plan_conv(ConvPlan& q, int smem_optin, int sm_count, const float* X, int N, 
         c.KS = 0;
         for (int ks = 4; ks >= 1; ks >>= 1) {
             if (ks > cin8 && ks > 1) continue;
+            if (ks > q.ks_max) continue;
             const long long st = cap / ((long long)c.nblocks * ks * kCB * kRowBytes);
             if (st >= 2) {
                 c.KS = ks;
@@ -842,6 +888,7 @@ int launch_conv(cb_ctx* err_ctx, const ConvEnv& env, const ConvPlan& q, const fl
     p.N = N; p.Cin = q.Cin; p.H = IH; p.W = IW; p.Cout = q.Cout;
     p.FH = FH; p.FW = FW; p.pH = pH; p.pW = pW;
     p.OCs = q.OCs; p.nsplit = q.nsplit; p.NQ = q.NQ; p.CG = q.CG; p.KS = q.KS;
+    p.c_wrap = q.c_wrap;
     p.NCB = (q.Cin + q.KS * kCB - 1) / (q.KS * kCB);
     p.L = q.L; p.LPI = IH / q.L;
     p.shared_rows = q.shared_rows; p.nblocks = q.nblocks;
@@ -1106,6 +1153,48 @@ static int conv_on_packed(cb_ctx* ctx, const ConvEnv& env, const ConvPlan& q, co
     rc = launch_conv(ctx, env, q, packed, X, Y, ep, N, IH, IW, FH, FW, pH, pW, in_batch, out_batch);
     if (rc != CB_OK) return rc;
     ctx->launches += 1;
+    return CB_OK;
+}
+
+// 3xTF32 forward / data gradient in ONE pass of the tensor-core kernel (stride 1): x = x_hi + x_lo, w = w_hi + w_lo and
+// y = x_hi w_hi + x_lo w_hi + x_hi w_lo are a single convolution over three groups of input channels, [x ; x_lo ; x]
+// against [w ; w ; w_lo], because the tensor core itself takes the hi part of what it reads. One small pass writes
+// X2 = [x ; x_lo] (dense scratch), the packed filter carries the three weight groups (cached like any other), and the
+// kernel's producer reads channels [0, cin) a second time for the third group. Everything accumulates in one TMEM
+// accumulator and leaves through the ordinary epilogue. CB_EUNSUPPORTED (nothing queued) when the channel count is not
+// a multiple of 8 or the tripled filter does not fit; the caller then composes three passes.
+int umma_conv_fwd_x3(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
+                     int IW, int OC, int FH, int FW, int pH, int pW, bool dgrad_of, long long in_batch, long long out_batch) {
+    if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
+    if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
+    const int cin = dgrad_of ? OC : IC, cout = dgrad_of ? IC : OC;
+    if (cin % 8 || ((long long)IH * IW) % 4) return CB_EUNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (in_batch & 3)) return CB_EUNSUPPORTED;
+    ConvEnv env{ctx->stream, ctx->sm_count, ctx->max_smem_optin, ctx->d_status};
+    ConvPlan q{};
+    q.c_wrap = 2 * cin;
+    q.ks_max = (cin % 32 == 0) ? 4 : ((cin % 16 == 0) ? 2 : 1);  // a stage's channels stay inside one group
+    int rc = plan_conv(q, ctx->max_smem_optin, ctx->sm_count, nullptr /* the scratch copy is aligned */, N, 3 * cin, cout, IH, IW,
+                       FH, FW, pH, pW);
+    if (rc != CB_OK) return rc;
+    // A tripled 64-channel filter only fits when the output channels are split four ways; every CTA then re-reads the
+    // input tile for 16 output channels, which pays on small maps (64->64 @8x8: 21 us against 36 composed) and not on
+    // large ones (64->64 @32x32: 207 us against 141).
+    if (q.nsplit > 2 && ((long long)N * (IH / q.L) + 3) / 4 > ctx->sm_count) return CB_EUNSUPPORTED;
+    const long long per = (long long)cin * IH * IW;
+    rc = ensure_workspace3(ctx, (size_t)N * 2 * per * sizeof(float));
+    if (rc != CB_OK) return rc;
+    float* X2 = static_cast<float*>(ctx->workspace3);
+    const long long items = (long long)N * (per / 4);
+    cudaError_t e = launch_dep(ctx, tf32_split2_kernel, dim3((unsigned)relayout_grid(ctx, items)), dim3(256), 0, X, X2, per / 4,
+                               in_batch ? in_batch : per, items);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "tf32_split2_kernel launch");
+    ctx->launches += 1;
+    const PackSpec ps{dgrad_of ? PACK_DGRAD_X3 : PACK_FWD_X3, OC, IC, FH, FW, 0, 0};
+    rc = conv_on_packed(ctx, env, q, ps, W, X2, Y, ep, N, IH, IW, FH, FW, pH, pW, 2 * per, out_batch);
+    if (rc != CB_OK) return rc;
+    ctx->last_kernel = "umma_3xtf32";
     return CB_OK;
 }
 
