@@ -82,15 +82,15 @@ struct __align__(8) ConvSmem {
 };
 
 enum { PACK_FWD = 0, PACK_DGRAD = 1, PACK_S2_FWD = 2, PACK_S2_DGRAD = 3, PACK_FWD_X3 = 4, PACK_DGRAD_X3 = 5 };
-constexpr int kMaxTileUmmas = 256;  // UMMAs of one tile (filter rows x 8-channel steps) the issuer's table holds
+constexpr int kMaxTileUmmas = 256;  // most UMMAs of one tile (filter rows x 8-channel steps) a plan may need
 
 // Horizontal tap sets the kernel is instantiated for: the taps' column offsets fw - pW.
 enum { TAPS_1 = 0 /* {0} */, TAPS_3 = 1 /* {-1, 0, +1} */, TAPS_2L = 2 /* {-1, 0} */, TAPS_2R = 3 /* {0, +1} */ };
 
 // One chunk of 8 output channels of a tile's epilogue: the horizontal taps were accumulated at the unshifted pixel in
 // column blocks fw*OCs + c; the tap with column offset d holds its partial sum d lanes away, and lanes that would read
-// across a row edge take zero instead (the horizontal padding). The epilogue is bound by instruction issue (every SM
-// runs 16 epilogue warps), so the tap set is a template parameter and the plain forms take a branch-free path.
+// across a row edge take zero instead (the horizontal padding). The epilogue is bound by latency and instruction issue (an SM
+// runs up to 16 epilogue warps of two CTAs), so the tap set is a template parameter and the plain forms take a branch-free path.
 // The 8 x 32 results leave either through one TMA store of the [8 channels][32 pixels] block, staged in this warp's
 // shared-memory slot `stage` (eight direct stores per thread land in eight different 4 KB-apart lines and were the
 // slowest part of the kernel), or, for the epilogue forms TMA cannot express (accumulate followed by ReLU), directly.
