@@ -134,8 +134,10 @@ int umma_conv_fwd(cb_ctx* ctx, const float* W, const float* X, float* Y, const C
 // 3xTF32 forward / data gradient in one tensor-core pass (stride 1; conv_sm100.cu), else CB_EUNSUPPORTED.
 int umma_conv_fwd_x3(cb_ctx* ctx, const float* W, const float* X, float* Y, const ConvEpilogue& ep, int N, int IC, int IH,
                      int IW, int OC, int FH, int FW, int pH, int pW, bool dgrad_of, long long in_batch, long long out_batch);
+// x3: 3xTF32 in one launch (the kernel walks (lo of X, dY), (X, lo of dY), (X, dY) into one accumulator).
 int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch);
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch,
+                    bool x3 = false);
 // Packed-filter cache of a context (conv_sm100.cu).
 int filter_cache_repack_all(cb_ctx* ctx);
 void filter_cache_destroy(cb_ctx* ctx);

@@ -275,9 +275,22 @@ static int conv_3xtf32(cb_ctx* ctx, const float* W, const float* In, float* Out,
     return CB_OK;
 }
 
-// 3xTF32 weight gradient: three accumulating TF32 passes (dY_hi X_lo, dY_lo X_hi, dY_hi X_hi); dense tensors.
+// 3xTF32 weight gradient: the products dY_hi X_hi, dY_hi X_lo, dY_lo X_hi in ONE launch of the tensor-core kernel
+// (it walks the pixels three times into one accumulator), or, with that switched off, as three accumulating launches
+// (dense tensors only).
 static int wgrad_3xtf32(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC, int FH,
-                        int FW, int sH, int sW, int pH, int pW, int accumulate, long long x_elems, long long dy_elems) {
+                        int FW, int sH, int sW, int pH, int pW, int accumulate, long long x_elems, long long dy_elems,
+                        long long dy_batch, long long x_batch) {
+    static const int onepass = [] {
+        const char* e = std::getenv("CB_WGRAD_X3_ONEPASS");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    if (onepass) {
+        const int rc1 = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, dy_batch, x_batch, true);
+        if (rc1 == CB_OK) ctx->last_kernel = "umma_3xtf32";
+        return rc1;
+    }
+    if (dy_batch || x_batch) return CB_EUNSUPPORTED;
     auto up = [](long long n) { return (n + 63) & ~63LL; };
     int rc = ensure_workspace3(ctx, (size_t)(up(x_elems) + up(dy_elems)) * sizeof(float));
     if (rc != CB_OK) return rc;
@@ -419,9 +432,9 @@ static int conv_wgrad_impl(cb_ctx* ctx, const float* dY, const float* X, float* 
     if (ctx->math == CB_MATH_TF32) {
         rc = umma_conv_wgrad(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate, dy_batch, x_batch);
         if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
-    } else if (ctx->math == CB_MATH_3XTF32 && !dy_batch && !x_batch) {
+    } else if (ctx->math == CB_MATH_3XTF32) {
         rc = wgrad_3xtf32(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, sH, sW, pH, pW, accumulate,
-                          (long long)N * IC * IH * IW, (long long)N * OC * g.OH * g.OW);
+                          (long long)N * IC * IH * IW, (long long)N * OC * g.OH * g.OW, dy_batch, x_batch);
         if (rc != CB_EUNSUPPORTED) return rc == CB_OK ? finish(ctx, who) : rc;
     }
     if (OC > 65535 || IC > 65535) return fail(ctx, CB_EUNSUPPORTED, std::string(who) + ": more than 65535 channels");

@@ -28,10 +28,19 @@ struct WgradParams {
     long long total_lines;
     int lps;                         // lines per pipeline stage
     int groups;                      // ceil(total_lines / lps)
+    // 3xTF32 in one launch: the line groups are walked three times, as (lo part of X, dY), (X, lo part of dY) and
+    // (X, dY) — the tensor core reads the hi part of whatever it is given — and all of it lands in one accumulator
+    int vgroups;                     // groups, or 3 * groups
     int stages, tmem_cols;
     uint32_t line_bytes, stage_bytes, a_bytes;  // one line slot of a stage / lps of them / the A part of a line slot
     float* partial;                  // [gridDim.x][NQ][mtiles * 128]; with `atomic`: ONE such tile that every CTA adds into
     int atomic;
+    // direct != 0: no second kernel. The CTA lays its tile out in the idle pipeline stages in the order of the filter
+    // block it belongs to (`OC` runs of `run` floats) and adds the runs into dW with coalesced atomics:
+    // dW[base_off + oc * oc_stride + j] += tile[oc * run + j]. dW must already hold what the sums are added to.
+    int direct, vec4, run, s2, IC_src;
+    long long oc_stride, base_off;
+    float* dW;
     int issue_uniform;               // the MMA warp issues as a whole with an elected lane instead of from lane 0
     int* status;
     long long* trace;
@@ -78,6 +87,7 @@ __device__ __forceinline__ void shift_dy_chunk(uint32_t src_row, uint32_t row_m1
 
 __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmdY,
+                      const __grid_constant__ CUtensorMap tmXlo, const __grid_constant__ CUtensorMap tmdYlo,
                       const WgradParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ WgradSmem ws;
@@ -102,6 +112,10 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
         mbar_fence_init();
         tma_prefetch_desc(&tmX);
         tma_prefetch_desc(&tmdY);
+        if (p.vgroups > p.groups) {
+            tma_prefetch_desc(&tmXlo);
+            tma_prefetch_desc(&tmdYlo);
+        }
     }
     __syncthreads();
     if (warp == 1) {
@@ -122,7 +136,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
         // ------------------------------------------------------------ TMA producer
         uint32_t s = 0, ph = 0;
         bool ok = true;
-        for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
+        for (int g = blockIdx.x; g < p.vgroups && ok; g += gridDim.x) {
             ok = conv_warp_wait(smem_u32(&ws.empty[s]), ph ^ 1u, lane, abort_flag, p.status, CBK_TIMEOUT_EMPTY);
             if (!ok) break;
             if (lane == 0) {
@@ -130,15 +144,21 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                 mbar_expect_tx(full, (uint32_t)p.lps * (p.a_bytes + set_bytes));
                 armed |= 1u << s;
                 armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+                // 3xTF32 form: the two small cross terms first, while the accumulator is small (the tensor core's
+                // fp32 accumulation error is relative to what the accumulator holds), the hi x hi products last
+                const int pass = g / p.groups, gg = g - pass * p.groups;
+                const bool x3 = p.vgroups > p.groups;
+                const CUtensorMap* mx = (x3 && pass == 0) ? &tmXlo : &tmX;
+                const CUtensorMap* my = (x3 && pass == 1) ? &tmdYlo : &tmdY;
                 for (int l = 0; l < p.lps; ++l) {
                     const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
                     // lines past the end use an image index >= N: their boxes are zero-filled and add nothing
-                    const int gi = g * p.lps + l;  // total_lines < 2^29 (checked on the host)
+                    const int gi = gg * p.lps + l;  // total_lines < 2^29 (checked on the host)
                     const int n = gi / p.LPI;
                     const int h0 = (gi - n * p.LPI) * p.L;
                     for (int fh = 0; fh < p.FH; ++fh)
-                        tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, &tmX, full, (h0 + fh - p.pH) * p.W, 0, n);
-                    tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, &tmdY, full, h0 * p.W, 0, n);
+                        tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, mx, full, (h0 + fh - p.pH) * p.W, 0, n);
+                    tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, my, full, h0 * p.W, 0, n);
                 }
             }
             __syncwarp();
@@ -154,7 +174,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
 #ifdef CB_TRACE
         long long t_full = 0, t_xf = 0, t_issue = 0;
 #endif
-        for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
+        for (int g = blockIdx.x; g < p.vgroups && ok; g += gridDim.x) {
 #ifdef CB_TRACE
             const long long c0 = clock64();
 #endif
@@ -192,9 +212,9 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                     }
                 }
                 tc_commit_elect(smem_u32(&ws.empty[s]));
-                if (g + (int)gridDim.x >= p.groups) tc_commit_elect(smem_u32(&ws.tfull));
+                if (g + (int)gridDim.x >= p.vgroups) tc_commit_elect(smem_u32(&ws.tfull));
                 if (lane == 0 && first_line) CB_TRACE_EVENT(p.trace, 6);
-                if (lane == 0 && g + (int)gridDim.x >= p.groups) CB_TRACE_EVENT(p.trace, 7);
+                if (lane == 0 && g + (int)gridDim.x >= p.vgroups) CB_TRACE_EVENT(p.trace, 7);
             } else if (lane == 0) {
                 for (int l = 0; l < p.lps; ++l) {
                     const uint32_t stg = st_base + s * p.stage_bytes + (uint32_t)l * p.line_bytes;
@@ -212,7 +232,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                 }
                 tc_commit(smem_u32(&ws.empty[s]));
                 if (first_line) CB_TRACE_EVENT(p.trace, 6);
-                if (g + (int)gridDim.x >= p.groups) {
+                if (g + (int)gridDim.x >= p.vgroups) {
                     tc_commit(smem_u32(&ws.tfull));
                     CB_TRACE_EVENT(p.trace, 7);
                 }
@@ -240,7 +260,42 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
         if (ok) {
             tc_fence_after();
             const int rows_tot = p.mtiles * 128;
-            for (int m = 0; m < p.mtiles; ++m) {
+            for (int m = 0; m < p.mtiles && p.direct; ++m) {
+                const int r = m * 128 + 32 * quarter + lane;
+                if (m * 128 + 32 * quarter >= p.rowsA) continue;  // warp-uniform: no valid row in this quarter
+                // Every UMMA of this CTA has completed (tfull), so nothing reads or writes the pipeline stages any more:
+                // they take the tile in filter order. Consecutive lanes are consecutive channels, FH*FW words apart
+                // (9 for a 3x3 filter): odd strides spread over the banks.
+                const int fh = r / p.Cp, c = r - fh * p.Cp;
+                bool row_ok = r < p.rowsA && c < p.Cin;
+                int roff, pw = 0;
+                if (!p.s2) {
+                    roff = (c * p.FH + fh) * p.FW;
+                } else {
+                    const int phase = c / p.IC_src, cc = c - phase * p.IC_src;
+                    const int sh = s2_tap(phase >> 1, fh);
+                    row_ok = row_ok && sh >= 0;
+                    roff = (cc * 3 + sh) * 3;
+                    pw = phase & 1;
+                }
+                const uint32_t t_row = tmem_base + (uint32_t)m * p.NQ + ((uint32_t)(32 * quarter) << 16);
+                for (int c0 = 0; c0 < p.NQ; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_row + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    const int fw = c0 / p.OCp, oc0 = c0 - fw * p.OCp;  // OCp is a multiple of 16: one fw per chunk
+                    const int sw = p.s2 ? s2_tap(pw, fw) : fw;
+                    if (row_ok && sw >= 0) {
+                        const uint32_t dst = st_base + 4u * (uint32_t)(oc0 * p.run + roff + sw);
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            if (oc0 + e < p.OC)
+                                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 4u * (uint32_t)(e * p.run)), "f"(__uint_as_float(v[e])) : "memory");
+                    }
+                    __syncwarp();  // the next tcgen05.ld is warp-wide
+                }
+            }
+            for (int m = 0; m < p.mtiles && !p.direct; ++m) {
                 const int r = m * 128 + 32 * quarter + lane;
                 if (m * 128 + 32 * quarter >= p.rowsA) continue;  // warp-uniform: no valid row in this quarter
                 // partial[cta][col][row]: for one column the warp's 32 rows are 128 contiguous bytes
@@ -269,7 +324,7 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
             uint32_t s = 0, ph = 0;
             bool ok = true;
             const int per_line = p.OCp * 8;
-            for (int g = blockIdx.x; g < p.groups && ok; g += gridDim.x) {
+            for (int g = blockIdx.x; g < p.vgroups && ok; g += gridDim.x) {
                 ok = mbar_wait(smem_u32(&ws.full[s]), ph, abort_flag, p.status, CBK_TIMEOUT_XFORM_FULL);
                 if (!ok) break;
                 for (int item = t; item < p.lps * per_line; item += 32 * kShiftWarps) {
@@ -309,6 +364,26 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+    if (p.direct && !ws.abort_flag) {
+        // the whole CTA adds the staged tile into dW: consecutive threads, consecutive addresses within a run
+        const int total = p.OC * p.run;
+        float* out = p.dW + p.base_off;
+        if (p.vec4) {  // runs start on 16-byte boundaries and are whole float4s: one vector add per four weights
+            for (int i = 4 * (int)threadIdx.x; i < total; i += 4 * (int)blockDim.x) {
+                const int oc = i / p.run, j = i - oc * p.run;
+                float4 v;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(st_base + 4u * (uint32_t)i));
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + (long long)oc * p.oc_stride + j), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+            }
+        } else {
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                const int oc = i / p.run, j = i - oc * p.run;
+                float v;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(st_base + 4u * (uint32_t)i));
+                atomicAdd(out + (long long)oc * p.oc_stride + j, v);
+            }
+        }
     }
     if (threadIdx.x == 0) {
         CB_TRACE_EVENT(p.trace, 11);
@@ -372,6 +447,48 @@ __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float*
     *dst = accumulate ? *dst + sum : sum;
 }
 
+// lo[n][i] = rna_tf32(x - hi(x)) of x[n * x_batch + i], hi = the 19 bits the tensor core reads; four elements per
+// thread, lo dense with `per4` float4 per image.
+__global__ void tf32_lo4_kernel(const float* __restrict__ x, float* __restrict__ lo, long long per4, long long x_batch,
+                                long long items) {
+    griddep_wait();
+    griddep_launch();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < items; i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / per4, r = i - n * per4;
+        const float4 v = *reinterpret_cast<const float4*>(x + n * x_batch + 4 * r);
+        const float in[4] = {v.x, v.y, v.z, v.w};
+        float out[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float hi = __uint_as_float(__float_as_uint(in[e]) & 0xFFFFE000u);
+            uint32_t q;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(q) : "f"(in[e] - hi));
+            out[e] = __uint_as_float(q);
+        }
+        reinterpret_cast<float4*>(lo)[i] = make_float4(out[0], out[1], out[2], out[3]);
+    }
+}
+
+int launch_lo(cb_ctx* ctx, const float* x, float* lo, long long images, long long per, long long x_batch) {
+    const long long items = images * (per / 4);
+    long long g = (items + 255) / 256;
+    const long long cap = (long long)ctx->sm_count * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    cudaError_t e = launch_dep(ctx, tf32_lo4_kernel, dim3((unsigned)g), dim3(256), 0, x, lo, per / 4, x_batch ? x_batch : per, items);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return check_cuda(ctx, e, "tf32_lo4_kernel launch");
+    ctx->launches += 1;
+    return CB_OK;
+}
+
+// lo parts of X and dY for the one-launch 3xTF32 form (dense scratch; batch strides 0 = dense)
+struct LoParts {
+    const float* x = nullptr;
+    const float* dy = nullptr;
+    long long x_batch = 0, dy_batch = 0;
+};
+
 // Development override of the lines per stage (1, 2 or 4); 0 = choose from the stage size.
 int forced_lps() {
     static const int v = [] {
@@ -395,7 +512,7 @@ int forced_min_groups() {
 // (FH, FW, pH, pW) in the same-size convention of the forward kernel. s2 / IC_src: see wgrad_reduce_kernel.
 static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int Cin, int IH, int IW, int OC, int FH,
                       int FW, int pH, int pW, int accumulate, int s2, int IC_src, long long dy_batch, long long x_batch,
-                      int IC_total = 0, int c_off = 0, int oc_off = 0) {
+                      int IC_total = 0, int c_off = 0, int oc_off = 0, const LoParts& lo = LoParts()) {
     if (IC_total == 0) IC_total = Cin;
     if (FH < 1 || FH > 3 || FW < 1 || FW > 3 || pH < 0 || pH > 1 || pW < 0 || pW > 1) return CB_EUNSUPPORTED;
     if (FH - 1 - pH > 1 || FW - 1 - pW > 1) return CB_EUNSUPPORTED;
@@ -438,12 +555,13 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     p.a_bytes = (uint32_t)rowsA * kRowBytes;
     p.lps = lps;
     p.groups = (int)((p.total_lines + lps - 1) / lps);
+    p.vgroups = lo.x ? 3 * p.groups : p.groups;
     p.status = ctx->d_status;
     p.trace = ctx->trace;
     // One CTA per line group up to the SM count: fewer, longer CTAs (fewer partial sums to write and reduce) measured
     // slower on every layer shape of the models.
     int min_groups = forced_min_groups() ? forced_min_groups() : 1;
-    int grid = p.groups / min_groups;
+    int grid = p.vgroups / min_groups;
     if (grid < 1) grid = 1;
     if (grid > ctx->sm_count) grid = ctx->sm_count;
     static const int max_grid = [] {
@@ -466,8 +584,30 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         return e ? std::atoi(e) : 0;
     }();
     p.issue_uniform = issue_mode;
+    static const int allow_direct = [] {
+        const char* e = std::getenv("CB_WGRAD_DIRECT");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    p.s2 = s2; p.IC_src = IC_src;
+    p.run = s2 ? IC_src * 9 : Cin * FH * FW;
+    p.oc_stride = s2 ? (long long)IC_src * 9 : (long long)IC_total * FH * FW;
+    p.base_off = s2 ? 0 : ((long long)oc_off * IC_total + c_off) * FH * FW;
+    p.dW = dW;
+    static const long long direct_limit = [] {
+        const char* e = std::getenv("CB_WGRAD_DIRECT_LIMIT");  // development override: most weights of a direct launch
+        return e ? std::atoll(e) : 1LL << 30;
+    }();
+    p.direct = (p.atomic && allow_direct && (long long)OC * p.run * 4 <= stages * (long long)stage_bytes &&
+                (long long)OC * p.run <= direct_limit) ? 1 : 0;
+    p.vec4 = ((p.run & 3) == 0 && (p.oc_stride & 3) == 0 && (p.base_off & 3) == 0 &&
+              (reinterpret_cast<uintptr_t>(dW) & 15u) == 0) ? 1 : 0;
     int rc;
-    if (p.atomic) {
+    if (p.direct) {
+        if (!accumulate) {
+            cudaError_t em = cudaMemset2DAsync(dW + p.base_off, (size_t)p.oc_stride * 4, 0, (size_t)p.run * 4, (size_t)OC, ctx->stream);
+            if (em != cudaSuccess) return check_cuda(ctx, em, "cudaMemset2DAsync(weight gradient)");
+        }
+    } else if (p.atomic) {
         rc = ensure_wgrad_acc(ctx, (size_t)mtiles * 128 * NQ * sizeof(float));
         if (rc != CB_OK) return rc;
         p.partial = static_cast<float*>(ctx->wgrad_acc);
@@ -494,14 +634,32 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         rc = encode_tmap(ctx, &tmdY, dY, 3, dims, str, box, nullptr, 128);
         if (rc != CB_OK) return rc;
     }
+    CUtensorMap tmXlo = tmX, tmdYlo = tmdY;
+    if (lo.x) {
+        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(lo.x_batch ? lo.x_batch : (long long)Cin * IH * IW) * 4};
+        uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
+        rc = encode_tmap(ctx, &tmXlo, lo.x, 3, dims, str, box, nullptr, 128);
+        if (rc != CB_OK) return rc;
+        uint64_t dimsy[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
+        uint64_t stry[2] = {(uint64_t)IH * IW * 4, (uint64_t)(lo.dy_batch ? lo.dy_batch : (long long)OC * IH * IW) * 4};
+        uint32_t boxy[3] = {32u, (uint32_t)OCp, 1u};
+        rc = encode_tmap(ctx, &tmdYlo, lo.dy, 3, dimsy, stry, boxy, nullptr, 128);
+        if (rc != CB_OK) return rc;
+    }
     const size_t smem = (size_t)p.stages * stage_bytes + 1024;
     int smem_bound = 0;
     cudaError_t e = raise_dynamic_smem_once(umma_wgrad_kernel, ctx->device, ctx->max_smem_optin, &smem_bound);
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel attribute");
     if ((int)smem > smem_bound) return CB_EUNSUPPORTED;
-    e = launch_dep(ctx, umma_wgrad_kernel, dim3((unsigned)grid), dim3(192 + 32 * kShiftWarps), smem, tmX, tmdY, p);
+    e = launch_dep(ctx, umma_wgrad_kernel, dim3((unsigned)grid), dim3(192 + 32 * kShiftWarps), smem, tmX, tmdY, tmXlo, tmdYlo, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "umma_wgrad_kernel launch");
+    if (p.direct) {
+        ctx->launches += 1;
+        ctx->last_kernel = "umma_tf32";
+        return CB_OK;
+    }
     const int rgrid = NQ * ((rowsA + 31) / 32);
     static const int groups = [] {
         const char* env = std::getenv("CB_WGRAD_REDUCE_GROUPS");  // development override: 2, 4 or 8
@@ -523,7 +681,23 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
 }
 
 int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int N, int IC, int IH, int IW, int OC,
-                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch) {
+                    int FH, int FW, int sH, int sW, int pH, int pW, int accumulate, long long dy_batch, long long x_batch,
+                    bool x3) {
+    // 3xTF32: lo parts of the two operands (as the kernel will read them: after the stride-2 re-layout) in scratch
+    auto make_lo = [&](const float* Xsrc, long long x_per, long long xb, const float* dYsrc, long long dy_per, long long yb,
+                       LoParts& lo) -> int {
+        auto up = [](long long n) { return (n + 63) & ~63LL; };
+        const long long xe = (long long)N * x_per, ye = (long long)N * dy_per;
+        int rc = ensure_workspace3(ctx, (size_t)(up(xe) + up(ye)) * sizeof(float));
+        if (rc != CB_OK) return rc;
+        float* xl = static_cast<float*>(ctx->workspace3);
+        float* yl = xl + up(xe);
+        rc = launch_lo(ctx, Xsrc, xl, N, x_per, xb);
+        if (rc == CB_OK) rc = launch_lo(ctx, dYsrc, yl, N, dy_per, yb);
+        lo.x = xl; lo.dy = yl; lo.x_batch = x_per; lo.dy_batch = dy_per;
+        return rc;
+    };
+    if (N < 1 || ((long long)IH * IW & 3)) return CB_EUNSUPPORTED;
     if (sH == 1 && sW == 1) {
         if (!((FH == 1 && pH == 0) || (FH == 3 && pH == 1))) return CB_EUNSUPPORTED;
         if (!((FW == 1 && pW == 0) || (FW == 3 && pW == 1))) return CB_EUNSUPPORTED;
@@ -541,16 +715,24 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
         if (c_max < 8) return CB_EUNSUPPORTED;
         const int c_blocks = (IC + c_max - 1) / c_max;
         const int c_step = ((IC + c_blocks - 1) / c_blocks + 7) & ~7;
-        if (oc_blocks == 1 && c_blocks == 1)
-            return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC, dy_batch, x_batch);
+        if (IW != 8 && IW != 16 && IW != 32) return CB_EUNSUPPORTED;  // before the lo parts are queued
         const long long plane = (long long)IH * IW;
+        LoParts lo;
+        if (x3) {
+            const int rc = make_lo(X, (long long)IC * plane, x_batch, dY, (long long)OC * plane, dy_batch, lo);
+            if (rc != CB_OK) return rc;
+        }
+        if (oc_blocks == 1 && c_blocks == 1)
+            return wgrad_core(ctx, dY, X, dW, N, IC, IH, IW, OC, FH, FW, pH, pW, accumulate, 0, IC, dy_batch, x_batch, 0, 0, 0, lo);
         const long long xb = x_batch ? x_batch : (long long)IC * plane, yb = dy_batch ? dy_batch : (long long)OC * plane;
         for (int o0 = 0; o0 < OC; o0 += oc_step) {
             const int on = OC - o0 < oc_step ? OC - o0 : oc_step;
             for (int c0 = 0; c0 < IC; c0 += c_step) {
                 const int cn = IC - c0 < c_step ? IC - c0 : c_step;
+                LoParts lc = lo;
+                if (x3) { lc.x = lo.x + c0 * plane; lc.dy = lo.dy + o0 * plane; }
                 const int rc = wgrad_core(ctx, dY + o0 * plane, X + c0 * plane, dW, N, cn, IH, IW, on, FH, FW, pH, pW, accumulate, 0, cn,
-                                          yb, xb, IC, c0, o0);
+                                          yb, xb, IC, c0, o0, lc);
                 if (rc != CB_OK) return rc;
             }
         }
@@ -569,7 +751,12 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
         float* sub = static_cast<float*>(ctx->workspace2);
         rc = launch_subsample2(ctx, X, sub, (long long)N * IC, IH, IW);
         if (rc != CB_OK) return rc;
-        return wgrad_core(ctx, dY, sub, dW, N, IC, H2, W2, OC, 1, 1, 0, 0, accumulate, 0, IC, 0, 0);
+        LoParts lo;
+        if (x3) {
+            rc = make_lo(sub, (long long)IC * plane2, 0, dY, (long long)OC * plane2, 0, lo);
+            if (rc != CB_OK) return rc;
+        }
+        return wgrad_core(ctx, dY, sub, dW, N, IC, H2, W2, OC, 1, 1, 0, 0, accumulate, 0, IC, 0, 0, 0, 0, 0, lo);
     }
     if (4 * IC > 256) return CB_EUNSUPPORTED;
     const long long n_el = (long long)N * 4 * IC * plane2;
@@ -578,7 +765,12 @@ int umma_conv_wgrad(cb_ctx* ctx, const float* dY, const float* X, float* dW, int
     float* Xs = static_cast<float*>(ctx->workspace2);
     rc = launch_space_to_depth2(ctx, X, Xs, N, IC, IH, IW);
     if (rc != CB_OK) return rc;
-    return wgrad_core(ctx, dY, Xs, dW, N, 4 * IC, H2, W2, OC, 2, 2, 1, 1, accumulate, 1, IC, 0, 0);
+    LoParts lo;
+    if (x3) {
+        rc = make_lo(Xs, 4LL * IC * plane2, 0, dY, (long long)OC * plane2, 0, lo);
+        if (rc != CB_OK) return rc;
+    }
+    return wgrad_core(ctx, dY, Xs, dW, N, 4 * IC, H2, W2, OC, 2, 2, 1, 1, accumulate, 1, IC, 0, 0, 0, 0, 0, lo);
 }
 
 }  // namespace cb

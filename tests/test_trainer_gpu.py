@@ -200,7 +200,8 @@ def test_wgrad_streams_do_not_change_results(torch_cuda):
     for g1, p, launches in results[2:]:
         assert orc.max_err_norm(g1.cpu().numpy(), results[0][0].cpu().numpy()) <= 1e-5
         assert orc.max_err_norm(p.cpu().numpy(), results[0][1].cpu().numpy()) <= 1e-5
-        assert launches == results[0][2]
+    assert results[2][2] == results[0][2]
+    assert results[3][2] <= results[0][2]   # the default context adds into the gradient directly: no second kernel
 
 
 def test_resnet56_loss_tracks_fp32_run(torch_cuda):
