@@ -17,9 +17,11 @@ namespace {
 //      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
 // A pipeline stage carries `lps` such lines (1, 2 or 4: as many as leave at least three stages), so that the per-stage
 // hand-offs between the producer, the shift warps and the MMA issuer are paid once per 32*lps pixels. Every CTA walks
-// its share of the line groups accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs), writes its
-// partial to the workspace column by column (the 32 lanes of a warp hold 32 consecutive rows: full 128-byte lines), and a second
-// kernel adds the partials in a fixed order (deterministic).
+// its share of the line groups accumulating D[(fh,c)][(fw,oc)] in TMEM (the whole K split across CTAs). Its tile then
+// leaves in one of two ways: laid out in filter order in the (by then idle) pipeline stages and added into dW with
+// vector atomics by the whole CTA (`direct`, the default: one launch), or written to the workspace as a partial, column
+// by column (the 32 lanes of a warp hold 32 consecutive rows: full 128-byte lines), for a second kernel that adds the
+// partials in a fixed order (deterministic contexts).
 struct WgradParams {
     int N, Cin, H, W, OC;
     int FH, FW, pH, pW;
