@@ -132,15 +132,37 @@ int encode_tmap(cb_ctx* ctx, CUtensorMap* out, const void* base, int rank, const
                 int swizzle_bytes) {
     EncodeTiledFn fn = resolve_encode();
     if (!fn) return fail(ctx, CB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t gd[5];
-    cuuint64_t gs[4];
-    cuuint32_t bd[5], es[5];
+    if (rank < 1 || rank > 5) return fail(ctx, CB_EINVAL, "tensor map rank outside 1..5");
+    cuuint64_t gd[5] = {};
+    cuuint64_t gs[4] = {};
+    cuuint32_t bd[5] = {}, es[5] = {};
     for (int i = 0; i < rank; ++i) {
         gd[i] = dims[i];
         bd[i] = box[i];
         es[i] = elem_strides ? elem_strides[i] : 1;
     }
     for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+    // The encoding is a pure function of these values: a context keeps what it has encoded (bounded: a caller that
+    // walks through ever new addresses starts over at 4096 entries).
+    struct Key {
+        const void* base;
+        cuuint64_t gd[5], gs[4];
+        cuuint32_t bd[5], es[5];
+        int rank, swizzle;
+    } key{};  // value-initialised: padding bytes are zero, the bytes are the hash key
+    std::string kbytes;
+    if (ctx) {
+        key.base = base; key.rank = rank; key.swizzle = swizzle_bytes;
+        for (int i = 0; i < 5; ++i) { key.gd[i] = gd[i]; key.bd[i] = bd[i]; key.es[i] = es[i]; }
+        for (int i = 0; i < 4; ++i) key.gs[i] = gs[i];
+        kbytes.assign(reinterpret_cast<const char*>(&key), sizeof(key));
+        auto it = ctx->tmap_cache.find(kbytes);
+        if (it != ctx->tmap_cache.end()) {
+            *out = it->second;
+            ++ctx->tmap_hits;
+            return CB_OK;
+        }
+    }
     CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
     if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
     else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
@@ -157,6 +179,11 @@ int encode_tmap(cb_ctx* ctx, CUtensorMap* out, const void* base, int rank, const
                  (unsigned long long)(rank > 2 ? gd[2] : 0), (unsigned long long)(rank > 3 ? gd[3] : 0), bd[0],
                  rank > 1 ? bd[1] : 0, rank > 2 ? bd[2] : 0, rank > 3 ? bd[3] : 0);
         return fail(ctx, CB_ECUDA, buf);
+    }
+    if (ctx) {
+        if (ctx->tmap_cache.size() >= 4096) ctx->tmap_cache.clear();
+        ctx->tmap_cache.emplace(std::move(kbytes), *out);
+        ++ctx->tmap_misses;
     }
     return CB_OK;
 }
@@ -269,6 +296,14 @@ int cb_set_deterministic(cb_ctx* ctx, int on) {
 int cb_synchronize(cb_ctx* ctx) {
     if (int rc_enter = enter(ctx)) return rc_enter;
     return read_status(ctx, "cb_synchronize");
+}
+
+// Development aid: how often this context reused / had to make an encoded tensor map.
+int cb_debug_tmap_stats(cb_ctx* ctx, long long* hits, long long* misses) {
+    if (!ctx) return CB_EINVAL;
+    if (hits) *hits = ctx->tmap_hits;
+    if (misses) *misses = ctx->tmap_misses;
+    return CB_OK;
 }
 
 #ifdef CB_TRACE

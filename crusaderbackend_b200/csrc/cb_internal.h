@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string>
+#include <unordered_map>
 #include <utility>
 #include <vector>
 
@@ -38,6 +39,10 @@ struct cb_ctx {
     void* wgrad_acc = nullptr;     // weight-gradient accumulator [column][row], all zero between calls (wgrad_sm100.cu)
     size_t wgrad_acc_bytes = 0;
     int wgrad_grid_cap = 0;        // > 0: most CTAs a weight-gradient kernel uses (contexts that run beside another stream)
+    // Encoded tensor maps by (base pointer, extents, strides, box, swizzle): a training loop presents the same few
+    // hundred (tensor, tiling) pairs every step, so the encode runs once per pair (encode_tmap, cb_abi.cu).
+    std::unordered_map<std::string, CUtensorMap> tmap_cache;
+    long long tmap_hits = 0, tmap_misses = 0;
 };
 
 namespace cb {
