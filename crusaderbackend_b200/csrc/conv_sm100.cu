@@ -824,8 +824,8 @@ int plan_conv(ConvPlan& q, int smem_optin, int sm_count, const float* X, int N, 
         c.ew = 8;
         if (forced_ew() == 8 || forced_ew() == 16) c.ew = forced_ew();
         const bool two_per_sm = c.OCs <= 32 && c.w_bytes <= 40 * 1024 && c.ew <= 8;
-        const long long budget = two_per_sm ? (long long)(smem_optin < 113 * 1024 ? smem_optin : 113 * 1024) : (long long)smem_optin;
-        const long long cap = budget - 4096 - (long long)c.w_bytes - 2048LL * c.ew;  // static shared memory, alignment slack;  // 2 KB of store staging per epilogue warp
+        const long long avail = two_per_sm ? (long long)(smem_optin < 113 * 1024 ? smem_optin : 113 * 1024) : (long long)smem_optin;
+        const long long cap = avail - 4096 - (long long)c.w_bytes - 2048LL * c.ew;  // static shared memory, alignment slack;  // 2 KB of store staging per epilogue warp
         // as many K steps per stage as leaves at least 2 stages: fewer, larger TMA boxes measured faster than a deeper
         // pipeline of small ones
         c.KS = 0;
