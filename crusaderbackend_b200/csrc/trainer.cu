@@ -1036,11 +1036,12 @@ int cbt_dp_unique_id(char* id128) {
     return CB_OK;
 }
 
-// Joins the communicator (collective over all ranks) and splits the flat gradient buffer into `buckets` ranges of
-// roughly equal size (1..8). From then on cbt_backward sum-allreduces each range over the ranks on a communication
+// Joins the communicator (collective over all ranks) and splits the flat gradient buffer into `buckets` ranges (1..8)
+// that double in size from the first layers' end (1 : 2 : 4 ...). From then on cbt_backward sum-allreduces each range over the ranks on a communication
 // stream as soon as its last gradient has been produced, and the gradients are the sums over all ranks when
 // cbt_backward's work is done. Call before capturing the step in a CUDA graph.
 int cbt_dp_init(cbt_model* m, const char* id128, int world, int rank, int buckets) {
+    if (const char* e = std::getenv("CBT_DP_BUCKETS")) buckets = std::atoi(e);  // development override
     if (!m || !id128 || world < 1 || rank < 0 || rank >= world || buckets < 1 || buckets > kMaxBuckets) return CB_EINVAL;
     if (m->comm) return CB_EINVAL;
     NcclApi* api = nccl_api(&m->err);
@@ -1062,8 +1063,14 @@ int cbt_dp_init(cbt_model* m, const char* id128, int world, int rank, int bucket
     // order) owning one of them, the last of them to be reached by the backward pass
     m->buckets.assign((size_t)buckets, GradBucket{});
     const long long total = m->param_count;
+    // The bucket at the lowest offsets holds the first layers: it is released last and nothing is left to overlap its
+    // exchange with, so the ranges double in size from there (1 : 2 : 4 ...) instead of being equal.
+    const char* ge = std::getenv("CBT_DP_GEOMETRIC");  // development switch
+    const bool geometric = ge ? std::atoi(ge) != 0 : true;
+    const long long units = geometric ? (1LL << buckets) - 1 : buckets;
     for (int b = 0; b < buckets; ++b) {
-        long long lo = total * b / buckets, hi = total * (b + 1) / buckets;
+        const long long u0 = geometric ? (1LL << b) - 1 : b, u1 = geometric ? (1LL << (b + 1)) - 1 : b + 1;
+        long long lo = total * u0 / units, hi = total * u1 / units;
         lo &= ~3LL;
         hi = b + 1 == buckets ? total : (hi & ~3LL);
         m->buckets[b].offset = lo;

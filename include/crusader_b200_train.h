@@ -66,7 +66,8 @@ int cbt_set_bn_groups(cbt_model* m, int groups);
  * one GPU only, seann/containers/Sequential.cu:107-163). Rank 0 obtains a 128-byte rendezvous id with
  * cbt_dp_unique_id and hands it to the other ranks over any host channel; every rank then calls cbt_dp_init
  * (collective). From then on cbt_backward sum-allreduces the flat gradient buffer over the ranks with NCCL, in
- * `buckets` contiguous ranges (1..8), each issued on a communication stream as soon as the backward pass has
+ * `buckets` contiguous ranges (1..8; the range of the first layers, which is ready last, is the smallest and each
+ * next one twice as large), each issued on a communication stream as soon as the backward pass has
  * produced its last gradient, so the exchange overlaps the rest of the backward pass; everything queued on the
  * context's stream after cbt_backward sees the summed gradients. Every rank then applies the same cbt_update, so the
  * replicas stay bit-identical without a broadcast. NCCL is loaded at run time (libnccl.so.2); CB_EUNSUPPORTED without it.
