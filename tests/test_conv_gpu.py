@@ -113,6 +113,32 @@ def test_densenet_layer_shapes_stay_on_the_tensor_cores(torch_cuda, ctxs, layer,
     assert all(k.startswith("umma") for k in kern), kern
 
 
+@pytest.mark.parametrize("deterministic", [False, True])
+@pytest.mark.parametrize("math", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("geo", [(8, 16, 32, 16, 3, 1), (4, 342, 8, 48, 1, 1), (4, 300, 16, 150, 1, 1), (8, 32, 32, 64, 3, 2),
+                                 (8, 16, 32, 32, 1, 2), (8, 3, 32, 16, 3, 1)])
+def test_weight_gradient_overwrite_and_accumulate(torch_cuda, geo, math, deterministic):
+    """convError in both of its output modes on the tensor-core kernel: `dW =` over a buffer full of NaN (the default
+    context clears the filter block, or the strided rows of a block of a wide filter, before its CTAs add into it)
+    and `dW +=` on top of the result (twice the gradient), one-launch and fixed-order forms, stride 1 and 2."""
+    torch = torch_cuda
+    from crusaderbackend_b200.api import Context
+    N, IC, H, OC, F, s = geo
+    p = 1 if F == 3 else 0
+    c = conv_case(("wmode", geo), N, IC, H, H, OC, F, s, p)
+    ctx = Context(0, math=math, sync=True)
+    ctx.set_deterministic(deterministic)
+    X, dY = torch.from_numpy(c["X"]).cuda(), torch.from_numpy(c["dY"]).cuda()
+    dW = torch.full((OC, IC, F, F), float("nan"), device="cuda")
+    ctx.convError(dY, X, dW, s, s, p, p, accumulate=False)
+    assert ctx.last_kernel.startswith("umma"), ctx.last_kernel
+    want = orc.conv_wgrad(c["dY"], c["X"], (OC, IC, F, F), (s, s), (p, p))
+    assert orc.max_err_norm(dW.cpu().numpy(), want) <= TOL[math]
+    ctx.convError(dY, X, dW, s, s, p, p, accumulate=True)
+    assert orc.max_err_norm(dW.cpu().numpy(), 2.0 * want) <= 2 * TOL[math]
+    ctx.close()
+
+
 @pytest.mark.parametrize("math", MATHS)
 @pytest.mark.parametrize("geo", [(2, 3, 7, 9, 5, 3, 1, 1), (1, 4, 11, 11, 6, 5, 1, 2), (3, 8, 12, 12, 8, 3, 2, 1),
                                  (2, 5, 6, 6, 4, 1, 1, 0), (2, 12, 8, 8, 24, 3, 1, 1), (4, 48, 16, 16, 12, 3, 1, 1)])
