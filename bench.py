@@ -17,6 +17,8 @@ backward + allreduce + update, replayed as one CUDA graph.
   roofline   of the dominant kernel of the step, umma_conv_kernel (its convolution forward / data-gradient launches):
          algorithmic bytes 4(|X|+|W|+|Y|) of the step's stride-1 3x3 launches over their measured time (each distinct
          layer shape timed live under graph replay), against the measured HBM copy bandwidth.
+  roofline_wgrad   the same object for umma_wgrad_kernel (the step's stride-1 3x3 weight gradients, which run on
+         streams of their own beside the critical chain).
   cpu_baseline / --impl reference   the OpenMP fp32 port of the same step (oracle/resnet_step.py; the reference has
          no CPU implementation of this path) on a bounded sample of the batch, all host threads.
 
@@ -288,6 +290,7 @@ def conv_section(torch, local, peak_tflops, hbm_gbs):
     ctx.lib.cb_conv_cache_filters(ctx.h, 1)
     out = {}
     agg_bytes = agg_us = 0.0
+    wg_bytes = wg_us = 0.0
     for (name, N, IC, H, OC, F, s, p, nf, nd) in CONV_SHAPES:
         OH = (H - F + 2 * p) // s + 1
         X = torch.randn(N, IC, H, H, device="cuda")
@@ -312,7 +315,11 @@ def conv_section(torch, local, peak_tflops, hbm_gbs):
             elif pname == "dgrad":
                 agg_bytes += nd * by
                 agg_us += nd * us
+            else:  # one weight gradient per forward launch of the shape
+                wg_bytes += nf * by
+                wg_us += nf * us
     ctx.close()
+    out["_wgrad_aggregate"] = (wg_bytes, wg_us)
     return out, agg_bytes, agg_us
 
 
@@ -654,6 +661,14 @@ def bench_ours(args):
                             "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": round(achieved / peaks["hbm_gbs"], 4),
                             "traffic": profiled_traffic("umma_conv_r56_16to16_fwd"), "peak_source": peaks["source"]}
+        wg_bytes, wg_us = conv.pop("_wgrad_aggregate")
+        wg = wg_bytes / wg_us / 1e3 if wg_us else 0.0
+        # the second tensor-core kernel of the step (off the critical chain, on the weight-gradient streams)
+        line["roofline_wgrad"] = {"bound": "hbm", "kernel": "umma_wgrad_kernel (the stride-1 3x3 weight-gradient launches of one "
+                                  "step, one launch each; each layer shape timed under graph replay)",
+                                  "achieved": round(wg, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": round(wg / peaks["hbm_gbs"], 4),
+                                  "traffic": profiled_traffic("umma_wgrad_r56_16to16"), "peak_source": peaks["source"]}
         line["tensor_peak"] = {"tf32_tflops_measured": round(umma_peak, 1),
                                "how": "cb_measure_umma_peak: resident-operand tcgen05.mma.kind::tf32 loop, M=128 N=256 K=8, every SM",
                                "bf16_tflops_measured_cublas": peaks["bf16_tflops"], "nominal_tf32_tflops": 1100.0}
