@@ -11,7 +11,8 @@ namespace {
 // over pixels, so both operands are K-major (32 pixels of one channel plane = one 128-byte row, standard 128-byte
 // swizzle). Per line of 32 output pixels a stage holds
 //   A: FH blocks [Cp channel rows][32 px] of X, fetched at the vertically shifted pixel offsets (UMMA M side,
-//      rows stacked as (fh, c); 128 rows per M tile), and
+//      rows stacked as (fh, c); 128 rows per M tile) — on 32-pixel-wide maps as one box [Cp][FH image rows][32 px],
+//      rows stacked as (c, fh) — and
 //   B: the dY line [OCp rows][32 px] three times, as (fw, oc) rows of the UMMA N side: the centre copy comes from
 //      TMA, the copies for fw = 0 / fw = 2 are the same rows rotated by one pixel (zeros entering at the image row
 //      edges), written by eight shift warps — shifting dY by -d is the same sum as shifting X by +d.
@@ -41,6 +42,10 @@ struct WgradParams {
     // block it belongs to (`OC` runs of `run` floats) and adds the runs into dW with coalesced atomics:
     // dW[base_off + oc * oc_stride + j] += tile[oc * run + j]. dW must already hold what the sums are added to.
     int direct, vec4, run, s2, IC_src;
+    // rows_cf != 0 (32-pixel-wide maps): a line is one image row, so the FH vertically shifted X blocks of a line are
+    // FH consecutive image rows and arrive as ONE 4-D box [channel][fh][32 px]: the accumulator rows are then ordered
+    // (c, fh) instead of (fh, c), and a line costs two TMA boxes instead of FH + 1.
+    int rows_cf;
     long long oc_stride, base_off;
     float* dW;
     int issue_uniform;               // the MMA warp issues as a whole with an elected lane instead of from lane 0
@@ -158,8 +163,12 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                     const int gi = gg * p.lps + l;  // total_lines < 2^29 (checked on the host)
                     const int n = gi / p.LPI;
                     const int h0 = (gi - n * p.LPI) * p.L;
-                    for (int fh = 0; fh < p.FH; ++fh)
-                        tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, mx, full, (h0 + fh - p.pH) * p.W, 0, n);
+                    if (p.rows_cf) {
+                        tma_load_4d(stg, mx, full, 0, h0 - p.pH, 0, n);
+                    } else {
+                        for (int fh = 0; fh < p.FH; ++fh)
+                            tma_load_3d(stg + (uint32_t)fh * p.Cp * kRowBytes, mx, full, (h0 + fh - p.pH) * p.W, 0, n);
+                    }
                     tma_load_3d(stg + p.a_bytes + (uint32_t)centre * set_bytes, my, full, h0 * p.W, 0, n);
                 }
             }
@@ -268,7 +277,8 @@ __global__ void __launch_bounds__(192 + 32 * kShiftWarps, 1)
                 // Every UMMA of this CTA has completed (tfull), so nothing reads or writes the pipeline stages any more:
                 // they take the tile in filter order. Consecutive lanes are consecutive channels, FH*FW words apart
                 // (9 for a 3x3 filter): odd strides spread over the banks.
-                const int fh = r / p.Cp, c = r - fh * p.Cp;
+                const int fh = p.rows_cf ? r % p.FH : r / p.Cp;
+                const int c = p.rows_cf ? r / p.FH : r - fh * p.Cp;
                 bool row_ok = r < p.rowsA && c < p.Cin;
                 int roff, pw = 0;
                 if (!p.s2) {
@@ -399,7 +409,8 @@ template <int kReduceGroups>
 __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float* __restrict__ partial, float* __restrict__ dW,
                                                            int nparts, int rows_tot, int rowsA, int NQ, int Cp, int Cin,
                                                            int OC, int OCp, int FH, int FW, int accumulate, int s2,
-                                                           int IC_src, int clear, int IC_total, int c_off, int oc_off) {
+                                                           int IC_src, int clear, int IC_total, int c_off, int oc_off,
+                                                           int rows_cf) {
     // Per-CTA partials (clear == 0): block = 32 consecutive valid accumulator rows of one column x kReduceGroups groups
     // of partials; each thread sums its group's partials in order, the group sums are added in order in shared memory:
     // a fixed summation order (deterministic). One shared accumulator tile (clear != 0): every thread row of the block
@@ -433,7 +444,8 @@ __global__ void __launch_bounds__(32 * kReduceGroups) wgrad_reduce_kernel(float*
 #pragma unroll
         for (int g = 0; g < kReduceGroups; ++g) sum += red[g][threadIdx.x];
     }
-    const int fh = r / Cp, c = r - fh * Cp;
+    const int fh = rows_cf ? r % FH : r / Cp;  // accumulator rows are (c, fh) or (fh, c): see WgradParams::rows_cf
+    const int c = rows_cf ? r / FH : r - fh * Cp;
     const int fw = col / OCp, oc = col - fw * OCp;
     if (c >= Cin || oc >= OC) return;
     float* dst;
@@ -591,6 +603,11 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
         return e ? std::atoi(e) : 1;
     }();
     p.s2 = s2; p.IC_src = IC_src;
+    static const int allow_cf = [] {
+        const char* e = std::getenv("CB_WGRAD_ROWBOX");  // development switch, default on
+        return e ? std::atoi(e) : 1;
+    }();
+    p.rows_cf = (allow_cf && IW == 32 && FH > 1 && !s2) ? 1 : 0;
     p.run = s2 ? IC_src * 9 : Cin * FH * FW;
     p.oc_stride = s2 ? (long long)IC_src * 9 : (long long)IC_total * FH * FW;
     p.base_off = s2 ? 0 : ((long long)oc_off * IC_total + c_off) * FH * FW;
@@ -620,14 +637,23 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     }
 
     CUtensorMap tmX, tmdY;
-    {
+    // X as (32 px, image row, channel, image) with a box of FH rows, or as (pixel, channel, image) with a box per tap
+    auto encode_x = [&](CUtensorMap* tm, const float* base, long long batch) -> int {
+        const uint64_t bstride = (uint64_t)(batch ? batch : (long long)Cin * IH * IW) * 4;
+        if (bstride & 15u) return CB_EUNSUPPORTED;
+        if (p.rows_cf) {
+            uint64_t dims[4] = {32u, (uint64_t)IH, (uint64_t)Cin, (uint64_t)N};
+            uint64_t str[3] = {128u, (uint64_t)IH * IW * 4, bstride};
+            uint32_t box[4] = {32u, (uint32_t)FH, (uint32_t)Cp, 1u};
+            return encode_tmap(ctx, tm, base, 4, dims, str, box, nullptr, 128);
+        }
         uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(x_batch ? x_batch : (long long)Cin * IH * IW) * 4};
-        if (str[1] & 15u) return CB_EUNSUPPORTED;
+        uint64_t str[2] = {(uint64_t)IH * IW * 4, bstride};
         uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
-        rc = encode_tmap(ctx, &tmX, X, 3, dims, str, box, nullptr, 128);
-        if (rc != CB_OK) return rc;
-    }
+        return encode_tmap(ctx, tm, base, 3, dims, str, box, nullptr, 128);
+    };
+    rc = encode_x(&tmX, X, x_batch);
+    if (rc != CB_OK) return rc;
     {
         uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
         uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(dy_batch ? dy_batch : (long long)OC * IH * IW) * 4};
@@ -638,10 +664,7 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     }
     CUtensorMap tmXlo = tmX, tmdYlo = tmdY;
     if (lo.x) {
-        uint64_t dims[3] = {(uint64_t)IH * IW, (uint64_t)Cin, (uint64_t)N};
-        uint64_t str[2] = {(uint64_t)IH * IW * 4, (uint64_t)(lo.x_batch ? lo.x_batch : (long long)Cin * IH * IW) * 4};
-        uint32_t box[3] = {32u, (uint32_t)Cp, 1u};
-        rc = encode_tmap(ctx, &tmXlo, lo.x, 3, dims, str, box, nullptr, 128);
+        rc = encode_x(&tmXlo, lo.x, lo.x_batch);
         if (rc != CB_OK) return rc;
         uint64_t dimsy[3] = {(uint64_t)IH * IW, (uint64_t)OC, (uint64_t)N};
         uint64_t stry[2] = {(uint64_t)IH * IW * 4, (uint64_t)(lo.dy_batch ? lo.dy_batch : (long long)OC * IH * IW) * 4};
@@ -671,10 +694,10 @@ static int wgrad_core(cb_ctx* ctx, const float* dY, const float* X, float* dW, i
     auto* reduce = groups == 2 ? wgrad_reduce_kernel<2> : (groups == 4 ? wgrad_reduce_kernel<4> : wgrad_reduce_kernel<8>);
     if (p.atomic)
         e = launch_dep(ctx, wgrad_reduce_kernel<8>, dim3((unsigned)((rgrid + 7) / 8)), dim3(32, 8), 0, p.partial, dW, 1, mtiles * 128,
-                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1, IC_total, c_off, oc_off);
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 1, IC_total, c_off, oc_off, p.rows_cf);
     else
         e = launch_dep(ctx, reduce, dim3((unsigned)rgrid), dim3(32, (unsigned)groups), 0, p.partial, dW, grid, mtiles * 128,
-                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0, IC_total, c_off, oc_off);
+                       rowsA, NQ, Cp, Cin, OC, OCp, FH, FW, accumulate ? 1 : 0, s2, IC_src, 0, IC_total, c_off, oc_off, p.rows_cf);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return check_cuda(ctx, e, "wgrad_reduce_kernel launch");
     ctx->launches += 2;
